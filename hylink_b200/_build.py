@@ -1,0 +1,149 @@
+"""In-tree build of the native libraries.
+
+Produces, under ``hylink_b200/lib/``:
+
+* ``libhylink_b200.so`` — the whole collective stack (core, control plane,
+  schedule IR, host SIMD, PCIe executor, sm_100a kernels, orchestrator, C API).
+  Host code is compiled with g++, device code with
+  ``nvcc -gencode arch=compute_100a,code=sm_100a``; the CUDA runtime is linked
+  statically and the driver is resolved at run time, so the library also loads
+  on a machine without a GPU.
+* ``libhylink_nccl.so`` — the drop-in ``nccl*`` symbol layer.
+* ``_hylink_c10d.so`` — the ``torch.distributed`` backend extension.
+
+Objects are rebuilt only when a source or any header is newer.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import os
+import shlex
+import subprocess
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+LIB = ROOT / "lib"
+OBJ = ROOT / "build" / "obj"
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+NVCC = str(CUDA_HOME / "bin" / "nvcc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+CORE_DIRS = ["core", "ctrl", "hal", "ir", "host", "pcie", "nvl", "orch", "api"]
+SEPARATE = {"nccl_shim.cpp", "cuda_block_shim.cpp"}  # built into libhylink_nccl.so
+
+
+def _run(cmd: list[str]) -> None:
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if p.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s" % (" ".join(shlex.quote(c) for c in cmd), p.stdout))
+
+
+def _newest_header() -> float:
+    t = 0.0
+    for ext in ("*.h", "*.cuh", "*.hpp"):
+        for f in CSRC.rglob(ext):
+            t = max(t, f.stat().st_mtime)
+    return t
+
+
+def _compile(src: Path, obj: Path, hdr_time: float, extra: list[str]) -> bool:
+    if obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_time):
+        return False
+    obj.parent.mkdir(parents=True, exist_ok=True)
+    inc = ["-I", str(CSRC), "-I", str(CSRC / "include"), "-I", str(CUDA_HOME / "include")]
+    if src.suffix == ".cu":
+        cmd = [NVCC, *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
+               *inc, *extra, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = ["g++", "-O2", "-g1", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function",
+               "-pthread", *inc, *extra, "-c", str(src), "-o", str(obj)]
+        if src.parent.name == "host":
+            cmd[1:1] = ["-mavx2", "-mfma", "-mf16c"]  # AVX-512 variants carry their own target attributes
+    _run(cmd)
+    return True
+
+
+def core_sources() -> list[Path]:
+    out: list[Path] = []
+    for d in CORE_DIRS:
+        p = CSRC / d
+        if not p.is_dir():
+            continue
+        for f in sorted(p.iterdir()):
+            if f.suffix in (".cpp", ".cu") and f.name not in SEPARATE:
+                out.append(f)
+    return out
+
+
+def build_core(verbose: bool = False) -> Path:
+    LIB.mkdir(parents=True, exist_ok=True)
+    hdr = _newest_header()
+    srcs = core_sources()
+    objs = [OBJ / (s.relative_to(CSRC).as_posix().replace("/", "_") + ".o") for s in srcs]
+    vis = ["-DHL_BUILDING=1"]
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+        changed = list(ex.map(lambda so: _compile(so[0], so[1], hdr, vis), zip(srcs, objs)))
+    target = LIB / "libhylink_b200.so"
+    if any(changed) or not target.exists():
+        cmd = [NVCC, *ARCH_FLAGS, "-shared", "-o", str(target), *map(str, objs), "-cudart", "static",
+               "-Xlinker", "--no-undefined", "-lpthread", "-ldl", "-lrt"]
+        _run(cmd)
+        if verbose:
+            print("linked", target)
+    return target
+
+
+def build_nccl_shim(verbose: bool = False) -> Path | None:
+    srcs = [CSRC / "api" / n for n in sorted(SEPARATE) if (CSRC / "api" / n).exists()]
+    if not srcs:
+        return None
+    hdr = _newest_header()
+    objs = [OBJ / ("shim_" + s.name + ".o") for s in srcs]
+    changed = [_compile(s, o, hdr, []) for s, o in zip(srcs, objs)]
+    target = LIB / "libhylink_nccl.so"
+    if any(changed) or not target.exists():
+        _run(["g++", "-shared", "-o", str(target), *map(str, objs), "-L", str(LIB), "-lhylink_b200",
+              "-Wl,-rpath,$ORIGIN", "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+        if verbose:
+            print("linked", target)
+    return target
+
+
+def build_torch_ext(verbose: bool = False) -> Path | None:
+    src = CSRC / "torch" / "backend.cpp"
+    if not src.exists():
+        return None
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    target = LIB / "_hylink_c10d.so"
+    hdr = _newest_header()
+    if target.exists() and target.stat().st_mtime > max(src.stat().st_mtime, hdr):
+        return target
+    tlib = Path(torch.__file__).parent / "lib"
+    inc = [f"-I{p}" for p in ce.include_paths()] + [f"-I{sysconfig.get_paths()['include']}",
+                                                     f"-I{CSRC}", f"-I{CSRC / 'include'}", f"-I{CUDA_HOME / 'include'}"]
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-DTORCH_EXTENSION_NAME=_hylink_c10d",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           "-DUSE_C10D_NCCL=0", *inc, str(src), "-o", str(target), f"-L{tlib}", "-ltorch", "-ltorch_cpu", "-lc10",
+           "-ltorch_python", "-ltorch_cuda", "-lc10_cuda", f"-L{LIB}", "-lhylink_b200",
+           f"-Wl,-rpath,{tlib}", "-Wl,-rpath,$ORIGIN", f"-L{CUDA_HOME / 'lib64'}", "-lcudart"]
+    _run(cmd)
+    if verbose:
+        print("built", target)
+    return target
+
+
+def build_all(verbose: bool = False) -> None:
+    build_core(verbose)
+    build_nccl_shim(verbose)
+    build_torch_ext(verbose)
+
+
+if __name__ == "__main__":
+    build_all(verbose=True)
+    print("ok")

@@ -1,0 +1,39 @@
+/*
+ * Low-level entry points: the single-GPU emulation of a multi-rank NVLink
+ * group (used to test the cross-rank kernels where only one GPU is present),
+ * the landing-reduce kernel, the host SIMD kernels, the schedule-IR tools and
+ * the controller objects. Everything here is also reachable from Python
+ * through ctypes.
+ */
+#ifndef HYLINK_HYLINK_EXT_H_
+#define HYLINK_HYLINK_EXT_H_
+
+#include "hylink/hylink.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- emulated NVLink group: N ranks on one device, one cooperative launch */
+typedef struct hlEmu* hlEmu_t;
+hlResult_t hlEmuCreate(int nranks, int device, size_t stage_bytes, int timeout_ms, hlEmu_t* out);
+hlResult_t hlEmuDestroy(hlEmu_t e);
+/* ins/outs: one pointer per rank. kind: 0 all-reduce, 1 reduce-scatter,
+ * 2 all-gather, 3 broadcast, 4 all-to-all, 5 barrier. */
+hlResult_t hlEmuCollective(hlEmu_t e, int kind, const void* const* ins, void* const* outs, size_t count,
+                           size_t in_seg_stride, size_t out_seg_stride, int in_dt, int out_dt, int wire_dt,
+                           int op, float scale, int root, int algo, int max_blocks, hlStream_t stream);
+hlResult_t hlEmuSetActiveRanks(hlEmu_t e, int k);
+/* status of emulated rank i: 0 ok, 1 a bounded wait ran out. detail = step<<32 | peer. */
+hlResult_t hlEmuStatus(hlEmu_t e, int i, uint64_t* code, uint64_t* detail, uint64_t* block);
+hlResult_t hlEmuReset(hlEmu_t e);
+hlResult_t hlEmuLaunches(hlEmu_t e, uint64_t* n);
+
+/* ---- landing reduce: dst = scale * op(srcs...) (+dst when accumulate) ---- */
+hlResult_t hlReduceLanding(void* dst, const void* const* srcs, int nsrc, int accumulate, size_t count,
+                           hlDataType_t t, hlRedOp_t op, float scale, int blocks, hlStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

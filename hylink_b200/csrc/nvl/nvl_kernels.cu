@@ -1,0 +1,525 @@
+// sm_100a kernels of the dedicated-link path: all-reduce (one-shot, two-shot
+// P2P, NVLS), reduce-scatter, all-gather, broadcast, all-to-all and barrier.
+//
+// Every kernel fuses, in one launch: the (converting) copy of the caller's
+// buffer into peer-mapped symmetric staging, the cross-GPU flag exchange, the
+// transfer itself (16-byte loads from peer memory issued by each CTA, or
+// multimem.ld_reduce / multimem.st through NVSwitch), the reduction with fp32
+// accumulation, the scale, and the converting store into the caller's output.
+// Segment strides and a handled-prefix length are native arguments, so the
+// orchestrator's "NVLink takes the first k elements of every segment" split
+// needs no pack or merge copies.
+//
+// Protocol rules that make staging reuse safe without extra round trips:
+//   A. a kernel touches a PEER's staging only after the first barrier of its
+//      call (the local copy-in may run before it);
+//   B. a kernel whose last phase READS peers' staging ends with a barrier;
+//   C. launches of one communicator are stream-ordered on every rank.
+// With these, when rank r starts call k+1 every peer has finished reading r's
+// staging of call k, and no peer writes r's staging of call k+1 before r has
+// entered call k+1 (its first-barrier signal) and therefore finished call k.
+//
+// Block b of a rank only ever consumes data produced by block b of a peer
+// (same in-segment packet residue class), so the barrier is per block.
+//
+// The reference delegates all of this to the vendor library
+// (multipath-orchestrator/libampccl/core/virtual_collective.h:246-252 for
+// all-reduce, :355-374 all-gather, :537-554 reduce-scatter, :740-757
+// all-to-all) and packs/merges segment prefixes with extra D2D copies
+// (virtual_collective.h:162-183).
+#include <cuda_runtime.h>
+
+#include "nvl/nvl_device.cuh"
+#include "nvl/nvl_launch.h"
+
+namespace hl {
+namespace dev {
+
+constexpr int kUnroll = 4;
+
+struct Ctx {
+  uint64_t g0;       // first in-segment packet index of this thread
+  uint64_t gstride;  // packets covered by the whole grid per sweep
+};
+__device__ __forceinline__ Ctx makeCtx() {
+  Ctx x;
+  x.g0 = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  x.gstride = (uint64_t)gridDim.x * blockDim.x;
+  return x;
+}
+
+// user segment -> staging (packets of this block's residue class)
+template <typename S, typename W, bool kMc>
+__device__ __forceinline__ void segCopyIn(uint4* stage_seg, const S* src, uint64_t seg_count, const Ctx& x) {
+  constexpr int N = Packet<W>::N;
+  const uint64_t np = (seg_count + N - 1) / N;
+  const bool vec = aligned16(src);
+  for (uint64_t i = x.g0; i < np; i += x.gstride * kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < np) v[u] = loadUserPacket<S, W>(src, j * N, seg_count, vec);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < np) {
+        if constexpr (kMc) multimemSt(stage_seg + j, v[u]);  // stage_seg is a multicast address
+        else stage_seg[j] = v[u];
+      }
+    }
+  }
+}
+
+// staging (local or peer) -> user segment
+template <typename W, typename D>
+__device__ __forceinline__ void segCopyOut(D* dst, const uint4* stage_seg, uint64_t seg_count, const Ctx& x) {
+  constexpr int N = Packet<W>::N;
+  const uint64_t np = (seg_count + N - 1) / N;
+  const bool vec = aligned16(dst);
+  for (uint64_t i = x.g0; i < np; i += x.gstride * kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < np) v[u] = stage_seg[j];
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < np) storeUserPacket<W, D>(dst, j * N, seg_count, vec, v[u]);
+    }
+  }
+}
+
+// Reduction over the same packet of every rank's staging, ranks visited in
+// ascending order whatever the caller's rank: the sum order is fixed, so the
+// result is bitwise identical on every rank and from run to run.
+template <typename W>
+__device__ __forceinline__ uint4 reducePackets(const uint4* v, int n, int op, float scale, int int_div) {
+  constexpr int N = Packet<W>::N;
+  typename Wire<W>::Acc acc[N], b[N];
+  Packet<W>::unpack(v[0], acc);
+#pragma unroll
+  for (int q = 1; q < HL_MAX_RANKS; ++q) {
+    if (q < n) {
+      Packet<W>::unpack(v[q], b);
+#pragma unroll
+      for (int i = 0; i < N; ++i) acc[i] = applyOp(op, acc[i], b[i]);
+    }
+  }
+  finish<W>(acc, scale, int_div);
+  return Packet<W>::pack(acc);
+}
+
+// Dispatch on the caller's element type. Conversions exist between fp32, fp16
+// and bf16; every other wire type requires identical user types.
+#define HL_USER_TYPE_SWITCH(W, dt, S, ...)                                    \
+  do {                                                                        \
+    if constexpr (IsFloatTrio<W>::value) {                                    \
+      switch (dt) {                                                           \
+        case hlFloat16: { using S = __half; __VA_ARGS__; } break;             \
+        case hlBfloat16: { using S = __nv_bfloat16; __VA_ARGS__; } break;     \
+        default: { using S = float; __VA_ARGS__; } break;                     \
+      }                                                                       \
+    } else {                                                                  \
+      using S = W;                                                            \
+      __VA_ARGS__;                                                            \
+    }                                                                         \
+  } while (0)
+
+template <typename W, bool kMc = false>
+__device__ __forceinline__ void copyInAny(uint4* stage_seg, const void* src, int dt, uint64_t elem_off,
+                                          uint64_t seg_count, const Ctx& x) {
+  HL_USER_TYPE_SWITCH(W, dt, S, segCopyIn<S, W, kMc>(stage_seg, reinterpret_cast<const S*>(src) + elem_off, seg_count, x));
+}
+template <typename W>
+__device__ __forceinline__ void copyOutAny(void* dst, int dt, uint64_t elem_off, const uint4* stage_seg,
+                                           uint64_t seg_count, const Ctx& x) {
+  HL_USER_TYPE_SWITCH(W, dt, D, segCopyOut<W, D>(reinterpret_cast<D*>(dst) + elem_off, stage_seg, seg_count, x));
+}
+
+__device__ __forceinline__ uint64_t segElems(uint64_t count, uint64_t first, uint64_t span) {
+  if (first >= count) return 0;
+  const uint64_t left = count - first;
+  return left < span ? left : span;
+}
+
+// ------------------------------------------------------------------ barrier
+__global__ void __launch_bounds__(HL_NVL_THREADS) kBarrier(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  blockBarrier(c, a.seq + 1, 1);
+}
+
+// ------------------------------------------------------------------ all-reduce, one-shot
+// copy-in | barrier | every rank reduces all n copies of the whole message
+// straight into its output | barrier (peers done reading).
+template <typename W>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceOneShot(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks;
+  const Ctx x = makeCtx();
+  const uint64_t np = (a.count + N - 1) / N;
+  copyInAny<W>(reinterpret_cast<uint4*>(c.stage[c.rank]), a.in, a.in_dt, 0, a.count, x);
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  const bool vec = aligned16(a.out);
+  for (uint64_t i = x.g0; i < np; i += x.gstride) {
+    uint4 v[HL_MAX_RANKS];
+#pragma unroll
+    for (int q = 0; q < HL_MAX_RANKS; ++q)
+      if (q < n) v[q] = reinterpret_cast<const uint4*>(c.stage[q])[i];
+    const uint4 r = reducePackets<W>(v, n, a.op, a.scale, a.int_div);
+    HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), i * N, a.count, vec, r));
+  }
+  blockBarrier(c, a.seq + 2, 2);
+}
+
+// ------------------------------------------------------------------ all-reduce, two-shot over P2P
+// copy-in | barrier | pull-reduce the owned shard from every peer, result
+// written in place into the local staging shard | barrier | pull every shard
+// from its owner straight into the output | barrier.
+template <typename W>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceTwoShot(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t np = (a.count + N - 1) / N;
+  const uint64_t sp = (np + n - 1) / n;  // packets per shard
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  for (int s = 0; s < n; ++s)
+    copyInAny<W>(mine + s * sp, a.in, a.in_dt, s * sp * N, segElems(a.count, s * sp * N, sp * N), x);
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  {
+    const uint64_t first = (uint64_t)r * sp;
+    const uint64_t shard_np = first >= np ? 0 : (np - first < sp ? np - first : sp);
+    for (uint64_t i = x.g0; i < shard_np; i += x.gstride * 2) {
+      uint4 v0[HL_MAX_RANKS], v1[HL_MAX_RANKS];
+      const uint64_t j = i + x.gstride;
+#pragma unroll
+      for (int q = 0; q < HL_MAX_RANKS; ++q)
+        if (q < n) {
+          v0[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + i];
+          if (j < shard_np) v1[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + j];
+        }
+      mine[first + i] = reducePackets<W>(v0, n, a.op, a.scale, a.int_div);
+      if (j < shard_np) mine[first + j] = reducePackets<W>(v1, n, a.op, a.scale, a.int_div);
+    }
+  }
+  if (!blockBarrier(c, a.seq + 2, 2)) return;
+  for (int k = 0; k < n; ++k) {
+    const int s = (r + k) % n;  // start at the local shard, then walk the peers
+    copyOutAny<W>(a.out, a.out_dt, s * sp * N, reinterpret_cast<const uint4*>(c.stage[s]) + s * sp,
+                  segElems(a.count, s * sp * N, sp * N), x);
+  }
+  blockBarrier(c, a.seq + 3, 3);
+}
+
+// ------------------------------------------------------------------ all-reduce through NVSwitch (NVLS)
+// copy-in | barrier | multimem.ld_reduce of the owned shard (the switch sums
+// all ranks' copies, fp32 accumulate), scale, multimem.st back in place into
+// every rank's staging | barrier | local copy-out.
+template <typename W>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceNvls(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t np = (a.count + N - 1) / N;
+  const uint64_t sp = (np + n - 1) / n;
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  for (int s = 0; s < n; ++s)
+    copyInAny<W>(mine + s * sp, a.in, a.in_dt, s * sp * N, segElems(a.count, s * sp * N, sp * N), x);
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  {
+    const uint64_t first = (uint64_t)r * sp;
+    const uint64_t shard_np = first >= np ? 0 : (np - first < sp ? np - first : sp);
+    uint4* mc = reinterpret_cast<uint4*>(c.mc_stage) + first;
+    for (uint64_t i = x.g0; i < shard_np; i += x.gstride * kUnroll) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint64_t j = i + (uint64_t)u * x.gstride;
+        if (j < shard_np) v[u] = multimemLdReduceAdd<W>(mc + j);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint64_t j = i + (uint64_t)u * x.gstride;
+        if (j < shard_np) {
+          if (a.scale != 1.0f) {
+            typename Wire<W>::Acc acc[N];
+            Packet<W>::unpack(v[u], acc);
+            finish<W>(acc, a.scale, 0);
+            v[u] = Packet<W>::pack(acc);
+          }
+          multimemSt(mc + j, v[u]);
+        }
+      }
+    }
+  }
+  if (!blockBarrier(c, a.seq + 2, 2)) return;
+  for (int s = 0; s < n; ++s)
+    copyOutAny<W>(a.out, a.out_dt, s * sp * N, mine + s * sp, segElems(a.count, s * sp * N, sp * N), x);
+}
+
+// ------------------------------------------------------------------ reduce-scatter
+// `in` holds n segments (stride in_seg_stride); the first `count` elements of
+// each are handled. copy-in | barrier | pull-reduce segment r from every peer
+// straight into the output | barrier.
+template <typename W, bool kNvls>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kReduceScatter(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t sp = (a.count + N - 1) / N;
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  for (int s = 0; s < n; ++s) copyInAny<W>(mine + s * sp, a.in, a.in_dt, s * a.in_seg_stride, a.count, x);
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  const bool vec = aligned16(a.out);
+  const uint64_t first = (uint64_t)r * sp;
+  if constexpr (kNvls) {
+    const uint4* mc = reinterpret_cast<const uint4*>(c.mc_stage) + first;
+    for (uint64_t i = x.g0; i < sp; i += x.gstride * kUnroll) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint64_t j = i + (uint64_t)u * x.gstride;
+        if (j < sp) v[u] = multimemLdReduceAdd<W>(mc + j);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const uint64_t j = i + (uint64_t)u * x.gstride;
+        if (j < sp) {
+          if (a.scale != 1.0f) {
+            typename Wire<W>::Acc acc[N];
+            Packet<W>::unpack(v[u], acc);
+            finish<W>(acc, a.scale, 0);
+            v[u] = Packet<W>::pack(acc);
+          }
+          HL_USER_TYPE_SWITCH(W, a.out_dt, D,
+                              storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), j * N, a.count, vec, v[u]));
+        }
+      }
+    }
+  } else {
+    for (uint64_t i = x.g0; i < sp; i += x.gstride * 2) {
+      uint4 v0[HL_MAX_RANKS], v1[HL_MAX_RANKS];
+      const uint64_t j = i + x.gstride;
+#pragma unroll
+      for (int q = 0; q < HL_MAX_RANKS; ++q)
+        if (q < n) {
+          v0[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + i];
+          if (j < sp) v1[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + j];
+        }
+      const uint4 r0 = reducePackets<W>(v0, n, a.op, a.scale, a.int_div);
+      HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), i * N, a.count, vec, r0));
+      if (j < sp) {
+        const uint4 r1 = reducePackets<W>(v1, n, a.op, a.scale, a.int_div);
+        HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), j * N, a.count, vec, r1));
+      }
+    }
+  }
+  blockBarrier(c, a.seq + 2, 2);
+}
+
+// ------------------------------------------------------------------ all-gather
+// P2P: copy-in of the local prefix | barrier | pull every rank's prefix into
+// out + q*out_seg_stride | barrier.
+// NVLS: barrier | multimem.st of the local prefix from the caller's buffer into
+// slot r of every rank's staging (one store, n destinations) | barrier | local
+// copy-out of all n slots.
+template <typename W, bool kNvls>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kAllGather(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t sp = (a.count + N - 1) / N;
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  if constexpr (kNvls) {
+    if (!blockBarrier(c, a.seq + 1, 1)) return;
+    uint4* mc = reinterpret_cast<uint4*>(c.mc_stage) + (uint64_t)r * sp;
+    copyInAny<W, true>(mc, a.in, a.in_dt, 0, a.count, x);
+    if (!blockBarrier(c, a.seq + 2, 2)) return;
+    for (int q = 0; q < n; ++q) copyOutAny<W>(a.out, a.out_dt, q * a.out_seg_stride, mine + q * sp, a.count, x);
+  } else {
+    copyInAny<W>(mine, a.in, a.in_dt, 0, a.count, x);
+    if (!blockBarrier(c, a.seq + 1, 1)) return;
+    for (int k = 0; k < n; ++k) {
+      const int q = (r + k) % n;
+      copyOutAny<W>(a.out, a.out_dt, q * a.out_seg_stride, reinterpret_cast<const uint4*>(c.stage[q]), a.count, x);
+    }
+    blockBarrier(c, a.seq + 2, 2);
+  }
+}
+
+// ------------------------------------------------------------------ broadcast
+template <typename W, bool kNvls>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int r = c.rank;
+  const Ctx x = makeCtx();
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  if constexpr (kNvls) {
+    if (!blockBarrier(c, a.seq + 1, 1)) return;
+    if (r == a.root) {
+      uint4* mc = reinterpret_cast<uint4*>(c.mc_stage);
+      copyInAny<W, true>(mc, a.in, a.in_dt, 0, a.count, x);
+    }
+    if (!blockBarrier(c, a.seq + 2, 2)) return;
+    if (r != a.root || a.out != a.in) copyOutAny<W>(a.out, a.out_dt, 0, mine, a.count, x);
+  } else {
+    if (r == a.root) copyInAny<W>(mine, a.in, a.in_dt, 0, a.count, x);
+    if (!blockBarrier(c, a.seq + 1, 1)) return;
+    if (r != a.root || a.out != a.in)
+      copyOutAny<W>(a.out, a.out_dt, 0, reinterpret_cast<const uint4*>(c.stage[a.root]), a.count, x);
+    blockBarrier(c, a.seq + 2, 2);
+  }
+}
+
+// ------------------------------------------------------------------ all-to-all
+// Segment q of `in` goes to rank q; segment q of `out` comes from rank q.
+template <typename W>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kAllToAll(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t sp = (a.count + N - 1) / N;
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  for (int s = 0; s < n; ++s) copyInAny<W>(mine + s * sp, a.in, a.in_dt, s * a.in_seg_stride, a.count, x);
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  for (int k = 0; k < n; ++k) {
+    const int q = (r + k) % n;
+    copyOutAny<W>(a.out, a.out_dt, q * a.out_seg_stride, reinterpret_cast<const uint4*>(c.stage[q]) + (uint64_t)r * sp,
+                  a.count, x);
+  }
+  blockBarrier(c, a.seq + 2, 2);
+}
+
+}  // namespace dev
+
+// ====================================================================== host
+namespace nvl {
+
+template <typename W>
+static const void* pickKernelT(int kind) {
+  using namespace dev;
+  switch (kind) {
+    case kNvlAllReduceOneShot: return (const void*)kAllReduceOneShot<W>;
+    case kNvlAllReduceTwoShot: return (const void*)kAllReduceTwoShot<W>;
+    case kNvlReduceScatter: return (const void*)kReduceScatter<W, false>;
+    case kNvlAllGather: return (const void*)kAllGather<W, false>;
+    case kNvlBroadcast: return (const void*)kBroadcast<W, false>;
+    case kNvlAllToAll: return (const void*)kAllToAll<W>;
+    case kNvlAllGatherNvls: return (const void*)kAllGather<W, true>;
+    case kNvlBroadcastNvls: return (const void*)kBroadcast<W, true>;
+    default: break;
+  }
+  if constexpr (dev::IsFloatTrio<W>::value) {
+    switch (kind) {
+      case kNvlAllReduceNvls: return (const void*)kAllReduceNvls<W>;
+      case kNvlReduceScatterNvls: return (const void*)kReduceScatter<W, true>;
+      default: break;
+    }
+  }
+  return nullptr;
+}
+
+const void* kernelFor(int kind, int wire_dt) {
+  if (kind == kNvlBarrier) return (const void*)dev::kBarrier;
+  switch (wire_dt) {
+    case hlInt8: return pickKernelT<int8_t>(kind);
+    case hlUint8: return pickKernelT<uint8_t>(kind);
+    case hlInt32: return pickKernelT<int32_t>(kind);
+    case hlUint32: return pickKernelT<uint32_t>(kind);
+    case hlInt64: return pickKernelT<long long>(kind);
+    case hlUint64: return pickKernelT<unsigned long long>(kind);
+    case hlFloat16: return pickKernelT<__half>(kind);
+    case hlFloat32: return pickKernelT<float>(kind);
+    case hlFloat64: return pickKernelT<double>(kind);
+    case hlBfloat16: return pickKernelT<__nv_bfloat16>(kind);
+    default: return nullptr;
+  }
+}
+
+const char* kernelName(int kind) {
+  switch (kind) {
+    case kNvlBarrier: return "barrier";
+    case kNvlAllReduceOneShot: return "allreduce_oneshot";
+    case kNvlAllReduceTwoShot: return "allreduce_twoshot_p2p";
+    case kNvlAllReduceNvls: return "allreduce_nvls";
+    case kNvlReduceScatter: return "reducescatter_p2p";
+    case kNvlReduceScatterNvls: return "reducescatter_nvls";
+    case kNvlAllGather: return "allgather_p2p";
+    case kNvlBroadcast: return "broadcast_p2p";
+    case kNvlAllToAll: return "alltoall_p2p";
+    case kNvlAllGatherNvls: return "allgather_nvls";
+    case kNvlBroadcastNvls: return "broadcast_nvls";
+    default: return "?";
+  }
+}
+
+hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCalls& calls, int emu_ranks, int blocks,
+                  cudaStream_t stream) {
+  const void* fn = kernelFor(kind, wire_dt);
+  if (!fn) return fail(hlUnsupported, "no %s kernel for wire type %d", kernelName(kind), wire_dt);
+  if (blocks < 1) blocks = 1;
+  if (blocks > HL_MAX_BLOCKS) blocks = HL_MAX_BLOCKS;
+  dim3 grid((unsigned)blocks, (unsigned)(emu_ranks > 1 ? emu_ranks : 1), 1);
+  dim3 block(HL_NVL_THREADS, 1, 1);
+  void* args[2] = {(void*)&dcomms, (void*)&calls};
+  cudaError_t e;
+  if (emu_ranks > 1) {
+    // The emulated ranks wait on one another: all their blocks must be
+    // co-resident, which only a cooperative launch guarantees (it fails
+    // cleanly instead of deadlocking when they would not fit).
+    e = cudaLaunchCooperativeKernel(fn, grid, block, args, 0, stream);
+  } else {
+    e = cudaLaunchKernel(fn, grid, block, args, 0, stream);
+  }
+  if (e != cudaSuccess) return fail(hlDeviceError, "launch of %s failed: %s", kernelName(kind), cudaGetErrorString(e));
+  return hlSuccess;
+}
+
+hlResult_t prepareKernels() {
+  // Resolve every variant once on the init thread: lazy module loading plus
+  // concurrent first launches from several threads can deadlock in the driver
+  // (same cure as pcie-ccl-cuda/kernels/wait_kernel.cu:216-234,400-432).
+  static const int kinds[] = {kNvlBarrier, kNvlAllReduceOneShot, kNvlAllReduceTwoShot, kNvlAllReduceNvls,
+                              kNvlReduceScatter, kNvlReduceScatterNvls, kNvlAllGather, kNvlBroadcast,
+                              kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls};
+  for (int k : kinds)
+    for (int dt = 0; dt < hlNumTypes; ++dt) {
+      const void* fn = kernelFor(k, dt);
+      if (!fn) continue;
+      cudaFuncAttributes at;
+      cudaError_t e = cudaFuncGetAttributes(&at, fn);
+      if (e != cudaSuccess) return fail(hlDeviceError, "cudaFuncGetAttributes: %s", cudaGetErrorString(e));
+      if (k == kNvlBarrier) break;
+    }
+  return hlSuccess;
+}
+
+}  // namespace nvl
+}  // namespace hl

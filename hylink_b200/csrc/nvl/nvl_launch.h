@@ -1,0 +1,47 @@
+// Host-side launch interface of the NVLink-path kernels and of the landing
+// reduce kernel (the only parts of the library compiled by nvcc).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "core/core.h"
+#include "nvl/nvl_types.h"
+
+namespace hl {
+namespace nvl {
+
+const void* kernelFor(int kind, int wire_dt);
+const char* kernelName(int kind);
+// emu_ranks > 1: cooperative launch with one grid row per emulated rank.
+hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCalls& calls, int emu_ranks, int blocks,
+                  cudaStream_t stream);
+hlResult_t prepareKernels();
+
+// dst[i] = scale * op(src_0[i], ..., src_{k-1}[i]) with fp32 accumulation for
+// 16-bit floats; when `accumulate` is set dst itself is the first operand.
+// Sources may live in pinned host memory (zero-copy read over PCIe).
+struct ReduceLandingArgs {
+  void* dst;
+  const void* src[8];
+  int nsrc;
+  int accumulate;
+  uint64_t count;
+  int dtype;      // element type of dst and of every source
+  int op;
+  float scale;
+};
+hlResult_t launchReduceLanding(const ReduceLandingArgs& a, int blocks, cudaStream_t stream);
+hlResult_t prepareReduceLanding();
+
+// Context warm-up (one trivial kernel): a context whose first work is pure
+// copy-engine traffic may stall (pcie-ccl-cuda/src/api/pccl_api.cpp:720-746).
+hlResult_t launchWarmup(cudaStream_t stream);
+
+// Doorbell fallback for drivers without stream memory operations: writes
+// `ready_value` to a host-mapped word, then waits (bounded) until
+// *complete >= wait_value. On expiry it writes HL_DEV_TIMEOUT to *status.
+hlResult_t launchDoorbell(volatile uint64_t* ready, uint64_t ready_value, volatile uint64_t* complete,
+                          uint64_t wait_value, uint64_t timeout_ns, uint64_t* status, const char* tag,
+                          cudaStream_t stream);
+
+}  // namespace nvl
+}  // namespace hl

@@ -1,0 +1,262 @@
+#include "nvl/nvl_path.h"
+
+#include <algorithm>
+#include <cstring>
+#include <memory>
+
+namespace hl {
+
+static constexpr size_t kFlagBytes = (size_t)HL_MAX_BLOCKS * HL_MAX_RANKS * sizeof(uint64_t);
+
+static size_t flagAreaBytes() { return (kFlagBytes + 4095) & ~(size_t)4095; }
+
+NvlPath::~NvlPath() {
+  if (device_ >= 0) cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  if (order_ev_) cudaEventDestroy(order_ev_);
+  if (dcomm_) cudaFree(dcomm_);
+  if (abort_dev_) cudaFree(abort_dev_);
+  if (status_host_) cudaFreeHost(status_host_);
+  if (emu_) {
+    for (int q = 0; q < nranks_; ++q)
+      if (emu_mem_[q]) cudaFree(emu_mem_[q]);
+  } else {
+    const bool gone = bs_ ? bs_->anyFailed() : true;
+    symmFree(bs_, &region_, gone);
+  }
+  cudaGetLastError();
+}
+
+hlResult_t NvlPath::finishInit(int timeout_ms) {
+  const int nl = localRanks();
+  HL_CUDA(cudaHostAlloc((void**)&status_host_, sizeof(uint64_t) * 8 * nl, cudaHostAllocMapped | cudaHostAllocPortable));
+  memset(status_host_, 0, sizeof(uint64_t) * 8 * nl);
+  uint64_t* status_dev = nullptr;
+  HL_CUDA(cudaHostGetDevicePointer((void**)&status_dev, status_host_, 0));
+  HL_CUDA(cudaMalloc((void**)&abort_dev_, sizeof(uint32_t) * 16 * nl));
+  HL_CUDA(cudaMemset(abort_dev_, 0, sizeof(uint32_t) * 16 * nl));
+  HlCommDev h[HL_MAX_RANKS];
+  memset(h, 0, sizeof(h));
+  for (int i = 0; i < nl; ++i) {
+    HlCommDev& c = h[i];
+    c.rank = emu_ ? i : rank_;
+    c.nranks = nranks_;
+    c.max_blocks = HL_MAX_BLOCKS;
+    for (int q = 0; q < nranks_; ++q) {
+      uint8_t* base = (uint8_t*)(emu_ ? emu_mem_[q] : region_.ptr[q]);
+      c.stage[q] = base;
+      c.flags[q] = (uint64_t*)(base + stage_bytes_);
+    }
+    c.mc_stage = emu_ ? nullptr : (uint8_t*)region_.mc;
+    c.status = status_dev + 8 * i;
+    c.abort_word = abort_dev_ + 16 * i;
+    c.stage_bytes = stage_bytes_;
+    c.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
+  }
+  HL_CUDA(cudaMalloc((void**)&dcomm_, sizeof(HlCommDev) * nl));
+  HL_CUDA(cudaMemcpy(dcomm_, h, sizeof(HlCommDev) * nl, cudaMemcpyHostToDevice));
+  HL_CUDA(cudaEventCreateWithFlags(&order_ev_, cudaEventDisableTiming));
+  HL_CHECK(nvl::prepareKernels());
+  HL_CUDA(cudaDeviceSynchronize());
+  return hlSuccess;
+}
+
+hlResult_t NvlPath::createReal(Bootstrap* bs, int device, NvlPath** out) {
+  const Config& cfg = Config::get();
+  std::unique_ptr<NvlPath> p(new NvlPath());
+  p->bs_ = bs;
+  p->rank_ = bs->rank();
+  p->nranks_ = bs->nranks();
+  p->device_ = device;
+  p->stage_bytes_ = (cfg.symm_stage_bytes + 4095) & ~(size_t)4095;
+  HL_CUDA(cudaSetDevice(device));
+  HL_CHECK(symmAlloc(bs, device, p->stage_bytes_ + flagAreaBytes(), cfg.nvls, cfg.symm_mode, &p->region_));
+  p->has_mc_ = p->region_.mc != nullptr;
+  // flags start at zero on every rank before anybody launches
+  HL_CUDA(cudaMemset((uint8_t*)p->region_.ptr[p->rank_] + p->stage_bytes_, 0, flagAreaBytes()));
+  HL_CUDA(cudaDeviceSynchronize());
+  HL_CHECK(p->finishInit(cfg.nvl_timeout_ms));
+  HL_CHECK(bs->barrier(kBarSymm));
+  HL_INFO("NVLink path ready: rank %d/%d dev %d symm=%d nvls=%d stage=%zu MiB", p->rank_, p->nranks_, device,
+          p->region_.mode, (int)p->has_mc_, p->stage_bytes_ >> 20);
+  *out = p.release();
+  return hlSuccess;
+}
+
+hlResult_t NvlPath::createEmu(int nranks, int device, size_t stage_bytes, int timeout_ms, NvlPath** out) {
+  if (nranks < 1 || nranks > HL_MAX_RANKS) return fail(hlInvalidArgument, "emulated nranks %d out of range", nranks);
+  std::unique_ptr<NvlPath> p(new NvlPath());
+  p->emu_ = true;
+  p->nranks_ = nranks;
+  p->emu_active_ = nranks;
+  p->device_ = device;
+  p->stage_bytes_ = (stage_bytes + 4095) & ~(size_t)4095;
+  HL_CUDA(cudaSetDevice(device));
+  for (int q = 0; q < nranks; ++q) {
+    HL_CUDA(cudaMalloc(&p->emu_mem_[q], p->stage_bytes_ + flagAreaBytes()));
+    HL_CUDA(cudaMemset((uint8_t*)p->emu_mem_[q] + p->stage_bytes_, 0, flagAreaBytes()));
+  }
+  HL_CHECK(p->finishInit(timeout_ms));
+  *out = p.release();
+  return hlSuccess;
+}
+
+uint64_t NvlPath::deviceStatus(int i, uint64_t* detail, uint64_t* block) const {
+  volatile uint64_t* s = status_host_ + 8 * i;
+  if (detail) *detail = s[1];
+  if (block) *block = s[2];
+  return s[0];
+}
+
+hlResult_t NvlPath::resetAfterError() {
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CUDA(cudaDeviceSynchronize());
+  const int nl = localRanks();
+  if (!emu_ && bs_) HL_CHECK(bs_->barrier(kBarSymm));
+  if (emu_) {
+    for (int q = 0; q < nranks_; ++q) HL_CUDA(cudaMemset((uint8_t*)emu_mem_[q] + stage_bytes_, 0, flagAreaBytes()));
+  } else {
+    HL_CUDA(cudaMemset((uint8_t*)region_.ptr[rank_] + stage_bytes_, 0, flagAreaBytes()));
+  }
+  HL_CUDA(cudaMemset(abort_dev_, 0, sizeof(uint32_t) * 16 * nl));
+  memset(status_host_, 0, sizeof(uint64_t) * 8 * nl);
+  HL_CUDA(cudaDeviceSynchronize());
+  seq_ = 0;
+  if (!emu_ && bs_) HL_CHECK(bs_->barrier(kBarSymm));
+  return hlSuccess;
+}
+
+hlResult_t NvlPath::orderAfterPrevious(cudaStream_t s) {
+  // Rule C of the kernels' protocol: consecutive launches of one communicator
+  // must not overlap on this rank, whatever streams the caller uses.
+  if (have_last_ && last_stream_ != s) {
+    HL_CUDA(cudaEventRecord(order_ev_, last_stream_));
+    HL_CUDA(cudaStreamWaitEvent(s, order_ev_, 0));
+  }
+  last_stream_ = s;
+  have_last_ = true;
+  return hlSuccess;
+}
+
+int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const {
+  const bool nvls_ok = has_mc_ && (wire_dt == hlFloat32 || wire_dt == hlFloat16 || wire_dt == hlBfloat16) &&
+                       (op == hlSum || op == hlAvg) && !deterministic;
+  if (requested == hlAlgoNvls && !nvls_ok) requested = hlAlgoAuto;
+  if (requested != hlAlgoAuto) return requested;
+  if (wire_bytes <= Config::get().oneshot_max_bytes) return hlAlgoOneShot;
+  return nvls_ok ? hlAlgoNvls : hlAlgoTwoShotP2p;
+}
+
+int NvlPath::blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const {
+  (void)kind;
+  int cap = max_blocks > 0 ? max_blocks : (Config::get().nvl_max_blocks > 0 ? Config::get().nvl_max_blocks : 148);
+  if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));
+  cap = std::min(cap, HL_MAX_BLOCKS);
+  // one CTA per 64 KiB moved, at least one
+  size_t want = (wire_bytes_per_rank + (64u << 10) - 1) / (64u << 10);
+  if (want < 1) want = 1;
+  return (int)std::min<size_t>(want, (size_t)cap);
+}
+
+hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, bool segmented, cudaStream_t s) {
+  const size_t ws = hlTypeSize((hlDataType_t)c.wire_dt);
+  const size_t is = hlTypeSize((hlDataType_t)c.in_dt), os = hlTypeSize((hlDataType_t)c.out_dt);
+  if (!ws || !is || !os) return fail(hlInvalidArgument, "unknown data type");
+  const bool trio = [&](int d) { return d == hlFloat32 || d == hlFloat16 || d == hlBfloat16; }(c.wire_dt);
+  if (!trio && (c.in_dt != c.wire_dt || c.out_dt != c.wire_dt))
+    return fail(hlUnsupported, "type conversion is only available between fp32, fp16 and bf16");
+  if (trio) {
+    auto is_trio = [](int d) { return d == hlFloat32 || d == hlFloat16 || d == hlBfloat16; };
+    if (!is_trio(c.in_dt) || !is_trio(c.out_dt)) return fail(hlUnsupported, "cannot convert integer/fp64 buffers to a float wire type");
+  }
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CHECK(orderAfterPrevious(s));
+  const int nl = localRanks();
+  const uint64_t epp = 16 / ws;                         // elements per wire packet
+  const uint64_t cap_packets = stage_bytes_ / 16;
+  uint64_t per_launch;                                  // elements handled per launch (per segment when segmented)
+  if (segmented || kind == kNvlAllReduceTwoShot || kind == kNvlAllReduceNvls) {
+    uint64_t sp = (cap_packets / (uint64_t)nranks_) & ~(uint64_t)63;
+    if (sp == 0) return fail(hlInvalidArgument, "staging region too small");
+    per_launch = (segmented ? sp : sp * (uint64_t)nranks_) * epp;
+  } else {
+    per_launch = (cap_packets & ~(uint64_t)63) * epp;
+  }
+  uint64_t done = 0;
+  do {
+    const uint64_t len = std::min<uint64_t>(per_launch, c.count - done);
+    HlEmuCalls calls;
+    memset(&calls, 0, sizeof(calls));
+    for (int i = 0; i < nl; ++i) {
+      HlCallArgs& a = calls.c[i];
+      a.in = b.in[i] ? (const char*)b.in[i] + done * is : nullptr;
+      a.out = b.out[i] ? (char*)b.out[i] + done * os : nullptr;
+      a.count = len;
+      a.in_seg_stride = c.in_seg_stride ? c.in_seg_stride : c.count;
+      a.out_seg_stride = c.out_seg_stride ? c.out_seg_stride : c.count;
+      a.seq = seq_;
+      a.scale = (c.scale == 0.0f ? 1.0f : c.scale) * (c.op == hlAvg ? 1.0f / (float)nranks_ : 1.0f);
+      a.op = c.op;
+      a.in_dt = c.in_dt;
+      a.out_dt = c.out_dt;
+      a.root = c.root;
+      a.int_div = (c.op == hlAvg) ? nranks_ : 0;
+    }
+    const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls ? nranks_ : 1);
+    const int blocks = blocksFor(kind, wire_bytes, c.max_blocks);
+    seq_ += HL_SEQ_STRIDE;
+    const int rows = emu_ ? emu_active_ : 1;
+    HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, rows, blocks, s));
+    ++launches_;
+    done += len;
+  } while (done < c.count);
+  return hlSuccess;
+}
+
+hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
+  if (c.count == 0) return hlSuccess;
+  const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
+  int algo = pickAllReduceAlgo(wire_bytes, c.wire_dt, c.op, c.deterministic, c.algo);
+  if (algo == hlAlgoOneShot && wire_bytes > stage_bytes_) algo = hlAlgoTwoShotP2p;
+  const int kind = algo == hlAlgoOneShot ? kNvlAllReduceOneShot : (algo == hlAlgoNvls ? kNvlAllReduceNvls : kNvlAllReduceTwoShot);
+  return launchSliced(kind, b, c, false, s);
+}
+
+hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
+  if (c.count == 0) return hlSuccess;
+  const bool nvls = has_mc_ && !c.deterministic && (c.op == hlSum || c.op == hlAvg) && c.algo != hlAlgoTwoShotP2p &&
+                    c.algo != hlAlgoOneShot &&
+                    (c.wire_dt == hlFloat32 || c.wire_dt == hlFloat16 || c.wire_dt == hlBfloat16);
+  return launchSliced(nvls ? kNvlReduceScatterNvls : kNvlReduceScatter, b, c, true, s);
+}
+
+hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
+  if (c.count == 0) return hlSuccess;
+  const bool nvls = has_mc_ && c.algo == hlAlgoNvls;
+  return launchSliced(nvls ? kNvlAllGatherNvls : kNvlAllGather, b, c, true, s);
+}
+
+hlResult_t NvlPath::broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
+  if (c.count == 0) return hlSuccess;
+  if (c.root < 0 || c.root >= nranks_) return fail(hlInvalidArgument, "broadcast root %d out of range", c.root);
+  const bool nvls = has_mc_ && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot;
+  return launchSliced(nvls ? kNvlBroadcastNvls : kNvlBroadcast, b, c, false, s);
+}
+
+hlResult_t NvlPath::allToAll(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
+  if (c.count == 0) return hlSuccess;
+  return launchSliced(kNvlAllToAll, b, c, true, s);
+}
+
+hlResult_t NvlPath::barrier(cudaStream_t s) {
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CHECK(orderAfterPrevious(s));
+  HlEmuCalls calls;
+  memset(&calls, 0, sizeof(calls));
+  for (int i = 0; i < localRanks(); ++i) calls.c[i].seq = seq_;
+  seq_ += HL_SEQ_STRIDE;
+  ++launches_;
+  return nvl::launch(kNvlBarrier, hlFloat32, dcomm_, calls, emu_ ? emu_active_ : 1, 1, s);
+}
+
+}  // namespace hl

@@ -1,0 +1,94 @@
+// Host side of the dedicated-link path: owns the symmetric staging region and
+// the flag area, chooses algorithm and CTA count per call, slices messages
+// that exceed the staging capacity, and launches the sm_100a kernels.
+//
+// Two flavours share all of the code: a real path (one rank per process or
+// thread, peers reached over NVLink) and an emulated group (N ranks on ONE
+// device, launched as one cooperative grid) that lets a single-GPU machine
+// check the cross-rank protocol of every kernel.
+//
+// Parity: stands where the reference's fast backend calls the vendor library
+// (multipath-orchestrator/libampccl/backend/fast_backend.cc:7-103,
+// original_collective_api.cc:60-148).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "ctrl/bootstrap.h"
+#include "nvl/nvl_launch.h"
+#include "nvl/symm_mem.h"
+
+namespace hl {
+
+struct NvlBufs {
+  const void* in[HL_MAX_RANKS];
+  void* out[HL_MAX_RANKS];
+};
+
+struct NvlCall {
+  uint64_t count = 0;           // AR/bcast: elements; AG/RS/A2A: handled prefix of a segment
+  uint64_t in_seg_stride = 0;   // elements between input segments (RS, A2A); 0 = count
+  uint64_t out_seg_stride = 0;  // elements between output segments (AG, A2A); 0 = count
+  int in_dt = hlFloat32, out_dt = hlFloat32, wire_dt = hlFloat32;
+  int op = hlSum;
+  float scale = 1.0f;
+  int root = 0;
+  int algo = hlAlgoAuto;
+  int max_blocks = 0;
+  bool deterministic = false;
+};
+
+class NvlPath {
+ public:
+  ~NvlPath();
+  static hlResult_t createReal(Bootstrap* bs, int device, NvlPath** out);
+  static hlResult_t createEmu(int nranks, int device, size_t stage_bytes, int timeout_ms, NvlPath** out);
+
+  int nranks() const { return nranks_; }
+  int localRanks() const { return emu_ ? nranks_ : 1; }
+  bool hasNvls() const { return has_mc_; }
+  int symmMode() const { return region_.mode; }
+  size_t stageBytes() const { return stage_bytes_; }
+  uint64_t launches() const { return launches_; }
+  // Emulation only: launch just the first k ranks' rows (the others never
+  // signal), to exercise the bounded-wait error path without hanging anything.
+  void setEmuActiveRanks(int k) { emu_active_ = k; }
+
+  hlResult_t allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
+  hlResult_t reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
+  hlResult_t allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
+  hlResult_t broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
+  hlResult_t allToAll(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
+  hlResult_t barrier(cudaStream_t s);
+
+  // Device status of local rank i: HL_DEV_OK or the code a kernel recorded.
+  uint64_t deviceStatus(int i = 0, uint64_t* detail = nullptr, uint64_t* block = nullptr) const;
+  // Clears the poison after a recorded timeout (all ranks, collectively, with
+  // no launch in flight); flags and sequence restart from a common value.
+  hlResult_t resetAfterError();
+  int pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const;
+  int blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const;
+
+ private:
+  NvlPath() = default;
+  hlResult_t finishInit(int timeout_ms);
+  hlResult_t launchSliced(int kind, const NvlBufs& b, const NvlCall& c, bool segmented, cudaStream_t s);
+  hlResult_t orderAfterPrevious(cudaStream_t s);
+  Bootstrap* bs_ = nullptr;
+  bool emu_ = false;
+  int emu_active_ = 0;
+  int rank_ = 0, nranks_ = 1, device_ = 0;
+  size_t stage_bytes_ = 0;
+  bool has_mc_ = false;
+  SymmRegion region_;
+  void* emu_mem_[HL_MAX_RANKS] = {nullptr};
+  HlCommDev* dcomm_ = nullptr;     // device array: 1 entry (real) or nranks (emu)
+  uint64_t* status_host_ = nullptr; // pinned, mapped; 8 words per local rank
+  uint32_t* abort_dev_ = nullptr;   // one word per local rank
+  uint64_t seq_ = 0;
+  uint64_t launches_ = 0;
+  cudaEvent_t order_ev_ = nullptr;
+  cudaStream_t last_stream_ = nullptr;
+  bool have_last_ = false;
+};
+
+}  // namespace hl

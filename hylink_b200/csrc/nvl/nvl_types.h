@@ -1,0 +1,69 @@
+// Plain-data structures shared by host code and the sm_100a kernels of the
+// dedicated-link (NVLink 5 / NVSwitch) path.
+#pragma once
+#include <stdint.h>
+
+#define HL_MAX_RANKS 8        // one NVSwitch domain of an HGX B200 board
+#define HL_MAX_BLOCKS 592     // 148 SMs x 4 resident CTAs
+#define HL_NVL_THREADS 512
+#define HL_SEQ_STRIDE 4       // flag values consumed per collective call
+
+// Device status codes written by a kernel whose bounded wait ran out.
+#define HL_DEV_OK 0
+#define HL_DEV_TIMEOUT 1
+#define HL_DEV_ABORTED 2
+#define HL_DEV_BOUNDS 3
+
+// Per-communicator constants, resident in device memory. Every pointer table
+// holds, for each rank q, the address at which THIS rank maps q's region
+// (entry [rank] is the local region itself).
+struct HlCommDev {
+  int rank;
+  int nranks;
+  int max_blocks;
+  int pad0;
+  uint8_t* stage[HL_MAX_RANKS];    // symmetric staging region
+  uint64_t* flags[HL_MAX_RANKS];   // [HL_MAX_BLOCKS][HL_MAX_RANKS] monotonically increasing words
+  uint8_t* mc_stage;               // NVSwitch multicast alias of stage (null without NVLS)
+  uint64_t* status;                // host-visible: [0] code, [1] detail (step<<32 | peer), [2] block
+  uint32_t* abort_word;            // device word: non-zero poisons the communicator
+  uint64_t stage_bytes;
+  uint64_t timeout_ns;
+};
+
+// Per-call arguments (by value in the launch).
+struct HlCallArgs {
+  const void* in;
+  void* out;
+  uint64_t count;           // elements: AR/bcast total; AG/RS/A2A the handled prefix of one segment
+  uint64_t in_seg_stride;   // elements between segments of `in`  (RS, A2A)
+  uint64_t out_seg_stride;  // elements between segments of `out` (AG, A2A)
+  uint64_t seq;             // flag base of this call; barrier k waits for seq + k
+  float scale;              // applied to the reduced value (floating types)
+  int op;                   // hlRedOp_t
+  int in_dt;                // hlDataType_t of `in`
+  int out_dt;               // hlDataType_t of `out`
+  int root;
+  int int_div;              // integer types: divide the sum (hlAvg), 0 = off
+};
+
+// One argument block per emulated rank: on a single GPU the N ranks of a test
+// run as ONE cooperative launch with gridDim.y == N (kernels that wait on one
+// another must never be separate launches on one device).
+struct HlEmuCalls {
+  HlCallArgs c[HL_MAX_RANKS];
+};
+
+enum HlNvlKernel {
+  kNvlBarrier = 0,
+  kNvlAllReduceOneShot = 1,
+  kNvlAllReduceTwoShot = 2,
+  kNvlAllReduceNvls = 3,
+  kNvlReduceScatter = 4,
+  kNvlReduceScatterNvls = 5,
+  kNvlAllGather = 6,
+  kNvlBroadcast = 7,
+  kNvlAllToAll = 8,
+  kNvlAllGatherNvls = 9,
+  kNvlBroadcastNvls = 10,
+};
