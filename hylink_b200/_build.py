@@ -129,7 +129,7 @@ def build_torch_ext(verbose: bool = False) -> Path | None:
                                                      f"-I{CSRC}", f"-I{CSRC / 'include'}", f"-I{CUDA_HOME / 'include'}"]
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-DTORCH_EXTENSION_NAME=_hylink_c10d",
            "-DTORCH_API_INCLUDE_EXTENSION_H", "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
-           "-DUSE_C10D_NCCL=0", *inc, str(src), "-o", str(target), f"-L{tlib}", "-ltorch", "-ltorch_cpu", "-lc10",
+           "-Wno-interference-size", *inc, str(src), "-o", str(target), f"-L{tlib}", "-ltorch", "-ltorch_cpu", "-lc10",
            "-ltorch_python", "-ltorch_cuda", "-lc10_cuda", f"-L{LIB}", "-lhylink_b200",
            f"-Wl,-rpath,{tlib}", "-Wl,-rpath,$ORIGIN", f"-L{CUDA_HOME / 'lib64'}", "-lcudart"]
     _run(cmd)

@@ -170,6 +170,10 @@ hlResult_t hlCommGetAsyncError(hlComm_t comm, hlResult_t* e) {
   if (*e == hlSuccess && comm->pcie) *e = comm->pcie->lastResult();
   return hlSuccess;
 }
+hlResult_t hlCommDrain(hlComm_t comm) {
+  if (!comm) return hlInvalidArgument;
+  return comm->pcie ? comm->pcie->drain() : hlSuccess;
+}
 hlResult_t hlFinalize(void) { return hlSuccess; }
 
 // ------------------------------------------------------------ collectives

@@ -99,6 +99,9 @@ hlResult_t hlCommDevice(hlComm_t comm, int* device);
 /* Latched asynchronous error of the communicator (device waits that ran out,
  * executor failures). hlSuccess while healthy. */
 hlResult_t hlCommGetAsyncError(hlComm_t comm, hlResult_t* async_error);
+/* Host-blocking: returns once everything this communicator submitted to the
+ * CPU-driven (PCIe / host-memory) path has completed. */
+hlResult_t hlCommDrain(hlComm_t comm);
 hlResult_t hlFinalize(void);
 
 /* ---- collectives ------------------------------------------------------- */

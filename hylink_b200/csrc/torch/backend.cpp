@@ -1,0 +1,414 @@
+// torch.distributed backend ("hylink"): a c10d::Backend whose collectives run
+// on this library's communicator.
+//
+// * One communicator per device kind, created lazily on the first collective;
+//   the unique id travels through the c10d Store (rank 0 sets, others get).
+// * CUDA tensors: every collective is launched on the backend's own
+//   high-priority stream, which first waits for the caller's current stream;
+//   the returned Work carries a CUDA event — wait() makes the caller's stream
+//   wait for it (no host synchronisation), getFuture() gives DDP a CUDA-aware
+//   future, so gradient buckets overlap with the backward pass.
+// * CPU tensors: served by the host-memory device of the schedule-IR path
+//   (no GPU needed), synchronously.
+// * send/recv are not implemented here: pipeline point-to-point traffic stays
+//   on NCCL (see hylink_b200.parallel.p2p).
+//
+// Parity: the reference has no c10d backend; PyTorch reaches it only through
+// LD_PRELOAD of NCCL symbols (pcie-ccl-cuda/torch_dist_smoke/
+// collectives_smoke.py:38-44, ddp_mlp_smoke.py:58-60).
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/chrono.h>
+#include <torch/csrc/distributed/c10d/Backend.hpp>
+#include <torch/csrc/distributed/c10d/Store.hpp>
+#include <torch/csrc/distributed/c10d/Types.hpp>
+#include <torch/csrc/distributed/c10d/Work.hpp>
+#include <torch/python.h>
+
+#include <cstring>
+#include <mutex>
+
+#include "hylink/hylink.h"
+
+namespace {
+
+using c10d::OpType;
+
+void hlCheck(hlResult_t r, const char* what) {
+  if (r != hlSuccess) {
+    TORCH_CHECK(false, "hylink ", what, ": ", hlGetErrorString(r), " (", hlGetLastError(), ")");
+  }
+}
+
+hlDataType_t toHl(at::ScalarType t) {
+  switch (t) {
+    case at::kChar: return hlInt8;
+    case at::kByte: return hlUint8;
+    case at::kBool: return hlUint8;
+    case at::kInt: return hlInt32;
+    case at::kLong: return hlInt64;
+    case at::kHalf: return hlFloat16;
+    case at::kFloat: return hlFloat32;
+    case at::kDouble: return hlFloat64;
+    case at::kBFloat16: return hlBfloat16;
+    case at::kUInt32: return hlUint32;
+    case at::kUInt64: return hlUint64;
+    default: TORCH_CHECK(false, "hylink: unsupported dtype ", t);
+  }
+}
+
+struct OpInfo {
+  hlRedOp_t op;
+  float scale;
+};
+OpInfo toHlOp(const c10d::ReduceOp& op) {
+  switch (op.op_) {
+    case c10d::ReduceOp::SUM: return {hlSum, 1.0f};
+    case c10d::ReduceOp::AVG: return {hlAvg, 1.0f};
+    case c10d::ReduceOp::PRODUCT: return {hlProd, 1.0f};
+    case c10d::ReduceOp::MIN: return {hlMin, 1.0f};
+    case c10d::ReduceOp::MAX: return {hlMax, 1.0f};
+    default: TORCH_CHECK(false, "hylink: unsupported reduce op");
+  }
+}
+
+class HylinkWork : public c10d::Work {
+ public:
+  HylinkWork(int rank, OpType op, std::vector<at::Tensor> outputs, std::vector<at::Tensor> keep)
+      : c10d::Work(rank, op), outputs_(std::move(outputs)), keep_(std::move(keep)) {}
+
+  // CUDA flavour: call with the communication stream current.
+  void armCuda(c10::cuda::CUDAStream comm_stream) {
+    cuda_ = true;
+    device_ = comm_stream.device();
+    event_ = std::make_shared<at::cuda::CUDAEvent>(cudaEventDisableTiming);
+    event_->record(comm_stream);
+    future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()),
+                                                       std::vector<c10::Device>{device_});
+    c10::cuda::CUDAStreamGuard g(comm_stream);
+    future_->markCompleted(at::IValue(outputs_));
+  }
+  void armCpu() {
+    future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+    future_->markCompleted(at::IValue(outputs_));
+  }
+
+  bool isCompleted() override { return cuda_ ? event_->query() : true; }
+  bool isSuccess() const override { return true; }
+  void synchronize() override {
+    if (cuda_) event_->block(c10::cuda::getCurrentCUDAStream(device_.index()));
+  }
+  bool wait(std::chrono::milliseconds /*timeout*/) override {
+    synchronize();
+    keep_.clear();
+    return true;
+  }
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+  std::vector<at::Tensor> result() override { return outputs_; }
+
+ private:
+  std::vector<at::Tensor> outputs_;
+  std::vector<at::Tensor> keep_;  // inputs kept alive until the caller has waited
+  bool cuda_ = false;
+  c10::Device device_{c10::kCPU};
+  std::shared_ptr<at::cuda::CUDAEvent> event_;
+  c10::intrusive_ptr<c10::ivalue::Future> future_;
+};
+
+class HylinkBackend : public c10d::Backend {
+ public:
+  HylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size, std::chrono::milliseconds timeout)
+      : c10d::Backend(rank, size), store_(store), timeout_(timeout) {}
+  ~HylinkBackend() override { shutdown(); }
+
+  const std::string getBackendName() const override { return "hylink"; }
+
+  void shutdown() override {
+    std::lock_guard<std::mutex> lk(mu_);
+    if (cuda_comm_) {
+      hlCommDestroy(cuda_comm_);
+      cuda_comm_ = nullptr;
+    }
+    if (cpu_comm_) {
+      hlCommDestroy(cpu_comm_);
+      cpu_comm_ = nullptr;
+    }
+  }
+  void abort() override { shutdown(); }
+
+  // ---- helpers -----------------------------------------------------------
+  hlComm_t commFor(const at::Tensor& t) {
+    std::lock_guard<std::mutex> lk(mu_);
+    const bool cuda = t.is_cuda();
+    hlComm_t& slot = cuda ? cuda_comm_ : cpu_comm_;
+    if (slot) return slot;
+    hlUniqueId id;
+    const std::string key = std::string("hylink/uid/") + (cuda ? "cuda" : "cpu") + "/" + std::to_string(generation_);
+    if (getRank() == 0) {
+      hlCheck(hlGetUniqueId(&id), "hlGetUniqueId");
+      std::vector<uint8_t> v(sizeof(id));
+      memcpy(v.data(), &id, sizeof(id));
+      store_->set(key, v);
+    } else {
+      std::vector<uint8_t> v = store_->get(key);
+      TORCH_CHECK(v.size() == sizeof(id), "hylink: bad unique id in the store");
+      memcpy(&id, v.data(), sizeof(id));
+    }
+    int device = -2;
+    if (cuda) {
+      device = t.device().index();
+      cuda_device_ = device;
+      comm_stream_ = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, device));
+    }
+    hlCheck(hlCommInitRankDevice(&slot, getSize(), id, getRank(), device), "hlCommInitRankDevice");
+    return slot;
+  }
+
+  template <typename F>
+  c10::intrusive_ptr<c10d::Work> run(OpType type, const at::Tensor& probe, std::vector<at::Tensor> outputs,
+                                     std::vector<at::Tensor> keep, F&& body) {
+    hlComm_t comm = commFor(probe);
+    auto work = c10::make_intrusive<HylinkWork>(getRank(), type, std::move(outputs), std::move(keep));
+    if (probe.is_cuda()) {
+      c10::cuda::CUDAGuard dg(probe.device());
+      auto cur = c10::cuda::getCurrentCUDAStream(probe.device().index());
+      at::cuda::CUDAEvent ready(cudaEventDisableTiming);
+      ready.record(cur);
+      ready.block(*comm_stream_);
+      body(comm, (hlStream_t)comm_stream_->stream());
+      work->armCuda(*comm_stream_);
+      ++collectives_;
+    } else {
+      body(comm, nullptr);
+      hlCheck(hlCommDrain(comm), "hlCommDrain");
+      work->armCpu();
+    }
+    return work;
+  }
+
+  static void checkContig(const at::Tensor& t) { TORCH_CHECK(t.is_contiguous(), "hylink: tensors must be contiguous"); }
+
+  // ---- collectives ---------------------------------------------------------
+  c10::intrusive_ptr<c10d::Work> allreduce(std::vector<at::Tensor>& tensors, const c10d::AllreduceOptions& opts) override {
+    TORCH_CHECK(tensors.size() == 1, "hylink: one tensor per allreduce");
+    at::Tensor t = tensors[0];
+    checkContig(t);
+    const OpInfo oi = toHlOp(opts.reduceOp);
+    return run(OpType::ALLREDUCE, t, {t}, {t}, [&](hlComm_t c, hlStream_t s) {
+      hlCallOpts o;
+      memset(&o, 0, sizeof(o));
+      o.scale = fused_scale_ != 0.0f ? fused_scale_ : oi.scale;
+      hlCheck(hlAllReduceEx(t.data_ptr(), t.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), oi.op, &o, c, s), "allreduce");
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> allreduce_coalesced(std::vector<at::Tensor>& tensors,
+                                                     const c10d::AllreduceCoalescedOptions& opts) override {
+    TORCH_CHECK(!tensors.empty(), "hylink: empty tensor list");
+    const OpInfo oi = toHlOp(opts.reduceOp);
+    std::vector<at::Tensor> ts = tensors;
+    return run(OpType::ALLREDUCE_COALESCED, ts[0], ts, ts, [&](hlComm_t c, hlStream_t s) {
+      for (auto& t : ts) {
+        checkContig(t);
+        hlCheck(hlAllReduce(t.data_ptr(), t.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), oi.op, c, s), "allreduce_coalesced");
+      }
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> broadcast(std::vector<at::Tensor>& tensors, const c10d::BroadcastOptions& opts) override {
+    TORCH_CHECK(tensors.size() == 1, "hylink: one tensor per broadcast");
+    at::Tensor t = tensors[0];
+    checkContig(t);
+    const int root = (int)opts.rootRank;
+    return run(OpType::BROADCAST, t, {t}, {t}, [&](hlComm_t c, hlStream_t s) {
+      hlCheck(hlBroadcast(t.data_ptr(), t.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), root, c, s), "broadcast");
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& out, at::Tensor& in, const c10d::AllgatherOptions&) override {
+    checkContig(out);
+    checkContig(in);
+    TORCH_CHECK(out.numel() == in.numel() * getSize(), "hylink: all_gather_into_tensor size mismatch");
+    at::Tensor o = out, i = in;
+    return run(OpType::_ALLGATHER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
+      hlCheck(hlAllGather(i.data_ptr(), o.data_ptr(), (size_t)i.numel(), toHl(i.scalar_type()), c, s), "allgather");
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> allgather(std::vector<std::vector<at::Tensor>>& outs, std::vector<at::Tensor>& ins,
+                                           const c10d::AllgatherOptions&) override {
+    TORCH_CHECK(ins.size() == 1 && outs.size() == 1, "hylink: one input per allgather");
+    at::Tensor in = ins[0].contiguous();
+    std::vector<at::Tensor> dst = outs[0];
+    TORCH_CHECK((int)dst.size() == getSize(), "hylink: allgather output list must have world_size entries");
+    at::Tensor flat = at::empty({(int64_t)getSize() * in.numel()}, in.options());
+    return run(OpType::ALLGATHER, in, dst, {in, flat}, [&](hlComm_t c, hlStream_t s) {
+      hlCheck(hlAllGather(in.data_ptr(), flat.data_ptr(), (size_t)in.numel(), toHl(in.scalar_type()), c, s), "allgather");
+      c10::OptionalStreamGuard sg;
+      if (in.is_cuda()) sg.reset_stream(*comm_stream_);
+      for (int q = 0; q < getSize(); ++q) dst[q].copy_(flat.narrow(0, (int64_t)q * in.numel(), in.numel()).view_as(dst[q]), true);
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> allgather_into_tensor_coalesced(std::vector<at::Tensor>& outs, std::vector<at::Tensor>& ins,
+                                                                 const c10d::AllgatherOptions&) override {
+    TORCH_CHECK(outs.size() == ins.size() && !ins.empty(), "hylink: list size mismatch");
+    std::vector<at::Tensor> o = outs, i = ins, keep = ins;
+    keep.insert(keep.end(), o.begin(), o.end());
+    return run(OpType::ALLGATHER_COALESCED, i[0], o, keep, [&](hlComm_t c, hlStream_t s) {
+      for (size_t k = 0; k < i.size(); ++k) {
+        checkContig(i[k]);
+        checkContig(o[k]);
+        hlCheck(hlAllGather(i[k].data_ptr(), o[k].data_ptr(), (size_t)i[k].numel(), toHl(i[k].scalar_type()), c, s), "allgather_coalesced");
+      }
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> _reduce_scatter_base(at::Tensor& out, at::Tensor& in, const c10d::ReduceScatterOptions& opts) override {
+    checkContig(out);
+    checkContig(in);
+    TORCH_CHECK(in.numel() == out.numel() * getSize(), "hylink: reduce_scatter_tensor size mismatch");
+    const OpInfo oi = toHlOp(opts.reduceOp);
+    at::Tensor o = out, i = in;
+    return run(OpType::_REDUCE_SCATTER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
+      hlCheck(hlReduceScatter(i.data_ptr(), o.data_ptr(), (size_t)o.numel(), toHl(i.scalar_type()), oi.op, c, s), "reduce_scatter");
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> reduce_scatter(std::vector<at::Tensor>& outs, std::vector<std::vector<at::Tensor>>& ins,
+                                                const c10d::ReduceScatterOptions& opts) override {
+    TORCH_CHECK(outs.size() == 1 && ins.size() == 1 && (int)ins[0].size() == getSize(), "hylink: bad reduce_scatter lists");
+    at::Tensor out = outs[0];
+    checkContig(out);
+    const OpInfo oi = toHlOp(opts.reduceOp);
+    std::vector<at::Tensor> parts = ins[0];
+    at::Tensor probe = out;
+    return run(OpType::REDUCE_SCATTER, probe, {out}, parts, [&](hlComm_t c, hlStream_t s) {
+      c10::OptionalStreamGuard sg;
+      if (out.is_cuda()) sg.reset_stream(*comm_stream_);
+      std::vector<at::Tensor> flat_parts;
+      for (auto& p : parts) flat_parts.push_back(p.reshape({-1}));
+      at::Tensor flat = at::cat(flat_parts);
+      hlCheck(hlReduceScatter(flat.data_ptr(), out.data_ptr(), (size_t)out.numel(), toHl(out.scalar_type()), oi.op, c, s), "reduce_scatter");
+      if (out.is_cuda()) c10::cuda::CUDACachingAllocator::recordStream(flat.storage().data_ptr(), *comm_stream_);
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> reduce_scatter_tensor_coalesced(std::vector<at::Tensor>& outs, std::vector<at::Tensor>& ins,
+                                                                 const c10d::ReduceScatterOptions& opts) override {
+    TORCH_CHECK(outs.size() == ins.size() && !ins.empty(), "hylink: list size mismatch");
+    const OpInfo oi = toHlOp(opts.reduceOp);
+    std::vector<at::Tensor> o = outs, i = ins, keep = ins;
+    keep.insert(keep.end(), o.begin(), o.end());
+    return run(OpType::COALESCED, i[0], o, keep, [&](hlComm_t c, hlStream_t s) {
+      for (size_t k = 0; k < i.size(); ++k) {
+        checkContig(i[k]);
+        checkContig(o[k]);
+        hlCheck(hlReduceScatter(i[k].data_ptr(), o[k].data_ptr(), (size_t)o[k].numel(), toHl(i[k].scalar_type()), oi.op, c, s), "reduce_scatter_coalesced");
+      }
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& out, at::Tensor& in, std::vector<int64_t>& outSplit,
+                                               std::vector<int64_t>& inSplit, const c10d::AllToAllOptions&) override {
+    TORCH_CHECK(outSplit.empty() && inSplit.empty(), "hylink: only equal splits are supported by all_to_all_single");
+    checkContig(out);
+    checkContig(in);
+    TORCH_CHECK(out.numel() == in.numel() && in.numel() % getSize() == 0, "hylink: all_to_all_single size mismatch");
+    at::Tensor o = out, i = in;
+    return run(OpType::ALLTOALL_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
+      hlCheck(hlAllToAll(i.data_ptr(), o.data_ptr(), (size_t)i.numel() / getSize(), toHl(i.scalar_type()), c, s), "all_to_all");
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> reduce(std::vector<at::Tensor>& tensors, const c10d::ReduceOptions& opts) override {
+    // Reduce to one root = all-reduce whose result the other ranks discard
+    // into a scratch buffer (keeps their tensors untouched).
+    TORCH_CHECK(tensors.size() == 1, "hylink: one tensor per reduce");
+    at::Tensor t = tensors[0];
+    checkContig(t);
+    const OpInfo oi = toHlOp(opts.reduceOp);
+    const bool root = (int)opts.rootRank == getRank();
+    at::Tensor dst = root ? t : at::empty_like(t);
+    return run(OpType::REDUCE, t, {t}, {t, dst}, [&](hlComm_t c, hlStream_t s) {
+      hlCheck(hlAllReduce(t.data_ptr(), dst.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), oi.op, c, s), "reduce");
+    });
+  }
+
+  c10::intrusive_ptr<c10d::Work> barrier(const c10d::BarrierOptions& opts) override {
+    at::Tensor probe;
+    if (cuda_comm_ || !cpu_comm_) {
+      int dev = cuda_device_ >= 0 ? cuda_device_ : (opts.device_ids.empty() ? -1 : (int)opts.device_ids[0]);
+      if (dev < 0 && at::hasCUDA()) dev = c10::cuda::current_device();
+      if (dev >= 0) probe = at::empty({1}, at::TensorOptions().device(at::kCUDA, dev).dtype(at::kFloat));
+    }
+    if (!probe.defined()) probe = at::empty({1}, at::TensorOptions().dtype(at::kFloat));
+    return run(OpType::BARRIER, probe, {}, {probe}, [&](hlComm_t c, hlStream_t s) { hlCheck(hlBarrier(c, s), "barrier"); });
+  }
+
+  c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>&, int, int) override {
+    TORCH_CHECK(false, "hylink: point-to-point traffic stays on NCCL; use hylink_b200.parallel.p2p");
+  }
+  c10::intrusive_ptr<c10d::Work> recv(std::vector<at::Tensor>&, int, int) override {
+    TORCH_CHECK(false, "hylink: point-to-point traffic stays on NCCL; use hylink_b200.parallel.p2p");
+  }
+
+  // ---- extras exposed to Python -------------------------------------------
+  void setFusedScale(float s) { fused_scale_ = s; }
+  py::dict stats() {
+    py::dict d;
+    hlComm_t c = cuda_comm_ ? cuda_comm_ : cpu_comm_;
+    d["collectives"] = collectives_;
+    if (c) {
+      hlCommStats st;
+      memset(&st, 0, sizeof(st));
+      hlCommGetStats(c, &st);
+      d["calls"] = st.calls;
+      d["bytes"] = st.bytes;
+      d["nvl_bytes"] = st.nvl_bytes;
+      d["pcie_bytes"] = st.pcie_bytes;
+      d["kernel_launches"] = st.kernel_launches;
+      d["copy_engine_ops"] = st.copy_engine_ops;
+      d["last_alpha"] = st.last_alpha;
+      d["last_fast_ms"] = st.last_fast_ms;
+      d["last_pcie_ms"] = st.last_pcie_ms;
+      d["nvls"] = st.nvls;
+      d["symm_mode"] = st.symm_mode;
+    }
+    return d;
+  }
+
+ private:
+  c10::intrusive_ptr<c10d::Store> store_;
+  std::chrono::milliseconds timeout_;
+  std::mutex mu_;
+  hlComm_t cuda_comm_ = nullptr;
+  hlComm_t cpu_comm_ = nullptr;
+  int cuda_device_ = -1;
+  int generation_ = 0;
+  std::unique_ptr<c10::cuda::CUDAStream> comm_stream_;
+  uint64_t collectives_ = 0;
+  float fused_scale_ = 0.0f;
+};
+
+c10::intrusive_ptr<c10d::Backend> createHylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
+                                                      const std::chrono::duration<float>& timeout) {
+  return c10::make_intrusive<HylinkBackend>(store, rank, size, std::chrono::duration_cast<std::chrono::milliseconds>(timeout));
+}
+
+HylinkBackend* asHylink(const c10::intrusive_ptr<c10d::Backend>& b) {
+  auto* p = dynamic_cast<HylinkBackend*>(b.get());
+  TORCH_CHECK(p, "not a hylink backend");
+  return p;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("create_backend", &createHylinkBackend, py::arg("store"), py::arg("rank"), py::arg("size"), py::arg("timeout"));
+  m.def("backend_stats", [](const c10::intrusive_ptr<c10d::Backend>& b) { return asHylink(b)->stats(); });
+  // Multiplies every all-reduce result by `scale` inside the kernel (0 = off):
+  // lets a DDP wrapper fold its gradient pre-division into the collective.
+  m.def("set_fused_scale", [](const c10::intrusive_ptr<c10d::Backend>& b, float s) { asHylink(b)->setFusedScale(s); });
+}

@@ -1,0 +1,70 @@
+"""Registration of the ``hylink`` backend with ``torch.distributed``.
+
+After :func:`register_backend`, ``dist.init_process_group(backend="hylink")``
+(or ``"cuda:hylink,cpu:gloo"``) routes all-reduce, broadcast, all-gather,
+reduce-scatter, all-to-all and barrier through this library. The C++ side is
+``csrc/torch/backend.cpp``.
+"""
+from __future__ import annotations
+
+import importlib.machinery
+import importlib.util
+from pathlib import Path
+
+_ext = None
+
+
+def _load_ext():
+    global _ext
+    if _ext is not None:
+        return _ext
+    import torch  # noqa: F401  (registers the c10d base classes with pybind)
+    import torch.distributed  # noqa: F401
+
+    from .. import _native  # noqa: F401  (loads libhylink_b200.so first)
+
+    path = Path(__file__).resolve().parent.parent / "lib" / "_hylink_c10d.so"
+    if not path.exists():
+        from .. import _build
+
+        _build.build_torch_ext()
+    loader = importlib.machinery.ExtensionFileLoader("_hylink_c10d", str(path))
+    spec = importlib.util.spec_from_loader("_hylink_c10d", loader)
+    mod = importlib.util.module_from_spec(spec)
+    loader.exec_module(mod)
+    _ext = mod
+    return mod
+
+
+_registered = False
+
+
+def register_backend() -> None:
+    """Make ``backend="hylink"`` known to ``torch.distributed`` (idempotent)."""
+    global _registered
+    if _registered:
+        return
+    import torch.distributed as dist
+
+    ext = _load_ext()
+    dist.Backend.register_backend("hylink", ext.create_backend, devices=["cuda", "cpu"])
+    _registered = True
+
+
+def _backend_of(group=None):
+    import torch
+    import torch.distributed as dist
+
+    pg = group if group is not None else dist.group.WORLD
+    dev = torch.device("cuda") if torch.cuda.is_available() else torch.device("cpu")
+    return pg._get_backend(dev)
+
+
+def backend_stats(group=None) -> dict:
+    """Counters of the group's communicator: calls, bytes per path, kernel launches, split ratio."""
+    return dict(_load_ext().backend_stats(_backend_of(group)))
+
+
+def set_fused_scale(scale: float, group=None) -> None:
+    """Multiply every all-reduce result by ``scale`` inside the kernel (0 switches it off)."""
+    _load_ext().set_fused_scale(_backend_of(group), float(scale))

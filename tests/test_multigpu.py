@@ -1,0 +1,31 @@
+"""Real multi-GPU runs (one process per GPU over NVLink): skipped below 2 GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(nproc, args, timeout=600, env=None):
+    e = dict(os.environ)
+    e.update(env or {})
+    e["PYTHONPATH"] = ROOT + os.pathsep + e.get("PYTHONPATH", "")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", "29631"] + args
+    p = subprocess.run(cmd, cwd=ROOT, env=e, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout)
+    assert p.returncode == 0, p.stdout[-4000:]
+    return p.stdout
+
+
+def test_sweep_correct_against_nccl():
+    out = _torchrun(2, ["-m", "hylink_b200.utils.sweep", "--min", "1K", "--max", "16M", "--factor", "8", "--check",
+                        "--colls", "allreduce,reducescatter,allgather,alltoall", "--dtypes", "bf16,fp32", "--iters", "3"])
+    assert '"failures": 0' in out, out[-3000:]
+
+
+def test_c10d_backend_and_ddp():
+    out = _torchrun(2, ["-m", "hylink_b200.utils.selftest"])
+    assert "SELFTEST PASSED" in out, out[-3000:]
