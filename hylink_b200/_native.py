@@ -99,6 +99,7 @@ _sig("hlEmuSetActiveRanks", _i, _vp, _i)
 _sig("hlEmuStatus", _i, _vp, _i, _u64p, _u64p, _u64p)
 _sig("hlEmuReset", _i, _vp)
 _sig("hlEmuLaunches", _i, _vp, _u64p)
+_sig("hlCtrlSelfTest", _i, UniqueId, _i, _i, _i)
 _sig("hlReduceLanding", _i, _vp, C.POINTER(_vp), _i, _i, _sz, _i, _i, _f, _i, _vp)
 
 

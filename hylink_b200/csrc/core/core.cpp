@@ -257,3 +257,6 @@ const char* hlGetLastError(void) { return hl::lastError(); }
 int hlVersion(void) { return 100; }
 
 }  // extern "C"
+
+// Re-reads every environment variable (tests flip settings between communicators).
+extern "C" void hlConfigReload(void) { hl::Config::reload(); }

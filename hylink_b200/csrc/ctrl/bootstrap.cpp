@@ -401,3 +401,47 @@ extern "C" hlResult_t hlGetUniqueId(hlUniqueId* id) {
   }
   return hlSuccess;
 }
+
+// Self-check of the control plane, callable from tests without a GPU: barrier,
+// mailbox all-gather and descriptor passing between `nranks` processes/threads.
+extern "C" hlResult_t hlCtrlSelfTest(hlUniqueId id, int nranks, int rank, int rounds) {
+  using namespace hl;
+  Bootstrap* raw = nullptr;
+  HL_CHECK(Bootstrap::create(id, nranks, rank, 8192, 20000, &raw));
+  std::unique_ptr<Bootstrap> bs(raw);
+  if (bs->extraBytes() < 8192) return fail(hlInternalError, "extra area too small");
+  for (int it = 0; it < rounds; ++it) {
+    int64_t mine = 1000 * it + rank, all[kMaxRanks];
+    HL_CHECK(bs->allGather(&mine, sizeof(mine), all));
+    for (int q = 0; q < nranks; ++q)
+      if (all[q] != 1000 * it + q) return fail(hlInternalError, "allGather mismatch at rank %d", q);
+    int fd = memfd_create("hylink_selftest", MFD_CLOEXEC);
+    if (fd < 0) return fail(hlSystemError, "memfd_create: %s", strerror(errno));
+    int64_t stamp = 7777 + 31 * it + rank;
+    if (write(fd, &stamp, sizeof(stamp)) != (ssize_t)sizeof(stamp)) return fail(hlSystemError, "write memfd");
+    int fds[kMaxRanks];
+    HL_CHECK(bs->exchangeFds(fd, fds));
+    for (int q = 0; q < nranks; ++q) {
+      int64_t got = 0;
+      if (pread(fds[q], &got, sizeof(got), 0) != (ssize_t)sizeof(got) || got != 7777 + 31 * it + q)
+        return fail(hlInternalError, "fd from rank %d carries the wrong object", q);
+      if (q != rank) close(fds[q]);
+    }
+    int bfd = -1;
+    HL_CHECK(bs->broadcastFd(nranks - 1, fd, &bfd));
+    int64_t got = 0;
+    if (pread(bfd, &got, sizeof(got), 0) != (ssize_t)sizeof(got) || got != 7777 + 31 * it + (nranks - 1))
+      return fail(hlInternalError, "broadcast fd carries the wrong object");
+    if (bfd != fd) close(bfd);
+    HL_CHECK(bs->barrier(kBarUser));
+    close(fd);
+  }
+  // the shared extra area is really shared
+  auto* words = reinterpret_cast<std::atomic<int>*>(bs->extra());
+  words[rank].store(rank + 1);
+  HL_CHECK(bs->barrier(kBarUser));
+  for (int q = 0; q < nranks; ++q)
+    if (words[q].load() != q + 1) return fail(hlInternalError, "extra area not shared");
+  HL_CHECK(bs->barrier(kBarUser));
+  return hlSuccess;
+}

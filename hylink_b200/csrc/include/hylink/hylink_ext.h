@@ -33,6 +33,9 @@ hlResult_t hlEmuLaunches(hlEmu_t e, uint64_t* n);
 hlResult_t hlReduceLanding(void* dst, const void* const* srcs, int nsrc, int accumulate, size_t count,
                            hlDataType_t t, hlRedOp_t op, float scale, int blocks, hlStream_t stream);
 
+/* ---- control-plane self check (no GPU): barrier, mailbox, fd passing ------ */
+hlResult_t hlCtrlSelfTest(hlUniqueId id, int nranks, int rank, int rounds);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,78 @@
+"""Control plane without a GPU: shared control block, barrier, mailbox
+all-gather and SCM_RIGHTS descriptor passing between real processes, and the
+thread flavour (zeroed id)."""
+import ctypes as C
+import multiprocessing as mp
+import threading
+
+import pytest
+
+
+def _worker(uid, n, r, q):
+    from hylink_b200._native import UniqueId, lib
+
+    u = UniqueId()
+    C.memmove(C.byref(u), uid, 128)
+    rc = lib.hlCtrlSelfTest(u, n, r, 3)
+    q.put((r, rc, lib.hlGetLastError().decode()))
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_multi_process_rendezvous(n):
+    from hylink_b200.parallel.comm import unique_id
+
+    uid = unique_id().ljust(128, b"\0")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_worker, args=(uid, n, r, q)) for r in range(n)]
+    for p in ps:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(n)]
+    for p in ps:
+        p.join(30)
+    assert all(rc == 0 for _, rc, _ in res), res
+
+
+def test_single_process_threads():
+    from hylink_b200._native import UniqueId, lib
+
+    n, out = 4, {}
+
+    def run(r):
+        out[r] = lib.hlCtrlSelfTest(UniqueId(), n, r, 2)
+
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(n)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(60)
+    assert out == {r: 0 for r in range(n)}, (out, lib.hlGetLastError())
+
+
+def test_missing_rank_times_out_not_hangs():
+    """A rank that never joins: the others give up with a timeout result."""
+    import os
+    import time
+
+    from hylink_b200._native import UniqueId, lib
+    from hylink_b200.parallel.comm import unique_id
+
+    os.environ["HYLINK_BARRIER_TIMEOUT_MS"] = "300"
+    try:
+        u = UniqueId()
+        C.memmove(C.byref(u), unique_id().ljust(128, b"\0"), 128)
+        t0 = time.time()
+        # hlCtrlSelfTest uses its own 20 s limit; go through the communicator instead
+        h = C.c_void_p()
+        lib.hlCommInitRankDevice.restype = C.c_int
+        rc = None
+        # a 2-rank communicator where rank 1 never shows up
+        from hylink_b200 import _native
+
+        _native.lib.hlConfigReload()
+        rc = lib.hlCommInitRankDevice(C.byref(h), 2, u, 0, -2)
+        assert rc == 6, (rc, lib.hlGetLastError())  # hlTimeout
+        assert time.time() - t0 < 20
+    finally:
+        del os.environ["HYLINK_BARRIER_TIMEOUT_MS"]
+        lib.hlConfigReload()
