@@ -4,7 +4,7 @@ Run one process per GPU::
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         -m hylink_b200.utils.sweep --colls allreduce,reducescatter,allgather --dtypes bf16,fp32 \
-        --min 1K --max 1G --check --out sweep.jsonl
+        --bytes-from 1K --bytes-to 1G --check --out sweep.jsonl
 
 Every number is timed on the device with CUDA events and is the MAX over ranks.
 busbw = algbw * 2(n-1)/n for all-reduce and * (n-1)/n for reduce-scatter /
@@ -56,15 +56,15 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--colls", default="allreduce,reducescatter,allgather")
     ap.add_argument("--dtypes", default="bf16,fp32")
-    ap.add_argument("--min", default="1K")
-    ap.add_argument("--max", default="256M")
+    ap.add_argument("--bytes-from", dest="lo", default="1K")
+    ap.add_argument("--bytes-to", dest="hi", default="256M")
     ap.add_argument("--factor", type=int, default=2)
     ap.add_argument("--iters", type=int, default=0, help="0 = by size")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--algo", default="auto", help="auto|oneshot|twoshot|nvls (all-reduce)")
     ap.add_argument("--path", default="nvlink", help="nvlink|pcie|split|auto")
-    ap.add_argument("--max-blocks", type=int, default=0)
+    ap.add_argument("--blocks", dest="max_blocks", type=int, default=0)
     ap.add_argument("--deterministic", action="store_true")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--out", default="")
@@ -83,7 +83,7 @@ def main(argv=None) -> int:
     if rank == 0:
         print(json.dumps({"event": "init", "world": world, "nvls": st["nvls"], "symm_mode": st["symm_mode"]}), flush=True)
 
-    lo, hi = parse_size(a.min), parse_size(a.max)
+    lo, hi = parse_size(a.lo), parse_size(a.hi)
     sizes = []
     s = lo
     while s <= hi:

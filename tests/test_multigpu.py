@@ -21,7 +21,7 @@ def _torchrun(nproc, args, timeout=600, env=None):
 
 
 def test_sweep_correct_against_nccl():
-    out = _torchrun(2, ["-m", "hylink_b200.utils.sweep", "--min", "1K", "--max", "16M", "--factor", "8", "--check",
+    out = _torchrun(2, ["-m", "hylink_b200.utils.sweep", "--bytes-from", "1K", "--bytes-to", "16M", "--factor", "8", "--check",
                         "--colls", "allreduce,reducescatter,allgather,alltoall", "--dtypes", "bf16,fp32", "--iters", "3"])
     assert '"failures": 0' in out, out[-3000:]
 
