@@ -59,8 +59,6 @@ def _compile(src: Path, obj: Path, hdr_time: float, extra: list[str]) -> bool:
     else:
         cmd = ["g++", "-O2", "-g1", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function",
                "-pthread", *inc, *extra, "-c", str(src), "-o", str(obj)]
-        if src.parent.name == "host":
-            cmd[1:1] = ["-mavx2", "-mfma", "-mf16c"]  # AVX-512 variants carry their own target attributes
     _run(cmd)
     return True
 

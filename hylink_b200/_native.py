@@ -99,6 +99,27 @@ _sig("hlEmuSetActiveRanks", _i, _vp, _i)
 _sig("hlEmuStatus", _i, _vp, _i, _u64p, _u64p, _u64p)
 _sig("hlEmuReset", _i, _vp)
 _sig("hlEmuLaunches", _i, _vp, _u64p)
+class IrInfo(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("nranks", "instructions", "dependency_edges", "input_chunks", "output_chunks",
+                                        "internal_chunks", "host_chunks", "numa_nodes", "uses_remote_device",
+                                        "uses_host_reduce")]
+
+
+_sig("hlIrGenerate", _i, C.c_char_p, C.c_char_p, C.c_char_p, _i, C.c_char_p, C.POINTER(_sz))
+_sig("hlIrInspect", _i, C.c_char_p, C.c_char_p, _i, _i, _i, C.POINTER(IrInfo))
+_sig("hlIrRoundTrip", _i, C.c_char_p, C.c_char_p, C.POINTER(_sz))
+_sig("hlSubmitIr", _i, _vp, C.c_char_p, _vp, _vp, _sz, _sz, _i, _i, _i, _i, _vp)
+_sig("hlCommNumaPattern", _i, _vp, C.c_char_p, C.POINTER(_sz))
+_sig("hlCommDrain", _i, _vp)
+_sig("hlHostReduce", _i, _vp, _vp, _vp, _sz, _i, _i, _i)
+_sig("hlHostCopy", None, _vp, _vp, _sz, _i)
+_sig("hlHostSimdLevel", _i)
+_sig("hlTraceOpen", None, C.c_char_p, _i)
+_sig("hlTraceFlush", None)
+_sig("hlConfigReload", None)
+_sig("pcclReduceScatterStridedTyped", _i, _vp, _vp, _sz, _sz, _i, _i, _vp, _vp)
+_sig("pcclAllGatherStridedTyped", _i, _vp, _vp, _sz, _sz, _i, _vp, _vp)
+_sig("pcclAllToAllStridedTyped", _i, _vp, _vp, _sz, _sz, _i, _vp, _vp)
 _sig("hlCtrlSelfTest", _i, UniqueId, _i, _i, _i)
 _sig("hlReduceLanding", _i, _vp, C.POINTER(_vp), _i, _i, _sz, _i, _i, _f, _i, _vp)
 

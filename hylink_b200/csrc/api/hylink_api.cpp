@@ -78,15 +78,8 @@ static hlPath_t choosePath(hlComm* c, hlPath_t asked, size_t bytes) {
   return c->orch->shouldSplit(bytes) ? hlPathSplit : hlPathNvlink;
 }
 
-}  // namespace hl
-
-extern "C" {
-
-hlResult_t hlCommInitRank(hlComm_t* comm, int nranks, hlUniqueId id, int rank) {
-  return hlCommInitRankDevice(comm, nranks, id, rank, -1);
-}
-
-hlResult_t hlCommInitRankDevice(hlComm_t* out, int nranks, hlUniqueId id, int rank, int device) {
+// flags: 1 = create the PCIe path, 2 = create the orchestrator, 4 = no NVLink path.
+hlResult_t commInit(hlComm_t* out, int nranks, hlUniqueId id, int rank, int device, unsigned flags) {
   if (!out) return fail(hlInvalidArgument, "null comm pointer");
   const Config& cfg = Config::get();
   std::unique_ptr<hlComm> c(new hlComm());
@@ -109,24 +102,42 @@ hlResult_t hlCommInitRankDevice(hlComm_t* out, int nranks, hlUniqueId id, int ra
       HL_CUDA(cudaDeviceSynchronize());
     }
     HL_CHECK(nvl::prepareReduceLanding());
-    if (nranks > 1) {
-      HL_CHECK(NvlPath::createReal(c->bs, device, &c->nvl));
-    } else {
-      HL_CHECK(NvlPath::createEmu(1, device, std::min<size_t>(cfg.symm_stage_bytes, (size_t)64 << 20), cfg.nvl_timeout_ms, &c->nvl));
+    if (!(flags & 4u)) {
+      if (nranks > 1) {
+        HL_CHECK(NvlPath::createReal(c->bs, device, &c->nvl));
+      } else {
+        HL_CHECK(NvlPath::createEmu(1, device, std::min<size_t>(cfg.symm_stage_bytes, (size_t)64 << 20), cfg.nvl_timeout_ms, &c->nvl));
+      }
+      c->stats.nvls = c->nvl->hasNvls() ? 1 : 0;
+      c->stats.symm_mode = c->nvl->symmMode();
     }
-    c->stats.nvls = c->nvl->hasNvls() ? 1 : 0;
-    c->stats.symm_mode = c->nvl->symmMode();
   }
-  const bool want_pcie = c->host_device || cfg.orch_enable || envBool({"HYLINK_PCIE_ENABLE"}, false);
+  const bool want_pcie = c->host_device || (flags & 1u);
   if (want_pcie && nranks > 1) {
     char* area = (char*)c->bs->extra();
     HL_CHECK(PciePath::create(c->bs, c->device, area, &c->pcie));
-    if (!c->host_device && cfg.orch_enable)
+    if (!c->host_device && (flags & 2u) && c->nvl)
       HL_CHECK(Orchestrator::create(c.get(), area + PciePath::ctrlBytes(nranks), &c->orch));
   }
   HL_CHECK(c->bs->barrier(kBarInit));
   *out = c.release();
   return hlSuccess;
+}
+
+}  // namespace hl
+
+extern "C" {
+
+hlResult_t hlCommInitRank(hlComm_t* comm, int nranks, hlUniqueId id, int rank) {
+  return hlCommInitRankDevice(comm, nranks, id, rank, -1);
+}
+
+hlResult_t hlCommInitRankDevice(hlComm_t* out, int nranks, hlUniqueId id, int rank, int device) {
+  const Config& cfg = Config::get();
+  unsigned flags = 0;
+  if (cfg.orch_enable) flags |= 1u | 2u;
+  if (envBool({"HYLINK_PCIE_ENABLE"}, false)) flags |= 1u;
+  return hl::commInit(out, nranks, id, rank, device, flags);
 }
 
 hlResult_t hlCommDestroy(hlComm_t comm) {

@@ -152,8 +152,8 @@ static Config* g_cfg = nullptr;
 
 static Config* loadConfig() {
   Config* c = new Config();
-  c->host_buffer_bytes = (size_t)envInt({"HYLINK_HOST_BUFFER_SIZE", "PCCL_HOST_BUFFER_SIZE"}, 2LL << 30);
-  c->internal_buffer_bytes = (size_t)envInt({"HYLINK_INTERNAL_BUFFER_BYTES", "PCCL_INTERNAL_BUFFER_BYTES"}, 1LL << 30);
+  c->host_buffer_bytes = (size_t)envInt({"HYLINK_HOST_BUFFER_SIZE", "PCCL_HOST_BUFFER_SIZE"}, 512LL << 20);
+  c->internal_buffer_bytes = (size_t)envInt({"HYLINK_INTERNAL_BUFFER_BYTES", "PCCL_INTERNAL_BUFFER_BYTES"}, 256LL << 20);
   c->subchunk_slice_bytes = (size_t)envInt({"HYLINK_SUBCHUNK_SLICE_SIZE", "PCCL_SUBCHUNK_SLICE_SIZE"}, 0);
   if (c->subchunk_slice_bytes && c->subchunk_slice_bytes < 4096) c->subchunk_slice_bytes = 0;
   c->host_ring_slots = (int)envInt({"HYLINK_HOST_RING_SLOTS", "PCCL_HOST_RING_SLOTS"}, 3);
@@ -180,7 +180,8 @@ static Config* loadConfig() {
   c->nvl_timeout_ms = (int)envInt({"HYLINK_NVL_TIMEOUT_MS"}, 20000);
   c->nvls = (int)envInt({"HYLINK_NVLS"}, -1);
   c->symm_mode = envStr({"HYLINK_SYMM_MODE"}, "auto");
-  c->oneshot_max_bytes = (size_t)envInt({"HYLINK_ONESHOT_MAX_BYTES"}, 256LL << 10);
+  c->oneshot_max_bytes = (size_t)envInt({"HYLINK_ONESHOT_MAX_BYTES"}, 128LL << 10);
+  c->nvls_min_ranks = (int)envInt({"HYLINK_NVLS_MIN_RANKS"}, 4);
   c->nvl_max_blocks = (int)envInt({"HYLINK_NVL_MAX_BLOCKS"}, 0);
 
   c->orch_enable = envBool({"HYLINK_ORCH_ENABLE", "AMPCCL_ENABLE"}, false);

@@ -33,6 +33,35 @@ hlResult_t hlEmuLaunches(hlEmu_t e, uint64_t* n);
 hlResult_t hlReduceLanding(void* dst, const void* const* srcs, int nsrc, int accumulate, size_t count,
                            hlDataType_t t, hlRedOp_t op, float scale, int blocks, hlStream_t stream);
 
+/* ---- schedule IR tools ---------------------------------------------------- */
+typedef struct {
+  int nranks, instructions, dependency_edges;
+  int input_chunks, output_chunks, internal_chunks, host_chunks, numa_nodes;
+  int uses_remote_device, uses_host_reduce;
+} hlIrInfo;
+/* Emits reference-format schedule XML for any gpu->NUMA pattern ("00001111").
+ * Returns the needed length in *len; call with buf == NULL to size. */
+hlResult_t hlIrGenerate(const char* collective, const char* numa_pattern, const char* variant, int root, char* buf,
+                        size_t* len);
+/* Parses and compiles a schedule; in_place: 0 none, 1 same buffer, 2 gather slot, 3 scatter slot. */
+hlResult_t hlIrInspect(const char* xml, const char* numa_pattern, int send_segs, int recv_segs, int in_place,
+                       hlIrInfo* info);
+hlResult_t hlIrRoundTrip(const char* xml, char* buf, size_t* len);
+/* Runs a caller-supplied schedule on the PCIe path of `comm`. */
+hlResult_t hlSubmitIr(hlComm_t comm, const char* xml, const void* send, void* recv, size_t seg_count, size_t stride,
+                      int send_segs, int recv_segs, hlDataType_t t, hlRedOp_t op, hlStream_t stream);
+hlResult_t hlCommNumaPattern(hlComm_t comm, char* buf, size_t* len);
+
+/* ---- host SIMD kernels ------------------------------------------------------ */
+int hlHostReduce(void* dst, const void* a, const void* b, size_t count, int dtype, int op, int level_cap);
+void hlHostCopy(void* dst, const void* src, size_t bytes, int non_temporal);
+int hlHostSimdLevel(void);
+
+/* ---- tracing and configuration --------------------------------------------- */
+void hlTraceOpen(const char* path, int rank);
+void hlTraceFlush(void);
+void hlConfigReload(void);
+
 /* ---- control-plane self check (no GPU): barrier, mailbox, fd passing ------ */
 hlResult_t hlCtrlSelfTest(hlUniqueId id, int nranks, int rank, int rounds);
 

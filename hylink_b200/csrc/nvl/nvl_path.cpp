@@ -138,22 +138,32 @@ hlResult_t NvlPath::orderAfterPrevious(cudaStream_t s) {
   return hlSuccess;
 }
 
+bool NvlPath::nvlsPays() const {
+  // Through the switch every GPU sends its whole buffer once (S bytes out)
+  // whatever the rank count, while peer pulls move (n-1)/n * S in each
+  // direction: NVLS halves the inbound side only, which starts to pay at four
+  // ranks and loses at two.
+  return has_mc_ && nranks_ >= Config::get().nvls_min_ranks;
+}
+
 int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const {
   const bool nvls_ok = has_mc_ && (wire_dt == hlFloat32 || wire_dt == hlFloat16 || wire_dt == hlBfloat16) &&
                        (op == hlSum || op == hlAvg) && !deterministic;
   if (requested == hlAlgoNvls && !nvls_ok) requested = hlAlgoAuto;
   if (requested != hlAlgoAuto) return requested;
   if (wire_bytes <= Config::get().oneshot_max_bytes) return hlAlgoOneShot;
-  return nvls_ok ? hlAlgoNvls : hlAlgoTwoShotP2p;
+  return (nvls_ok && nvlsPays()) ? hlAlgoNvls : hlAlgoTwoShotP2p;
 }
 
 int NvlPath::blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const {
-  (void)kind;
   int cap = max_blocks > 0 ? max_blocks : (Config::get().nvl_max_blocks > 0 ? Config::get().nvl_max_blocks : 148);
   if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));
   cap = std::min(cap, HL_MAX_BLOCKS);
-  // one CTA per 64 KiB moved, at least one
-  size_t want = (wire_bytes_per_rank + (64u << 10) - 1) / (64u << 10);
+  // Latency-bound sizes want every thread to own one or two packets so that
+  // all remote accesses of a phase are in flight at once: one CTA (512
+  // threads x 16 B) per 8 KiB for the one-shot kernel, per 16 KiB otherwise.
+  const size_t per_cta = kind == kNvlAllReduceOneShot ? (8u << 10) : (16u << 10);
+  size_t want = (wire_bytes_per_rank + per_cta - 1) / per_cta;
   if (want < 1) want = 1;
   return (int)std::min<size_t>(want, (size_t)cap);
 }
@@ -225,7 +235,7 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
 hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   const bool nvls = has_mc_ && !c.deterministic && (c.op == hlSum || c.op == hlAvg) && c.algo != hlAlgoTwoShotP2p &&
-                    c.algo != hlAlgoOneShot &&
+                    c.algo != hlAlgoOneShot && (c.algo == hlAlgoNvls || nvlsPays()) &&
                     (c.wire_dt == hlFloat32 || c.wire_dt == hlFloat16 || c.wire_dt == hlBfloat16);
   return launchSliced(nvls ? kNvlReduceScatterNvls : kNvlReduceScatter, b, c, true, s);
 }

@@ -66,6 +66,7 @@ class NvlPath {
   // no launch in flight); flags and sequence restart from a common value.
   hlResult_t resetAfterError();
   int pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const;
+  bool nvlsPays() const;
   int blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const;
 
  private:

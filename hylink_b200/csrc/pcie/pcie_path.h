@@ -3,6 +3,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <vector>
 
 #include "core/core.h"
 #include "ctrl/bootstrap.h"
@@ -38,6 +39,8 @@ class PciePath {
   hlResult_t lastResult() const;
   uint64_t kernelLaunches() const;
   uint64_t copyOps() const;
+  // Logical NUMA node of every rank.
+  const std::vector<int>& rankNuma() const;
   PcieImpl* impl() { return impl_; }
 
  private:

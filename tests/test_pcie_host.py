@@ -1,0 +1,210 @@
+"""The CPU-driven schedule executor on the host-memory device: real processes,
+shared pinned-pool stand-ins, per-node progress counters in shared memory, the
+NUMA worker pool and the host SIMD reduce — everything except the GPU."""
+import ctypes as C
+
+import pytest
+import torch
+
+from mp_util import run_ranks
+
+SMALL_POOLS = {"HYLINK_HOST_BUFFER_SIZE": "64M", "HYLINK_INTERNAL_BUFFER_BYTES": "32M", "HYLINK_EXECUTOR_TIMEOUT_MS": "30000"}
+
+
+def _comm(rank, n, uid):
+    from hylink_b200.parallel.comm import Communicator
+
+    return Communicator(rank, n, uid=uid, device=-2)
+
+
+def _data(r, count, dtype, seed=0):
+    g = torch.Generator().manual_seed(1000 * seed + r)
+    return (torch.rand(count, generator=g, dtype=torch.float64) * 2 - 1).to(dtype)
+
+
+def _allreduce_worker(rank, n, uid, count, dtype_name, inplace):
+    dtype = getattr(torch, dtype_name)
+    c = _comm(rank, n, uid)
+    x = _data(rank, count, dtype)
+    out = x.clone() if inplace else torch.zeros(count, dtype=dtype)
+    c.all_reduce(out if inplace else x, out)
+    c.drain()
+    ref = sum(_data(r, count, dtype).double() for r in range(n))
+    tol = 1e-6 if dtype == torch.float32 else 3e-2
+    assert torch.allclose(out.double(), ref, rtol=tol, atol=tol * n), (out[:4], ref[:4])
+    st = c.stats()
+    c.close()
+    return st["pcie_bytes"]
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_allreduce_4mib_fp32_against_fp64_oracle(n):
+    """The CPU-only plumbing configuration: 4 MiB fp32 per rank, ring-free mesh schedule from the generator."""
+    res = run_ranks(_allreduce_worker, n, 1 << 20, "float32", False, env=SMALL_POOLS)
+    assert all(b == 4 << 20 for b in res)
+
+
+def test_allreduce_bf16_in_place_odd_count():
+    run_ranks(_allreduce_worker, 2, 100003, "bfloat16", True, env=SMALL_POOLS)
+
+
+def test_allreduce_two_numa_nodes_host_reduce_variant():
+    env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP="0011", HYLINK_IR_VARIANT="host_reduce")
+    run_ranks(_allreduce_worker, 4, 50000, "float32", False, env=env)
+
+
+def test_allreduce_rounds_when_message_exceeds_pools():
+    env = dict(SMALL_POOLS, HYLINK_HOST_BUFFER_SIZE="4M", HYLINK_INTERNAL_BUFFER_BYTES="2M")
+    run_ranks(_allreduce_worker, 2, 3 << 20, "float32", False, env=env)  # 12 MiB through 4 MiB pools
+
+
+def _strided_worker(rank, n, uid):
+    """Reduce-scatter / all-gather / all-to-all on the suffix of every segment (the multipath split)."""
+    import hylink_b200._native as N
+
+    c = _comm(rank, n, uid)
+    seg, stride = 6000, 2500
+    lib = N.lib
+    f32, SUM = 7, 0
+    # reduce-scatter: n input segments, output one segment; only [stride, seg) is touched
+    x = torch.cat([_data(rank, seg, torch.float32, seed=q) for q in range(n)])
+    out = torch.full((seg,), -7.0)
+    from hylink_b200._native import check
+
+    pccl = C.CDLL(None)
+    check(lib.pcclReduceScatterStridedTyped(x.data_ptr(), out.data_ptr(), seg * n, stride, f32, SUM, c._h, None), "rs strided")
+    c.drain()
+    ref = sum(_data(r, seg, torch.float32, seed=rank).double() for r in range(n))
+    assert torch.all(out[:stride] == -7.0)
+    assert torch.allclose(out[stride:].double(), ref[stride:], atol=1e-5)
+    # all-gather
+    mine = _data(rank, seg, torch.float32, seed=50)
+    full = torch.full((seg * n,), -3.0)
+    check(lib.pcclAllGatherStridedTyped(mine.data_ptr(), full.data_ptr(), seg, stride, f32, c._h, None), "ag strided")
+    c.drain()
+    for q in range(n):
+        assert torch.all(full[q * seg:q * seg + stride] == -3.0)
+        assert torch.equal(full[q * seg + stride:(q + 1) * seg], _data(q, seg, torch.float32, seed=50)[stride:])
+    # all-to-all
+    a = torch.cat([_data(rank, seg, torch.float32, seed=70 + q) for q in range(n)])
+    b = torch.full((seg * n,), -1.0)
+    check(lib.pcclAllToAllStridedTyped(a.data_ptr(), b.data_ptr(), seg * n, stride, f32, c._h, None), "a2a strided")
+    c.drain()
+    for q in range(n):
+        assert torch.all(b[q * seg:q * seg + stride] == -1.0)
+        assert torch.equal(b[q * seg + stride:(q + 1) * seg], _data(q, seg, torch.float32, seed=70 + rank)[stride:])
+    c.close()
+    return True
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_strided_collectives(n):
+    run_ranks(_strided_worker, n, env=SMALL_POOLS)
+
+
+def _misc_worker(rank, n, uid):
+    c = _comm(rank, n, uid)
+    # broadcast from the last rank
+    t = _data(rank, 33333, torch.float32, seed=3)
+    c.broadcast(t, root=n - 1)
+    c.drain()
+    assert torch.equal(t, _data(n - 1, 33333, torch.float32, seed=3))
+    # in-place all-gather (send is the caller's slot of recv) and in-place reduce-scatter
+    seg = 4097
+    full = torch.zeros(seg * n)
+    full[rank * seg:(rank + 1) * seg] = _data(rank, seg, torch.float32, seed=9)
+    c.all_gather(full[rank * seg:(rank + 1) * seg], full)
+    c.drain()
+    for q in range(n):
+        assert torch.equal(full[q * seg:(q + 1) * seg], _data(q, seg, torch.float32, seed=9))
+    x = torch.cat([_data(rank, seg, torch.float32, seed=20 + q) for q in range(n)])
+    ref = sum(_data(r, seg, torch.float32, seed=20 + rank).double() for r in range(n))
+    c.reduce_scatter(x, x[rank * seg:(rank + 1) * seg])
+    c.drain()
+    assert torch.allclose(x[rank * seg:(rank + 1) * seg].double(), ref, atol=1e-5)
+    # max / avg and integer types
+    v = torch.full((1000,), float(rank + 1))
+    c.all_reduce(v, op="max")
+    c.drain()
+    assert torch.all(v == n)
+    v = torch.full((1000,), float(rank + 1))
+    c.all_reduce(v, op="avg")
+    c.drain()
+    assert torch.allclose(v, torch.full((1000,), (n + 1) / 2))
+    iv = torch.arange(777, dtype=torch.int64) + rank
+    c.all_reduce(iv)
+    c.drain()
+    assert torch.equal(iv, torch.arange(777, dtype=torch.int64) * n + sum(range(n)))
+    assert c.async_error() == 0
+    c.close()
+    return True
+
+
+def test_broadcast_inplace_ops_and_integers():
+    run_ranks(_misc_worker, 4, env=SMALL_POOLS)
+
+
+def _custom_ir_worker(rank, n, uid, xml):
+    import hylink_b200._native as N
+
+    c = _comm(rank, n, uid)
+    count = 20000
+    x = _data(rank, count, torch.float32, seed=5)
+    out = torch.zeros(count)
+    N.check(N.lib.hlSubmitIr(c._h, xml.encode(), x.data_ptr(), out.data_ptr(), count, 0, 1, 1, 7, 0, None), "hlSubmitIr")
+    c.drain()
+    ref = sum(_data(r, count, torch.float32, seed=5) for r in range(n))
+    assert torch.allclose(out, ref, atol=1e-5)
+    c.close()
+    return True
+
+
+def test_hand_written_schedule_runs():
+    from test_ir import RELAY_AR
+
+    run_ranks(_custom_ir_worker, 2, RELAY_AR, env=SMALL_POOLS)
+
+
+def _dead_peer_worker(rank, n, uid):
+    """Rank 1 leaves between collectives; rank 0's next collective must end with an error, not hang."""
+    import time
+
+    c = _comm(rank, n, uid)
+    x = torch.ones(1000)
+    c.all_reduce(x)
+    c.drain()
+    if rank == 1:
+        import os
+
+        os._exit(0)  # no goodbye: the peer has to notice on its own
+    time.sleep(0.5)
+    from hylink_b200 import HylinkError
+
+    t0 = time.time()
+    try:
+        c.all_reduce(x)
+        c.drain()
+    except HylinkError as e:
+        assert e.code in (6, 8), e  # timeout or remote error
+        assert time.time() - t0 < 20
+        return "detected"
+    raise AssertionError("collective with a dead peer completed")
+
+
+def test_dead_peer_is_detected():
+    import multiprocessing as mp
+
+    from hylink_b200.parallel.comm import unique_id
+    from mp_util import _entry
+
+    uid = unique_id().ljust(128, b"\0")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    env = dict(SMALL_POOLS, HYLINK_EXECUTOR_TIMEOUT_MS="3000", HYLINK_BARRIER_TIMEOUT_MS="3000", HYLINK_LOG_LEVEL="OFF")
+    ps = [ctx.Process(target=_entry, args=(_dead_peer_worker, r, 2, uid, (), q, env)) for r in range(2)]
+    for p in ps:
+        p.start()
+    r, status, val = q.get(timeout=60)
+    for p in ps:
+        p.join(20)
+    assert (r, status, val) == (0, "ok", "detected"), val
