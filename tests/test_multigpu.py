@@ -29,3 +29,28 @@ def test_sweep_correct_against_nccl():
 def test_c10d_backend_and_ddp():
     out = _torchrun(2, ["-m", "hylink_b200.utils.selftest"])
     assert "SELFTEST PASSED" in out, out[-3000:]
+
+
+def test_pcie_path_alone_is_correct():
+    """Collectives routed only through pinned host memory by the CPU executor."""
+    env = {"HYLINK_PCIE_ENABLE": "1", "HYLINK_HOST_BUFFER_SIZE": "256M", "HYLINK_INTERNAL_BUFFER_BYTES": "128M"}
+    out = _torchrun(2, ["-m", "hylink_b200.utils.sweep", "--bytes-from", "64K", "--bytes-to", "32M", "--factor", "8", "--check",
+                        "--colls", "allreduce,reducescatter,allgather,alltoall", "--dtypes", "bf16,fp32", "--iters", "3",
+                        "--path", "pcie", "--no-nccl"], env=env)
+    assert '"failures": 0' in out, out[-3000:]
+    assert '"copy_engine_ops": 0' not in out
+
+
+def test_forked_collectives_are_correct_and_retune():
+    """Every collective forked over NVLink kernels + PCIe schedules, with the feedback controller running."""
+    env = {"HYLINK_ORCH_ENABLE": "1", "HYLINK_MIN_MSG_SIZE": "1M", "HYLINK_MIN_MSG_SIZE_8": "1M",
+           "HYLINK_HOST_BUFFER_SIZE": "256M", "HYLINK_INTERNAL_BUFFER_BYTES": "128M"}
+    out = _torchrun(2, ["-m", "hylink_b200.utils.sweep", "--bytes-from", "2M", "--bytes-to", "128M", "--factor", "8", "--check",
+                        "--colls", "allreduce,reducescatter,allgather,alltoall", "--dtypes", "bf16", "--iters", "12",
+                        "--path", "split", "--no-nccl"], env=env)
+    assert '"failures": 0' in out, out[-3000:]
+    import json
+
+    done = [json.loads(l) for l in out.splitlines() if l.startswith('{"event": "done"')][0]
+    assert done["stats"]["pcie_bytes"] > 0 and done["stats"]["nvl_bytes"] > 0
+    assert 0.0 < done["stats"]["last_alpha"] < 0.5
