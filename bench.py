@@ -36,7 +36,7 @@ REF_UNAVAILABLE = ("reference cannot run this config here: it has no torch.distr
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index: int):
@@ -44,10 +44,17 @@ class ClockSampler:
         self.rows = []
         self.proc = None
         self.thread = None
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        self.t_begin = time.time()
+
+    def mark_end(self):
+        self.t_end = time.time()
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -70,9 +77,18 @@ class ClockSampler:
             self.thread.join(timeout=2)
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        import datetime as _dt
+
         for r in self.rows:
             if len(r) < 9:
                 continue
+            try:
+                ts = _dt.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                # samples outside the timed region (warm-up, set-up) are not evidence about it
+                if self.t_begin and self.t_end and not (self.t_begin - 0.05 <= ts <= self.t_end + 0.25):
+                    continue
+            except ValueError:
+                pass
             try:
                 sm.append(float(r[1]))
                 smax.append(float(r[2]))
@@ -109,15 +125,16 @@ def run_arm(backend: str, args, tokens_shape):
 
         return backend_stats()
 
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to come up: start it before the warm-up
     for i in range(args.warmup):
         t = dev_tokens[i % len(dev_tokens)]
         trainer.step_device(t[:, :-1], t[:, 1:])
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    sampler = ClockSampler(dev.index)
-    if rank == 0:
-        sampler.start()
+    sampler.mark_begin()
     before = stats().get("kernel_launches", 0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -127,6 +144,7 @@ def run_arm(backend: str, args, tokens_shape):
         loss = trainer.step_device(t[:, :-1], t[:, 1:])
     e1.record()
     torch.cuda.synchronize()
+    sampler.mark_end()
     dist.barrier()
     torch.cuda.synchronize()
     dev_ms = e0.elapsed_time(e1) / args.steps

@@ -140,6 +140,11 @@ hlResult_t hlCommInitRankDevice(hlComm_t* out, int nranks, hlUniqueId id, int ra
   return hl::commInit(out, nranks, id, rank, device, flags);
 }
 
+hlResult_t hlSetRendezvousTimeoutMs(int ms) {
+  hl::setAttachTimeoutMs(ms);
+  return hlSuccess;
+}
+
 hlResult_t hlCommDestroy(hlComm_t comm) {
   if (!comm) return hlSuccess;
   if (!comm->host_device) {

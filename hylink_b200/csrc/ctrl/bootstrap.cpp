@@ -34,6 +34,12 @@ bool idIsZero(const hlUniqueId& id) {
   return true;
 }
 
+// Rendezvous limit of the NEXT Bootstrap::create on this thread (0 = the
+// configured barrier timeout). Lets a caller probe "are all ranks on this
+// node?" with a short wait without shortening the run-time barriers.
+static thread_local int g_attach_timeout_ms = 0;
+void setAttachTimeoutMs(int ms) { g_attach_timeout_ms = ms; }
+
 static void backoff(uint32_t& spins) {
   ++spins;
   if (spins < 256) cpuRelax();
@@ -90,7 +96,9 @@ hlResult_t Bootstrap::create(const hlUniqueId& id, int nranks, int rank, size_t 
   std::unique_ptr<Bootstrap> b(new Bootstrap());
   b->rank_ = rank;
   b->nranks_ = nranks;
-  b->timeout_ms_ = timeout_ms > 0 ? timeout_ms : Config::get().barrier_timeout_ms;
+  const int run_timeout = timeout_ms > 0 ? timeout_ms : Config::get().barrier_timeout_ms;
+  b->timeout_ms_ = g_attach_timeout_ms > 0 ? g_attach_timeout_ms : run_timeout;
+  g_attach_timeout_ms = 0;
   b->map_bytes_ = blockBytes(extra_bytes);
   b->single_process_ = idIsZero(id);
   char tag[32];
@@ -167,6 +175,7 @@ hlResult_t Bootstrap::create(const hlUniqueId& id, int nranks, int rank, size_t 
   const uint32_t att = b->block_->attached.fetch_add(1) + 1;
   // Everybody is in: the name has served its purpose.
   hlResult_t r = b->barrier(kBarInit);
+  b->timeout_ms_ = run_timeout;
   if (!b->single_process_ && att == (uint32_t)nranks) shm_unlink(b->shm_name_.c_str());
   if (r != hlSuccess) {
     if (!b->single_process_) shm_unlink(b->shm_name_.c_str());

@@ -107,6 +107,7 @@ class Bootstrap {
   std::vector<std::pair<int, std::pair<int, uint32_t>>> early_;  // (from, (fd, tag)) received ahead of time
 };
 
+void setAttachTimeoutMs(int ms);
 uint64_t hashId(const hlUniqueId& id);
 bool idIsZero(const hlUniqueId& id);
 

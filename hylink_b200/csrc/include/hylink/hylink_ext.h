@@ -33,6 +33,10 @@ hlResult_t hlEmuLaunches(hlEmu_t e, uint64_t* n);
 hlResult_t hlReduceLanding(void* dst, const void* const* srcs, int nsrc, int accumulate, size_t count,
                            hlDataType_t t, hlRedOp_t op, float scale, int blocks, hlStream_t stream);
 
+/* Limits how long the NEXT hlCommInitRank* on the calling thread waits for
+ * its peers to show up (then reverts to the configured timeout). */
+hlResult_t hlSetRendezvousTimeoutMs(int ms);
+
 /* ---- schedule IR tools ---------------------------------------------------- */
 typedef struct {
   int nranks, instructions, dependency_edges;

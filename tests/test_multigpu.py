@@ -54,3 +54,13 @@ def test_forked_collectives_are_correct_and_retune():
     done = [json.loads(l) for l in out.splitlines() if l.startswith('{"event": "done"')][0]
     assert done["stats"]["pcie_bytes"] > 0 and done["stats"]["nvl_bytes"] > 0
     assert 0.0 < done["stats"]["last_alpha"] < 0.5
+
+
+def test_nccl_symbol_layer_serves_an_unmodified_nccl_program():
+    from hylink_b200.utils.nccl_shim_check import real_nccl_path, shim_path
+
+    env = {"LD_PRELOAD": shim_path(), "HYLINK_REAL_NCCL": real_nccl_path()}
+    out = _torchrun(2, ["-m", "hylink_b200.utils.nccl_shim_check"], env=env)
+    line = [l for l in out.splitlines() if l.startswith("NCCL_SHIM_CHECK")][-1]
+    served = int(line.split("served=")[1].split()[0])
+    assert served >= 8, line
