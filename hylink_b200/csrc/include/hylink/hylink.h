@@ -67,7 +67,8 @@ typedef enum {
   hlAlgoAuto = 0,
   hlAlgoOneShot = 1,     /* every rank reads all peers, one barrier pair */
   hlAlgoTwoShotP2p = 2,  /* pull-reduce of the owned shard, pull all-gather; fixed sum order */
-  hlAlgoNvls = 3         /* multimem.ld_reduce + multimem.st through NVSwitch */
+  hlAlgoNvls = 3,        /* multimem.ld_reduce + multimem.st through NVSwitch */
+  hlAlgoPipelined = 4    /* warp-specialised tiles: copy-in, link exchange and copy-out overlap */
 } hlAlgo_t;
 
 #define HL_UNIQUE_ID_BYTES 128

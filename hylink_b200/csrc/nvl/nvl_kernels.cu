@@ -272,6 +272,186 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceNvls(const HlCommDev
     copyOutAny<W>(a.out, a.out_dt, s * sp * N, mine + s * sp, segElems(a.count, s * sp * N, sp * N), x);
 }
 
+// ------------------------------------------------------------------ pipelined all-reduce / reduce-scatter
+// Large messages: the three phases of the two-shot scheme run CONCURRENTLY on
+// different tiles. Each CTA is split into three warp groups,
+//   A (6 warps)  copy-in:   caller's buffer -> symmetric staging (HBM traffic)
+//   B (4 warps)  exchange:  reduce the owned part of the tile over NVLink
+//                           (multimem.ld_reduce through the switch, or 16-byte
+//                           pulls from every peer) and hand the result out
+//                           (multimem.st / pushes to every peer)
+//   C (6 warps)  copy-out:  staging -> caller's output (all-reduce only)
+// and walks the tiles b, b+G, b+2G ... of the message. Tile k of block b is
+// handed from group to group — and from GPU to GPU — by the same mechanism: a
+// monotonically increasing word per (stage, block, source rank) in every rank's
+// flag area, written with st.release.sys after a group-wide named barrier and
+// polled (bounded) with ld.acquire.sys. While group B of a block moves tile k
+// over NVLink, group A already stages tile k+1 from HBM and group C drains tile
+// k-1, so the HBM copies hide behind the link time instead of adding to it.
+// Staging is as large as the (sliced) message, so tiles never wait for space.
+__device__ __forceinline__ void groupSync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+__device__ __forceinline__ void tileSignal(const HlCommDev& c, int kind, uint64_t value, int gtid) {
+  if (gtid < c.nranks) {
+    __threadfence_system();
+    stReleaseSys(c.flags[gtid] + ((size_t)kind * HL_MAX_BLOCKS + blockIdx.x) * HL_MAX_RANKS + c.rank, value);
+  }
+}
+
+// Returns through *abort_flag (shared memory) whether the wait was abandoned.
+__device__ __forceinline__ void tileWait(const HlCommDev& c, int kind, uint64_t value, int gtid, volatile int* abort_flag, int step) {
+  if (gtid < c.nranks) {
+    const uint64_t* mine = c.flags[c.rank] + ((size_t)kind * HL_MAX_BLOCKS + blockIdx.x) * HL_MAX_RANKS + gtid;
+    uint64_t t0 = 0;
+    uint32_t spins = 0;
+    while (ldAcquireSys(mine) < value) {
+      if ((++spins & 31u) == 0) {
+        const uint64_t now = globalTimerNs();
+        if (t0 == 0) t0 = now;
+        const bool aborted = *reinterpret_cast<volatile uint32_t*>(c.abort_word) != 0 || *abort_flag != 0;
+        if (aborted || now - t0 > c.timeout_ns) {
+          if (!aborted) {
+            volatile uint64_t* st = c.status;
+            st[1] = ((uint64_t)step << 32) | (uint64_t)gtid;
+            st[2] = blockIdx.x;
+            st[0] = HL_DEV_TIMEOUT;
+            *reinterpret_cast<volatile uint32_t*>(c.abort_word) = 1;
+            __threadfence_system();
+          }
+          *abort_flag = 1;
+          break;
+        }
+      }
+    }
+  }
+}
+
+constexpr int kPipeWarpsA = 6, kPipeWarpsB = 4, kPipeWarpsC = 6;
+
+template <typename W, bool kNvls, bool kAllReduce>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kPipelined(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const uint64_t np = (a.count + N - 1) / N;
+  const uint64_t sp = kAllReduce ? (np + n - 1) / n : np;   // packets per shard (all-reduce) or per segment (reduce-scatter)
+  const uint64_t tps = a.tile_packets;
+  const uint64_t tiles = (sp + tps - 1) / tps;
+  const uint64_t in_stride = kAllReduce ? sp * N : a.in_seg_stride;   // elements between shards / segments in the input
+  const uint64_t seg_elems = a.count;                                 // reduce-scatter: valid elements per segment
+  const int warp = threadIdx.x >> 5;
+  const int role = warp < kPipeWarpsA ? 0 : (warp < kPipeWarpsA + kPipeWarpsB ? 1 : 2);
+  const int gthreads = (role == 0 ? kPipeWarpsA : (role == 1 ? kPipeWarpsB : kPipeWarpsC)) * 32;
+  const int gtid = threadIdx.x - (role == 0 ? 0 : (role == 1 ? kPipeWarpsA : kPipeWarpsA + kPipeWarpsB)) * 32;
+  Ctx x;
+  x.g0 = (uint64_t)gtid;
+  x.gstride = (uint64_t)gthreads;
+  uint4* mine = reinterpret_cast<uint4*>(c.stage[r]);
+  // all-reduce over P2P keeps results in a second region so that peers never overwrite inputs still being pulled
+  const uint64_t res_off = (kAllReduce && !kNvls) ? sp * (uint64_t)n : 0;
+  uint64_t k = 0;
+  for (uint64_t t = blockIdx.x; t < tiles; t += gridDim.x, ++k) {
+    const uint64_t target = a.pipe_seq + k + 1;
+    const uint64_t p0 = t * tps;                                   // first packet of the tile inside a shard
+    const uint64_t tp = sp - p0 < tps ? sp - p0 : tps;             // packets of this tile inside a shard
+    if (role == 0) {
+      for (int s = 0; s < n; ++s) {
+        // elements of shard / segment s that fall into this tile
+        uint64_t e0 = p0 * N, cnt;
+        if constexpr (kAllReduce) {
+          const uint64_t g0e = (uint64_t)s * in_stride + e0;       // global element index
+          cnt = g0e >= a.count ? 0 : (a.count - g0e < tp * N ? a.count - g0e : tp * N);
+          const uint64_t shard_left = sp * N - e0;                 // never run into the next shard
+          if (cnt > shard_left) cnt = shard_left;
+        } else {
+          cnt = e0 >= seg_elems ? 0 : (seg_elems - e0 < tp * N ? seg_elems - e0 : tp * N);
+        }
+        copyInAny<W>(mine + (uint64_t)s * sp + p0, a.in, a.in_dt, (uint64_t)s * in_stride + e0, cnt, x);
+      }
+      groupSync(1, gthreads);
+      tileSignal(c, 1, target, gtid);
+    } else if (role == 1) {
+      tileWait(c, 1, target, gtid, &s_abort, 1);
+      groupSync(2, gthreads);
+      if (s_abort) break;
+      const uint64_t first = (uint64_t)r * sp + p0;
+      if constexpr (kNvls) {
+        uint4* mc = reinterpret_cast<uint4*>(c.mc_stage) + first;
+        for (uint64_t i = x.g0; i < tp; i += x.gstride * kUnroll) {
+          uint4 v[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const uint64_t j = i + (uint64_t)u * x.gstride;
+            if (j < tp) v[u] = multimemLdReduceAdd<W>(mc + j);
+          }
+#pragma unroll
+          for (int u = 0; u < kUnroll; ++u) {
+            const uint64_t j = i + (uint64_t)u * x.gstride;
+            if (j < tp) {
+              if (a.scale != 1.0f) {
+                typename Wire<W>::Acc acc[N];
+                Packet<W>::unpack(v[u], acc);
+                finish<W>(acc, a.scale, 0);
+                v[u] = Packet<W>::pack(acc);
+              }
+              if constexpr (kAllReduce) {
+                multimemSt(mc + j, v[u]);
+              } else {
+                HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + j) * N, a.count, aligned16(a.out), v[u]));
+              }
+            }
+          }
+        }
+      } else {
+        for (uint64_t i = x.g0; i < tp; i += x.gstride) {
+          uint4 v[HL_MAX_RANKS];
+#pragma unroll
+          for (int q = 0; q < HL_MAX_RANKS; ++q)
+            if (q < n) v[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + i];
+          const uint4 red = reducePackets<W>(v, n, a.op, a.scale, a.int_div);
+          if constexpr (kAllReduce) {
+#pragma unroll
+            for (int q = 0; q < HL_MAX_RANKS; ++q)
+              if (q < n) reinterpret_cast<uint4*>(c.stage[q])[res_off + first + i] = red;
+          } else {
+            HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + i) * N, a.count, aligned16(a.out), red));
+          }
+        }
+      }
+      if constexpr (kAllReduce) {
+        groupSync(2, gthreads);
+        tileSignal(c, 2, target, gtid);
+      }
+    } else {
+      if constexpr (kAllReduce) {
+        tileWait(c, 2, target, gtid, &s_abort, 2);
+        groupSync(3, gthreads);
+        if (s_abort) break;
+        for (int s = 0; s < n; ++s) {
+          const uint64_t e0 = p0 * N;
+          const uint64_t g0e = (uint64_t)s * in_stride + e0;
+          uint64_t cnt = g0e >= a.count ? 0 : (a.count - g0e < tp * N ? a.count - g0e : tp * N);
+          const uint64_t shard_left = sp * N - e0;
+          if (cnt > shard_left) cnt = shard_left;
+          copyOutAny<W>(a.out, a.out_dt, g0e, mine + res_off + (uint64_t)s * sp + p0, cnt, x);
+        }
+      }
+    }
+  }
+  if constexpr (!kAllReduce) {
+    // peers pull from this rank's staging in their exchange stage: nobody may start
+    // the next call's copy-in before everybody is through
+    blockBarrier(c, a.seq + 1, 3);
+  }
+}
+
 // ------------------------------------------------------------------ reduce-scatter
 // `in` holds n segments (stride in_seg_stride); the first `count` elements of
 // each are handled. copy-in | barrier | pull-reduce segment r from every peer
@@ -434,12 +614,16 @@ static const void* pickKernelT(int kind) {
     case kNvlAllToAll: return (const void*)kAllToAll<W>;
     case kNvlAllGatherNvls: return (const void*)kAllGather<W, true>;
     case kNvlBroadcastNvls: return (const void*)kBroadcast<W, true>;
+    case kNvlAllReducePipeP2p: return (const void*)kPipelined<W, false, true>;
+    case kNvlReduceScatterPipeP2p: return (const void*)kPipelined<W, false, false>;
     default: break;
   }
   if constexpr (dev::IsFloatTrio<W>::value) {
     switch (kind) {
       case kNvlAllReduceNvls: return (const void*)kAllReduceNvls<W>;
       case kNvlReduceScatterNvls: return (const void*)kReduceScatter<W, true>;
+      case kNvlAllReducePipeNvls: return (const void*)kPipelined<W, true, true>;
+      case kNvlReduceScatterPipeNvls: return (const void*)kPipelined<W, true, false>;
       default: break;
     }
   }
@@ -476,6 +660,10 @@ const char* kernelName(int kind) {
     case kNvlAllToAll: return "alltoall_p2p";
     case kNvlAllGatherNvls: return "allgather_nvls";
     case kNvlBroadcastNvls: return "broadcast_nvls";
+    case kNvlAllReducePipeP2p: return "allreduce_pipelined_p2p";
+    case kNvlAllReducePipeNvls: return "allreduce_pipelined_nvls";
+    case kNvlReduceScatterPipeP2p: return "reducescatter_pipelined_p2p";
+    case kNvlReduceScatterPipeNvls: return "reducescatter_pipelined_nvls";
     default: return "?";
   }
 }
@@ -508,7 +696,8 @@ hlResult_t prepareKernels() {
   // (same cure as pcie-ccl-cuda/kernels/wait_kernel.cu:216-234,400-432).
   static const int kinds[] = {kNvlBarrier, kNvlAllReduceOneShot, kNvlAllReduceTwoShot, kNvlAllReduceNvls,
                               kNvlReduceScatter, kNvlReduceScatterNvls, kNvlAllGather, kNvlBroadcast,
-                              kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls};
+                              kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls, kNvlAllReducePipeP2p,
+                              kNvlAllReducePipeNvls, kNvlReduceScatterPipeP2p, kNvlReduceScatterPipeNvls};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
       const void* fn = kernelFor(k, dt);

@@ -6,7 +6,7 @@
 
 namespace hl {
 
-static constexpr size_t kFlagBytes = (size_t)HL_MAX_BLOCKS * HL_MAX_RANKS * sizeof(uint64_t);
+static constexpr size_t kFlagBytes = (size_t)HL_FLAG_KINDS * HL_MAX_BLOCKS * HL_MAX_RANKS * sizeof(uint64_t);
 
 static size_t flagAreaBytes() { return (kFlagBytes + 4095) & ~(size_t)4095; }
 
@@ -122,6 +122,7 @@ hlResult_t NvlPath::resetAfterError() {
   memset(status_host_, 0, sizeof(uint64_t) * 8 * nl);
   HL_CUDA(cudaDeviceSynchronize());
   seq_ = 0;
+  pipe_seq_ = 0;
   if (!emu_ && bs_) HL_CHECK(bs_->barrier(kBarSymm));
   return hlSuccess;
 }
@@ -146,12 +147,17 @@ bool NvlPath::nvlsPays() const {
   return has_mc_ && nranks_ >= Config::get().nvls_min_ranks;
 }
 
+bool NvlPath::nvlsUsable(int wire_dt, int op, bool deterministic) const {
+  return has_mc_ && (wire_dt == hlFloat32 || wire_dt == hlFloat16 || wire_dt == hlBfloat16) && (op == hlSum || op == hlAvg) &&
+         !deterministic;
+}
+
 int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const {
-  const bool nvls_ok = has_mc_ && (wire_dt == hlFloat32 || wire_dt == hlFloat16 || wire_dt == hlBfloat16) &&
-                       (op == hlSum || op == hlAvg) && !deterministic;
+  const bool nvls_ok = nvlsUsable(wire_dt, op, deterministic);
   if (requested == hlAlgoNvls && !nvls_ok) requested = hlAlgoAuto;
   if (requested != hlAlgoAuto) return requested;
   if (wire_bytes <= Config::get().oneshot_max_bytes) return hlAlgoOneShot;
+  if (wire_bytes >= Config::get().pipe_min_bytes) return hlAlgoPipelined;
   return (nvls_ok && nvlsPays()) ? hlAlgoNvls : hlAlgoTwoShotP2p;
 }
 
@@ -185,8 +191,13 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
   const uint64_t epp = 16 / ws;                         // elements per wire packet
   const uint64_t cap_packets = stage_bytes_ / 16;
   uint64_t per_launch;                                  // elements handled per launch (per segment when segmented)
-  if (segmented || kind == kNvlAllReduceTwoShot || kind == kNvlAllReduceNvls) {
-    uint64_t sp = (cap_packets / (uint64_t)nranks_) & ~(uint64_t)63;
+  const bool pipe = kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePipeNvls || kind == kNvlReduceScatterPipeP2p ||
+                    kind == kNvlReduceScatterPipeNvls;
+  const bool pipe_ar = kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePipeNvls;
+  if (segmented || kind == kNvlAllReduceTwoShot || kind == kNvlAllReduceNvls || pipe_ar) {
+    // the P2P pipelined all-reduce keeps inputs and results in separate halves of the staging region
+    const uint64_t regions = kind == kNvlAllReducePipeP2p ? 2 : 1;
+    uint64_t sp = (cap_packets / ((uint64_t)nranks_ * regions)) & ~(uint64_t)63;
     if (sp == 0) return fail(hlInvalidArgument, "staging region too small");
     per_launch = (segmented ? sp : sp * (uint64_t)nranks_) * epp;
   } else {
@@ -213,7 +224,22 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       a.int_div = (c.op == hlAvg) ? nranks_ : 0;
     }
     const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls ? nranks_ : 1);
-    const int blocks = blocksFor(kind, wire_bytes, c.max_blocks);
+    int blocks = blocksFor(kind, wire_bytes, c.max_blocks);
+    if (pipe) {
+      // tiles: up to 2048 packets (32 KiB) of every shard, at least four tiles per CTA so the stages overlap
+      const uint64_t np = (len + epp - 1) / epp;
+      const uint64_t sp = pipe_ar ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;
+      uint64_t tps = std::min<uint64_t>(2048, std::max<uint64_t>(256, (sp / ((uint64_t)blocks * 4)) & ~(uint64_t)63));
+      const char* forced = getenv("HYLINK_PIPE_TILE_PACKETS");
+      if (forced) tps = std::max<uint64_t>(64, (uint64_t)atoll(forced) & ~(uint64_t)63);
+      const uint64_t tiles = (sp + tps - 1) / tps;
+      blocks = (int)std::min<uint64_t>((uint64_t)blocks, tiles);
+      for (int i = 0; i < nl; ++i) {
+        calls.c[i].tile_packets = tps;
+        calls.c[i].pipe_seq = pipe_seq_;
+      }
+      pipe_seq_ += (tiles + (uint64_t)blocks - 1) / (uint64_t)blocks;
+    }
     seq_ += HL_SEQ_STRIDE;
     const int rows = emu_ ? emu_active_ : 1;
     HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, rows, blocks, s));
@@ -228,16 +254,23 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
   int algo = pickAllReduceAlgo(wire_bytes, c.wire_dt, c.op, c.deterministic, c.algo);
   if (algo == hlAlgoOneShot && wire_bytes > stage_bytes_) algo = hlAlgoTwoShotP2p;
-  const int kind = algo == hlAlgoOneShot ? kNvlAllReduceOneShot : (algo == hlAlgoNvls ? kNvlAllReduceNvls : kNvlAllReduceTwoShot);
+  int kind;
+  if (algo == hlAlgoOneShot) kind = kNvlAllReduceOneShot;
+  else if (algo == hlAlgoNvls) kind = kNvlAllReduceNvls;
+  else if (algo == hlAlgoPipelined) kind = (nvlsUsable(c.wire_dt, c.op, c.deterministic) && nvlsPays()) ? kNvlAllReducePipeNvls : kNvlAllReducePipeP2p;
+  else kind = kNvlAllReduceTwoShot;
   return launchSliced(kind, b, c, false, s);
 }
 
 hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
-  const bool nvls = has_mc_ && !c.deterministic && (c.op == hlSum || c.op == hlAvg) && c.algo != hlAlgoTwoShotP2p &&
-                    c.algo != hlAlgoOneShot && (c.algo == hlAlgoNvls || nvlsPays()) &&
-                    (c.wire_dt == hlFloat32 || c.wire_dt == hlFloat16 || c.wire_dt == hlBfloat16);
-  return launchSliced(nvls ? kNvlReduceScatterNvls : kNvlReduceScatter, b, c, true, s);
+  const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
+  const bool nvls = nvlsUsable(c.wire_dt, c.op, c.deterministic) && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot &&
+                    (c.algo == hlAlgoNvls || nvlsPays());
+  const bool pipe = c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().pipe_min_bytes);
+  int kind = nvls ? kNvlReduceScatterNvls : kNvlReduceScatter;
+  if (pipe) kind = nvls ? kNvlReduceScatterPipeNvls : kNvlReduceScatterPipeP2p;
+  return launchSliced(kind, b, c, true, s);
 }
 
 hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {

@@ -7,6 +7,7 @@
 #define HL_MAX_BLOCKS 592     // 148 SMs x 4 resident CTAs
 #define HL_NVL_THREADS 512
 #define HL_SEQ_STRIDE 4       // flag values consumed per collective call
+#define HL_FLAG_KINDS 3       // 0: block barriers; 1, 2: tile hand-offs of the pipelined kernels
 
 // Device status codes written by a kernel whose bounded wait ran out.
 #define HL_DEV_OK 0
@@ -23,7 +24,7 @@ struct HlCommDev {
   int max_blocks;
   int pad0;
   uint8_t* stage[HL_MAX_RANKS];    // symmetric staging region
-  uint64_t* flags[HL_MAX_RANKS];   // [HL_MAX_BLOCKS][HL_MAX_RANKS] monotonically increasing words
+  uint64_t* flags[HL_MAX_RANKS];   // [HL_FLAG_KINDS][HL_MAX_BLOCKS][HL_MAX_RANKS] monotonically increasing words
   uint8_t* mc_stage;               // NVSwitch multicast alias of stage (null without NVLS)
   uint64_t* status;                // host-visible: [0] code, [1] detail (step<<32 | peer), [2] block
   uint32_t* abort_word;            // device word: non-zero poisons the communicator
@@ -45,6 +46,8 @@ struct HlCallArgs {
   int out_dt;               // hlDataType_t of `out`
   int root;
   int int_div;              // integer types: divide the sum (hlAvg), 0 = off
+  uint64_t pipe_seq;        // pipelined kernels: tile k of a block is announced as pipe_seq + k + 1
+  uint64_t tile_packets;    // pipelined kernels: 16-byte packets of one shard handled per tile
 };
 
 // One argument block per emulated rank: on a single GPU the N ranks of a test
@@ -66,4 +69,8 @@ enum HlNvlKernel {
   kNvlAllToAll = 8,
   kNvlAllGatherNvls = 9,
   kNvlBroadcastNvls = 10,
+  kNvlAllReducePipeP2p = 11,
+  kNvlAllReducePipeNvls = 12,
+  kNvlReduceScatterPipeP2p = 13,
+  kNvlReduceScatterPipeNvls = 14,
 };

@@ -119,7 +119,10 @@ class HylinkWork : public c10d::Work {
 class HylinkBackend : public c10d::Backend {
  public:
   HylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size, std::chrono::milliseconds timeout)
-      : c10d::Backend(rank, size), store_(store), timeout_(timeout) {}
+      : c10d::Backend(rank, size), store_(store), timeout_(timeout) {
+    // CTAs the all-reduce may occupy while it overlaps with the backward pass (0 = the library's table)
+    if (const char* e = getenv("HYLINK_TORCH_MAX_BLOCKS")) max_blocks_ = atoi(e);
+  }
   ~HylinkBackend() override { shutdown(); }
 
   const std::string getBackendName() const override { return "hylink"; }
@@ -199,6 +202,7 @@ class HylinkBackend : public c10d::Backend {
       hlCallOpts o;
       memset(&o, 0, sizeof(o));
       o.scale = fused_scale_ != 0.0f ? fused_scale_ : oi.scale;
+      o.max_blocks = max_blocks_;
       hlCheck(hlAllReduceEx(t.data_ptr(), t.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), oi.op, &o, c, s), "allreduce");
     });
   }
@@ -390,6 +394,7 @@ class HylinkBackend : public c10d::Backend {
   std::unique_ptr<c10::cuda::CUDAStream> comm_stream_;
   uint64_t collectives_ = 0;
   float fused_scale_ = 0.0f;
+  int max_blocks_ = 0;
 };
 
 c10::intrusive_ptr<c10d::Backend> createHylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,

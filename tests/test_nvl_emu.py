@@ -210,3 +210,69 @@ def test_bounded_wait_reports_timeout_and_recovers():
     assert g.status(0)[0] == 0
     assert torch.equal(outs[0], ins[0] + ins[1]) and torch.equal(outs[1], outs[0])
     g.close()
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pipelined_allreduce_bitwise(n, dtype):
+    """Warp-specialised tiles (copy-in / exchange / copy-out overlapped): same fixed-order sum."""
+    g = _group(n, stage_bytes=64 << 20)
+    for count in [5, 4097, 300001, (1 << 21) + 13]:
+        ins = [_rand(count, dtype, 7 * r + count % 89) for r in range(n)]
+        outs = [torch.full((count + 8,), 3, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("all_reduce", ins, [o[:count] for o in outs], count, algo="pipelined", scale=0.5)
+        torch.cuda.synchronize()
+        ref = (_ordered_sum(ins, torch.float32) * 0.5).to(dtype)
+        for r in range(n):
+            assert torch.equal(outs[r][:count], ref), (n, dtype, count, r)
+            assert torch.all(outs[r][count:] == 3)
+        assert g.status(0)[0] == 0
+    g.close()
+
+
+def test_pipelined_allreduce_in_place_sliced_and_mixed_with_classic_kernels():
+    n, count = 4, (3 << 20) + 5
+    g = _group(n, stage_bytes=8 << 20)  # forces several launches per call
+    for it in range(3):
+        bufs = [_rand(count, torch.float32, 31 * it + r) for r in range(n)]
+        ref = _ordered_sum([b.clone() for b in bufs], torch.float32)
+        g.run("all_reduce", bufs, bufs, count, algo="pipelined")
+        small = [b[:1000].clone() for b in bufs]
+        g.run("all_reduce", small, small, 1000, algo="oneshot")
+        torch.cuda.synchronize()
+        for b, s in zip(bufs, small):
+            assert torch.equal(b, ref)
+            assert torch.equal(s, ref[:1000] * n)
+    g.close()
+
+
+@pytest.mark.parametrize("n", [2, 8])
+def test_pipelined_reduce_scatter_strided(n):
+    g = _group(n, stage_bytes=64 << 20)
+    seg, prefix = 400000, 333337
+    ins = [_rand(seg * n, torch.bfloat16, 5 + r) for r in range(n)]
+    outs = [torch.full((seg,), 9, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    g.run("reduce_scatter", ins, outs, prefix, in_seg_stride=seg, algo="pipelined")
+    torch.cuda.synchronize()
+    for r in range(n):
+        ref = _ordered_sum([t[r * seg:r * seg + prefix] for t in ins], torch.float32).to(torch.bfloat16)
+        assert torch.equal(outs[r][:prefix], ref)
+        assert torch.all(outs[r][prefix:] == 9)
+    g.close()
+
+
+def test_pipelined_wait_is_bounded():
+    n, count = 2, 1 << 20
+    g = _group(n, timeout_ms=200)
+    ins = [_rand(count, torch.float32, r) for r in range(n)]
+    outs = [torch.zeros(count, device="cuda") for _ in range(n)]
+    g.set_active_ranks(1)
+    g.run("all_reduce", ins, outs, count, algo="pipelined")
+    torch.cuda.synchronize()
+    assert g.status(0)[0] == 1
+    g.set_active_ranks(n)
+    g.reset()
+    g.run("all_reduce", ins, outs, count, algo="pipelined")
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], ins[0] + ins[1])
+    g.close()
