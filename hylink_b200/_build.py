@@ -8,7 +8,8 @@ Produces, under ``hylink_b200/lib/``:
   ``nvcc -gencode arch=compute_100a,code=sm_100a``; the CUDA runtime is linked
   statically and the driver is resolved at run time, so the library also loads
   on a machine without a GPU.
-* ``libhylink_nccl.so`` — the drop-in ``nccl*`` symbol layer.
+* ``libhylink_nccl.so`` — the drop-in ``nccl*`` symbol layer; ``libhylink_cudashim.so`` — opt-in
+  interposers of host-blocking CUDA runtime calls.
 * ``_hylink_c10d.so`` — the ``torch.distributed`` backend extension.
 
 Objects are rebuilt only when a source or any header is newer.
@@ -94,19 +95,25 @@ def build_core(verbose: bool = False) -> Path:
 
 
 def build_nccl_shim(verbose: bool = False) -> Path | None:
-    srcs = [CSRC / "api" / n for n in sorted(SEPARATE) if (CSRC / "api" / n).exists()]
-    if not srcs:
-        return None
+    """libhylink_nccl.so (drop-in nccl* symbols) and libhylink_cudashim.so (opt-in interposers of blocking CUDA calls)."""
     hdr = _newest_header()
-    objs = [OBJ / ("shim_" + s.name + ".o") for s in srcs]
-    changed = [_compile(s, o, hdr, []) for s, o in zip(srcs, objs)]
-    target = LIB / "libhylink_nccl.so"
-    if any(changed) or not target.exists():
-        _run(["g++", "-shared", "-o", str(target), *map(str, objs), "-L", str(LIB), "-lhylink_b200",
-              "-Wl,-rpath,$ORIGIN", "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
-        if verbose:
-            print("linked", target)
-    return target
+    out = None
+    plan = [("nccl_shim.cpp", "libhylink_nccl.so", ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static"]),
+            ("cuda_block_shim.cpp", "libhylink_cudashim.so", [])]
+    for src_name, lib_name, extra in plan:
+        src = CSRC / "api" / src_name
+        if not src.exists():
+            continue
+        obj = OBJ / ("shim_" + src_name + ".o")
+        changed = _compile(src, obj, hdr, [])
+        target = LIB / lib_name
+        if changed or not target.exists():
+            _run(["g++", "-shared", "-o", str(target), str(obj), "-L", str(LIB), "-lhylink_b200", "-Wl,-rpath,$ORIGIN",
+                  *extra, "-lpthread", "-ldl", "-lrt"])
+            if verbose:
+                print("linked", target)
+        out = out or target
+    return out
 
 
 def build_torch_ext(verbose: bool = False) -> Path | None:

@@ -82,6 +82,7 @@ static hlPath_t choosePath(hlComm* c, hlPath_t asked, size_t bytes) {
 hlResult_t commInit(hlComm_t* out, int nranks, hlUniqueId id, int rank, int device, unsigned flags) {
   if (!out) return fail(hlInvalidArgument, "null comm pointer");
   const Config& cfg = Config::get();
+  installSigdump();
   std::unique_ptr<hlComm> c(new hlComm());
   c->rank = rank;
   c->nranks = nranks;

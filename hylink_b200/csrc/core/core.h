@@ -132,4 +132,7 @@ struct Config {
 // chunk/64 up to 16 MiB. Same rule as pcie-ccl-cuda/src/ir/ir.hpp:29-54.
 size_t subchunkSliceFor(size_t chunk_bytes);
 
+// Arms the SIGUSR1 stack dump when the configuration asks for it (idempotent).
+void installSigdump();
+
 }  // namespace hl

@@ -65,6 +65,8 @@ int hlHostSimdLevel(void);
 void hlTraceOpen(const char* path, int rank);
 void hlTraceFlush(void);
 void hlConfigReload(void);
+/* Arms the SIGUSR1 all-threads stack dump (needs HYLINK_SIGDUMP=1). */
+void hlInstallSigdump(void);
 
 /* ---- control-plane self check (no GPU): barrier, mailbox, fd passing ------ */
 hlResult_t hlCtrlSelfTest(hlUniqueId id, int nranks, int rank, int rounds);

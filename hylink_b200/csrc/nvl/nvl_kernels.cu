@@ -49,20 +49,20 @@ __device__ __forceinline__ Ctx makeCtx() {
 }
 
 // user segment -> staging (packets of this block's residue class)
-template <typename S, typename W, bool kMc>
+template <typename S, typename W, bool kMc, int U = kUnroll>
 __device__ __forceinline__ void segCopyIn(uint4* stage_seg, const S* src, uint64_t seg_count, const Ctx& x) {
   constexpr int N = Packet<W>::N;
   const uint64_t np = (seg_count + N - 1) / N;
   const bool vec = aligned16(src);
-  for (uint64_t i = x.g0; i < np; i += x.gstride * kUnroll) {
-    uint4 v[kUnroll];
+  for (uint64_t i = x.g0; i < np; i += x.gstride * U) {
+    uint4 v[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
       if (j < np) v[u] = loadUserPacket<S, W>(src, j * N, seg_count, vec);
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
       if (j < np) {
         if constexpr (kMc) multimemSt(stage_seg + j, v[u]);  // stage_seg is a multicast address
@@ -73,20 +73,20 @@ __device__ __forceinline__ void segCopyIn(uint4* stage_seg, const S* src, uint64
 }
 
 // staging (local or peer) -> user segment
-template <typename W, typename D>
+template <typename W, typename D, int U = kUnroll>
 __device__ __forceinline__ void segCopyOut(D* dst, const uint4* stage_seg, uint64_t seg_count, const Ctx& x) {
   constexpr int N = Packet<W>::N;
   const uint64_t np = (seg_count + N - 1) / N;
   const bool vec = aligned16(dst);
-  for (uint64_t i = x.g0; i < np; i += x.gstride * kUnroll) {
-    uint4 v[kUnroll];
+  for (uint64_t i = x.g0; i < np; i += x.gstride * U) {
+    uint4 v[U];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
       if (j < np) v[u] = stage_seg[j];
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
       if (j < np) storeUserPacket<W, D>(dst, j * N, seg_count, vec, v[u]);
     }
@@ -129,15 +129,15 @@ __device__ __forceinline__ uint4 reducePackets(const uint4* v, int n, int op, fl
     }                                                                         \
   } while (0)
 
-template <typename W, bool kMc = false>
+template <typename W, bool kMc = false, int U = kUnroll>
 __device__ __forceinline__ void copyInAny(uint4* stage_seg, const void* src, int dt, uint64_t elem_off,
                                           uint64_t seg_count, const Ctx& x) {
-  HL_USER_TYPE_SWITCH(W, dt, S, segCopyIn<S, W, kMc>(stage_seg, reinterpret_cast<const S*>(src) + elem_off, seg_count, x));
+  HL_USER_TYPE_SWITCH(W, dt, S, segCopyIn<S, W, kMc, U>(stage_seg, reinterpret_cast<const S*>(src) + elem_off, seg_count, x));
 }
-template <typename W>
+template <typename W, int U = kUnroll>
 __device__ __forceinline__ void copyOutAny(void* dst, int dt, uint64_t elem_off, const uint4* stage_seg,
                                            uint64_t seg_count, const Ctx& x) {
-  HL_USER_TYPE_SWITCH(W, dt, D, segCopyOut<W, D>(reinterpret_cast<D*>(dst) + elem_off, stage_seg, seg_count, x));
+  HL_USER_TYPE_SWITCH(W, dt, D, segCopyOut<W, D, U>(reinterpret_cast<D*>(dst) + elem_off, stage_seg, seg_count, x));
 }
 
 __device__ __forceinline__ uint64_t segElems(uint64_t count, uint64_t first, uint64_t span) {
@@ -275,12 +275,12 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceNvls(const HlCommDev
 // ------------------------------------------------------------------ pipelined all-reduce / reduce-scatter
 // Large messages: the three phases of the two-shot scheme run CONCURRENTLY on
 // different tiles. Each CTA is split into three warp groups,
-//   A (6 warps)  copy-in:   caller's buffer -> symmetric staging (HBM traffic)
-//   B (4 warps)  exchange:  reduce the owned part of the tile over NVLink
+//   A  copy-in:   caller's buffer -> symmetric staging (HBM traffic)
+//   B  exchange:  reduce the owned part of the tile over NVLink
 //                           (multimem.ld_reduce through the switch, or 16-byte
 //                           pulls from every peer) and hand the result out
 //                           (multimem.st / pushes to every peer)
-//   C (6 warps)  copy-out:  staging -> caller's output (all-reduce only)
+//   C  copy-out:  staging -> caller's output (all-reduce only)
 // and walks the tiles b, b+G, b+2G ... of the message. Tile k of block b is
 // handed from group to group — and from GPU to GPU — by the same mechanism: a
 // monotonically increasing word per (stage, block, source rank) in every rank's
@@ -328,10 +328,59 @@ __device__ __forceinline__ void tileWait(const HlCommDev& c, int kind, uint64_t 
   }
 }
 
-constexpr int kPipeWarpsA = 6, kPipeWarpsB = 4, kPipeWarpsC = 6;
+// Warp split A / B / C. Through the switch a rank receives only 1/n of the
+// message, so few warps keep the link busy and the HBM copies get the rest;
+// peer pulls need (n-1)/n of the message in flight and get half of the CTA.
+template <bool kNvls> struct PipeShape {
+  static constexpr int A = kNvls ? 5 : 4, B = kNvls ? 2 : 4, C = kNvls ? 5 : 4;
+};
+constexpr int kPipeCopyUnroll = 4;
+constexpr int kPipeThreads = 384;  // 12 warps: leaves ~170 registers per thread for the deep unrolls
+
+// Exchange stage over peer pointers with the rank count known at compile
+// time: U packets x NR peers of 16-byte loads are in flight per thread.
+template <typename W, int NR, int U, bool kAllReduce>
+__device__ __forceinline__ void pullReduceTile(const HlCommDev& c, const HlCallArgs& a, uint64_t first, uint64_t res_off,
+                                               uint64_t p0, uint64_t tp, const Ctx& x) {
+  constexpr int N = Packet<W>::N;
+  const bool vec = aligned16(a.out);
+  for (uint64_t i = x.g0; i < tp; i += x.gstride * U) {
+    uint4 v[U][NR];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < tp) {
+#pragma unroll
+        for (int q = 0; q < NR; ++q) v[u][q] = reinterpret_cast<const uint4*>(c.stage[q])[first + j];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < tp) {
+        typename Wire<W>::Acc acc[N], b[N];
+        Packet<W>::unpack(v[u][0], acc);
+#pragma unroll
+        for (int q = 1; q < NR; ++q) {
+          Packet<W>::unpack(v[u][q], b);
+#pragma unroll
+          for (int e = 0; e < N; ++e) acc[e] = applyOp(a.op, acc[e], b[e]);
+        }
+        finish<W>(acc, a.scale, a.int_div);
+        const uint4 red = Packet<W>::pack(acc);
+        if constexpr (kAllReduce) {
+#pragma unroll
+          for (int q = 0; q < NR; ++q) reinterpret_cast<uint4*>(c.stage[q])[res_off + first + j] = red;
+        } else {
+          HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + j) * N, a.count, vec, red));
+        }
+      }
+    }
+  }
+}
 
 template <typename W, bool kNvls, bool kAllReduce>
-__global__ void __launch_bounds__(HL_NVL_THREADS) kPipelined(const HlCommDev* comms, HlEmuCalls calls) {
+__global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
   const HlCallArgs& a = calls.c[blockIdx.y];
   if (!entryOk(c)) return;
@@ -347,6 +396,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPipelined(const HlCommDev* co
   const uint64_t in_stride = kAllReduce ? sp * N : a.in_seg_stride;   // elements between shards / segments in the input
   const uint64_t seg_elems = a.count;                                 // reduce-scatter: valid elements per segment
   const int warp = threadIdx.x >> 5;
+  constexpr int kPipeWarpsA = PipeShape<kNvls>::A, kPipeWarpsB = PipeShape<kNvls>::B, kPipeWarpsC = PipeShape<kNvls>::C;
+  static_assert((kPipeWarpsA + kPipeWarpsB + kPipeWarpsC) * 32 == kPipeThreads, "warp groups must fill the CTA");
   const int role = warp < kPipeWarpsA ? 0 : (warp < kPipeWarpsA + kPipeWarpsB ? 1 : 2);
   const int gthreads = (role == 0 ? kPipeWarpsA : (role == 1 ? kPipeWarpsB : kPipeWarpsC)) * 32;
   const int gtid = threadIdx.x - (role == 0 ? 0 : (role == 1 ? kPipeWarpsA : kPipeWarpsA + kPipeWarpsB)) * 32;
@@ -373,7 +424,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPipelined(const HlCommDev* co
         } else {
           cnt = e0 >= seg_elems ? 0 : (seg_elems - e0 < tp * N ? seg_elems - e0 : tp * N);
         }
-        copyInAny<W>(mine + (uint64_t)s * sp + p0, a.in, a.in_dt, (uint64_t)s * in_stride + e0, cnt, x);
+        copyInAny<W, false, kPipeCopyUnroll>(mine + (uint64_t)s * sp + p0, a.in, a.in_dt, (uint64_t)s * in_stride + e0, cnt, x);
       }
       groupSync(1, gthreads);
       tileSignal(c, 1, target, gtid);
@@ -410,19 +461,26 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPipelined(const HlCommDev* co
           }
         }
       } else {
-        for (uint64_t i = x.g0; i < tp; i += x.gstride) {
-          uint4 v[HL_MAX_RANKS];
+        switch (n) {
+          case 2: pullReduceTile<W, 2, 4, kAllReduce>(c, a, first, res_off, p0, tp, x); break;
+          case 4: pullReduceTile<W, 4, 2, kAllReduce>(c, a, first, res_off, p0, tp, x); break;
+          case 8: pullReduceTile<W, 8, 1, kAllReduce>(c, a, first, res_off, p0, tp, x); break;
+          default:
+            for (uint64_t i = x.g0; i < tp; i += x.gstride) {
+              uint4 v[HL_MAX_RANKS];
 #pragma unroll
-          for (int q = 0; q < HL_MAX_RANKS; ++q)
-            if (q < n) v[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + i];
-          const uint4 red = reducePackets<W>(v, n, a.op, a.scale, a.int_div);
-          if constexpr (kAllReduce) {
+              for (int q = 0; q < HL_MAX_RANKS; ++q)
+                if (q < n) v[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + i];
+              const uint4 red = reducePackets<W>(v, n, a.op, a.scale, a.int_div);
+              if constexpr (kAllReduce) {
 #pragma unroll
-            for (int q = 0; q < HL_MAX_RANKS; ++q)
-              if (q < n) reinterpret_cast<uint4*>(c.stage[q])[res_off + first + i] = red;
-          } else {
-            HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + i) * N, a.count, aligned16(a.out), red));
-          }
+                for (int q = 0; q < HL_MAX_RANKS; ++q)
+                  if (q < n) reinterpret_cast<uint4*>(c.stage[q])[res_off + first + i] = red;
+              } else {
+                HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + i) * N, a.count, aligned16(a.out), red));
+              }
+            }
+            break;
         }
       }
       if constexpr (kAllReduce) {
@@ -440,7 +498,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPipelined(const HlCommDev* co
           uint64_t cnt = g0e >= a.count ? 0 : (a.count - g0e < tp * N ? a.count - g0e : tp * N);
           const uint64_t shard_left = sp * N - e0;
           if (cnt > shard_left) cnt = shard_left;
-          copyOutAny<W>(a.out, a.out_dt, g0e, mine + res_off + (uint64_t)s * sp + p0, cnt, x);
+          copyOutAny<W, kPipeCopyUnroll>(a.out, a.out_dt, g0e, mine + res_off + (uint64_t)s * sp + p0, cnt, x);
         }
       }
     }
@@ -675,7 +733,8 @@ hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCal
   if (blocks < 1) blocks = 1;
   if (blocks > HL_MAX_BLOCKS) blocks = HL_MAX_BLOCKS;
   dim3 grid((unsigned)blocks, (unsigned)(emu_ranks > 1 ? emu_ranks : 1), 1);
-  dim3 block(HL_NVL_THREADS, 1, 1);
+  const bool pipe = kind >= kNvlAllReducePipeP2p && kind <= kNvlReduceScatterPipeNvls;
+  dim3 block(pipe ? dev::kPipeThreads : HL_NVL_THREADS, 1, 1);
   void* args[2] = {(void*)&dcomms, (void*)&calls};
   cudaError_t e;
   if (emu_ranks > 1) {

@@ -115,6 +115,7 @@ class PcieImpl {
                     size_t seg_count, size_t stride, int send_segs, int recv_segs, hlDataType_t t, hlRedOp_t op,
                     float scale, int root, hlStream_t stream);
   hlResult_t drain();
+  void drainHostSide() { (void)drain(); }
   hlResult_t lastResult() const { return (hlResult_t)last_result_.load(); }
   uint64_t kernelLaunches() const { return kernel_launches_.load(); }
   uint64_t copyOps() const { return copy_ops_.load(); }
@@ -825,7 +826,18 @@ hlResult_t PcieImpl::runWork(const Work& w) {
 }
 
 // ====================================================================== facade
-PciePath::~PciePath() { delete impl_; }
+namespace {
+std::mutex g_reg_mu;
+std::vector<PcieImpl*> g_registry;
+}  // namespace
+
+PciePath::~PciePath() {
+  {
+    std::lock_guard<std::mutex> lk(g_reg_mu);
+    g_registry.erase(std::remove(g_registry.begin(), g_registry.end(), impl_), g_registry.end());
+  }
+  delete impl_;
+}
 
 size_t PciePath::ctrlBytes(int) { return (sizeof(SharedArea) + 4095) & ~(size_t)4095; }
 
@@ -833,6 +845,10 @@ hlResult_t PciePath::create(Bootstrap* bs, int device, void* ctrl_area, PciePath
   std::unique_ptr<PciePath> p(new PciePath());
   p->impl_ = new PcieImpl(bs, device, ctrl_area);
   HL_CHECK(p->impl_->init());
+  {
+    std::lock_guard<std::mutex> lk(g_reg_mu);
+    g_registry.push_back(p->impl_);
+  }
   *out = p.release();
   return hlSuccess;
 }
@@ -865,3 +881,14 @@ uint64_t PciePath::copyOps() const { return impl_->copyOps(); }
 const std::vector<int>& PciePath::rankNuma() const { return impl_->rankNuma(); }
 
 }  // namespace hl
+
+// Blocks until every executor of the process is idle (used by the interposers
+// of host-blocking CUDA calls).
+extern "C" void hlDrainAllExecutors(void) {
+  std::vector<hl::PcieImpl*> snapshot;
+  {
+    std::lock_guard<std::mutex> lk(hl::g_reg_mu);
+    snapshot = hl::g_registry;
+  }
+  for (auto* e : snapshot) e->drainHostSide();
+}
