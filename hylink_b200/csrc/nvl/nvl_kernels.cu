@@ -328,53 +328,81 @@ __device__ __forceinline__ void tileWait(const HlCommDev& c, int kind, uint64_t 
   }
 }
 
-// Warp split A / B / C. Through the switch a rank receives only 1/n of the
-// message, so few warps keep the link busy and the HBM copies get the rest;
-// peer pulls need (n-1)/n of the message in flight and get half of the CTA.
+// Warp split A / B / C (four warps each).
 template <bool kNvls> struct PipeShape {
-  static constexpr int A = kNvls ? 5 : 4, B = kNvls ? 2 : 4, C = kNvls ? 5 : 4;
+  static constexpr int A = 4, B = 4, C = 4;
 };
 constexpr int kPipeCopyUnroll = 4;
+constexpr int kPipeNvlsUnroll = 8;  // 16-byte multimem.ld_reduce in flight per exchange thread
 constexpr int kPipeThreads = 384;  // 12 warps: leaves ~170 registers per thread for the deep unrolls
 
-// Exchange stage over peer pointers with the rank count known at compile
-// time: U packets x NR peers of 16-byte loads are in flight per thread.
-template <typename W, int NR, int U, bool kAllReduce>
-__device__ __forceinline__ void pullReduceTile(const HlCommDev& c, const HlCallArgs& a, uint64_t first, uint64_t res_off,
-                                               uint64_t p0, uint64_t tp, const Ctx& x) {
+// Peer-pointer variant: every access that crosses NVLink is a posted STORE.
+// A remote load stalls its thread for a full round trip through the switch
+// (several microseconds under load), so a pull design needs megabytes in
+// flight; pushes are fire-and-forget until the fence before the flag. Stage A
+// therefore pushes, straight from the caller's buffer, the tile of every
+// shard into slot `rank` of that shard's owner (no local staging copy at
+// all); stage B folds the owner's own tile (read from the caller's buffer)
+// with the landed slots — all local reads, ascending rank order — and pushes
+// the result to every peer's result area (its own part goes directly to the
+// caller's output); stage C copies the other owners' results out locally.
+template <typename S, typename W>
+__device__ __forceinline__ void pushTile(uint4* remote_slot, const S* src, uint64_t cnt, const Ctx& x) {
   constexpr int N = Packet<W>::N;
-  const bool vec = aligned16(a.out);
-  for (uint64_t i = x.g0; i < tp; i += x.gstride * U) {
-    uint4 v[U][NR];
+  const uint64_t np = (cnt + N - 1) / N;
+  const bool vec = aligned16(src);
+  for (uint64_t i = x.g0; i < np; i += x.gstride * kPipeCopyUnroll) {
+    uint4 v[kPipeCopyUnroll];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < kPipeCopyUnroll; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
-      if (j < tp) {
-#pragma unroll
-        for (int q = 0; q < NR; ++q) v[u][q] = reinterpret_cast<const uint4*>(c.stage[q])[first + j];
-      }
+      if (j < np) v[u] = loadUserPacket<S, W>(src, j * N, cnt, vec);
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < kPipeCopyUnroll; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
-      if (j < tp) {
-        typename Wire<W>::Acc acc[N], b[N];
-        Packet<W>::unpack(v[u][0], acc);
+      if (j < np) remote_slot[j] = v[u];
+    }
+  }
+}
+
+template <typename S, typename W, typename D, bool kAllReduce>
+__device__ __forceinline__ void foldTile(const HlCommDev& c, const HlCallArgs& a, const S* own, uint64_t own_cnt, D* out,
+                                         uint64_t out_cnt, uint64_t sp, uint64_t p0, uint64_t tp, uint64_t res_off, const Ctx& x) {
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const uint4* slots = reinterpret_cast<const uint4*>(c.stage[r]);
+  const bool vin = aligned16(own), vout = aligned16(out);
+  for (uint64_t i = x.g0; i < tp; i += x.gstride * 2) {
+    const uint64_t j = i + x.gstride;
+    const bool two = j < tp;
+    uint4 v0[HL_MAX_RANKS], v1[HL_MAX_RANKS];
 #pragma unroll
-        for (int q = 1; q < NR; ++q) {
-          Packet<W>::unpack(v[u][q], b);
-#pragma unroll
-          for (int e = 0; e < N; ++e) acc[e] = applyOp(a.op, acc[e], b[e]);
-        }
-        finish<W>(acc, a.scale, a.int_div);
-        const uint4 red = Packet<W>::pack(acc);
-        if constexpr (kAllReduce) {
-#pragma unroll
-          for (int q = 0; q < NR; ++q) reinterpret_cast<uint4*>(c.stage[q])[res_off + first + j] = red;
+    for (int q = 0; q < HL_MAX_RANKS; ++q)
+      if (q < n) {
+        if (q == r) {
+          v0[q] = loadUserPacket<S, W>(own, i * N, own_cnt, vin);
+          if (two) v1[q] = loadUserPacket<S, W>(own, j * N, own_cnt, vin);
         } else {
-          HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + j) * N, a.count, vec, red));
+          v0[q] = slots[(uint64_t)q * sp + p0 + i];
+          if (two) v1[q] = slots[(uint64_t)q * sp + p0 + j];
         }
       }
+    const uint4 r0 = reducePackets<W>(v0, n, a.op, a.scale, a.int_div);
+    storeUserPacket<W, D>(out, i * N, out_cnt, vout, r0);
+    uint4 r1 = r0;
+    if (two) {
+      r1 = reducePackets<W>(v1, n, a.op, a.scale, a.int_div);
+      storeUserPacket<W, D>(out, j * N, out_cnt, vout, r1);
+    }
+    if constexpr (kAllReduce) {
+#pragma unroll
+      for (int q = 0; q < HL_MAX_RANKS; ++q)
+        if (q < n && q != r) {
+          uint4* dst = reinterpret_cast<uint4*>(c.stage[q]) + res_off + (uint64_t)r * sp + p0;
+          dst[i] = r0;
+          if (two) dst[j] = r1;
+        }
     }
   }
 }
@@ -413,18 +441,23 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
     const uint64_t p0 = t * tps;                                   // first packet of the tile inside a shard
     const uint64_t tp = sp - p0 < tps ? sp - p0 : tps;             // packets of this tile inside a shard
     if (role == 0) {
-      for (int s = 0; s < n; ++s) {
+      for (int k2 = 0; k2 < n; ++k2) {
+        const int s = kNvls ? k2 : (r + 1 + k2) % n;               // pushes start at the next rank to spread the load
         // elements of shard / segment s that fall into this tile
         uint64_t e0 = p0 * N, cnt;
         if constexpr (kAllReduce) {
           const uint64_t g0e = (uint64_t)s * in_stride + e0;       // global element index
           cnt = g0e >= a.count ? 0 : (a.count - g0e < tp * N ? a.count - g0e : tp * N);
-          const uint64_t shard_left = sp * N - e0;                 // never run into the next shard
-          if (cnt > shard_left) cnt = shard_left;
         } else {
           cnt = e0 >= seg_elems ? 0 : (seg_elems - e0 < tp * N ? seg_elems - e0 : tp * N);
         }
-        copyInAny<W, false, kPipeCopyUnroll>(mine + (uint64_t)s * sp + p0, a.in, a.in_dt, (uint64_t)s * in_stride + e0, cnt, x);
+        if constexpr (kNvls) {
+          copyInAny<W, false, kPipeCopyUnroll>(mine + (uint64_t)s * sp + p0, a.in, a.in_dt, (uint64_t)s * in_stride + e0, cnt, x);
+        } else {
+          if (s == r) continue;                                    // the owner reads its own tile from the caller's buffer
+          uint4* slot = reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp + p0;
+          pushTile<W, W>(slot, reinterpret_cast<const W*>(a.in) + (uint64_t)s * in_stride + e0, cnt, x);
+        }
       }
       groupSync(1, gthreads);
       tileSignal(c, 1, target, gtid);
@@ -435,15 +468,15 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
       const uint64_t first = (uint64_t)r * sp + p0;
       if constexpr (kNvls) {
         uint4* mc = reinterpret_cast<uint4*>(c.mc_stage) + first;
-        for (uint64_t i = x.g0; i < tp; i += x.gstride * kUnroll) {
-          uint4 v[kUnroll];
+        for (uint64_t i = x.g0; i < tp; i += x.gstride * kPipeNvlsUnroll) {
+          uint4 v[kPipeNvlsUnroll];
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
+          for (int u = 0; u < kPipeNvlsUnroll; ++u) {
             const uint64_t j = i + (uint64_t)u * x.gstride;
             if (j < tp) v[u] = multimemLdReduceAdd<W>(mc + j);
           }
 #pragma unroll
-          for (int u = 0; u < kUnroll; ++u) {
+          for (int u = 0; u < kPipeNvlsUnroll; ++u) {
             const uint64_t j = i + (uint64_t)u * x.gstride;
             if (j < tp) {
               if (a.scale != 1.0f) {
@@ -461,27 +494,23 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
           }
         }
       } else {
-        switch (n) {
-          case 2: pullReduceTile<W, 2, 4, kAllReduce>(c, a, first, res_off, p0, tp, x); break;
-          case 4: pullReduceTile<W, 4, 2, kAllReduce>(c, a, first, res_off, p0, tp, x); break;
-          case 8: pullReduceTile<W, 8, 1, kAllReduce>(c, a, first, res_off, p0, tp, x); break;
-          default:
-            for (uint64_t i = x.g0; i < tp; i += x.gstride) {
-              uint4 v[HL_MAX_RANKS];
-#pragma unroll
-              for (int q = 0; q < HL_MAX_RANKS; ++q)
-                if (q < n) v[q] = reinterpret_cast<const uint4*>(c.stage[q])[first + i];
-              const uint4 red = reducePackets<W>(v, n, a.op, a.scale, a.int_div);
-              if constexpr (kAllReduce) {
-#pragma unroll
-                for (int q = 0; q < HL_MAX_RANKS; ++q)
-                  if (q < n) reinterpret_cast<uint4*>(c.stage[q])[res_off + first + i] = red;
-              } else {
-                HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), (p0 + i) * N, a.count, aligned16(a.out), red));
-              }
-            }
-            break;
+        const uint64_t e0 = p0 * N;
+        const uint64_t own_first = (uint64_t)r * in_stride + e0;   // element index of the owned tile in the input
+        uint64_t own_cnt, out_first, out_cnt;
+        if constexpr (kAllReduce) {
+          own_cnt = own_first >= a.count ? 0 : (a.count - own_first < tp * N ? a.count - own_first : tp * N);
+          out_first = own_first;
+          out_cnt = own_cnt;
+        } else {
+          own_cnt = e0 >= seg_elems ? 0 : (seg_elems - e0 < tp * N ? seg_elems - e0 : tp * N);
+          out_first = e0;
+          out_cnt = own_cnt;
         }
+        const uint64_t tpk = (own_cnt + N - 1) / N;                // packets that hold valid elements
+        // the push variant moves the caller's element type unchanged (the host side
+        // routes converting calls to the staged kernels)
+        foldTile<W, W, W, kAllReduce>(c, a, reinterpret_cast<const W*>(a.in) + own_first, own_cnt,
+                                      reinterpret_cast<W*>(a.out) + out_first, out_cnt, sp, p0, tpk, res_off, x);
       }
       if constexpr (kAllReduce) {
         groupSync(2, gthreads);
@@ -493,6 +522,7 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
         groupSync(3, gthreads);
         if (s_abort) break;
         for (int s = 0; s < n; ++s) {
+          if (!kNvls && s == r) continue;                          // written by the exchange stage already
           const uint64_t e0 = p0 * N;
           const uint64_t g0e = (uint64_t)s * in_stride + e0;
           uint64_t cnt = g0e >= a.count ? 0 : (a.count - g0e < tp * N ? a.count - g0e : tp * N);

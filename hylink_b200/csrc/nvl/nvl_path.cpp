@@ -257,8 +257,11 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   int kind;
   if (algo == hlAlgoOneShot) kind = kNvlAllReduceOneShot;
   else if (algo == hlAlgoNvls) kind = kNvlAllReduceNvls;
-  else if (algo == hlAlgoPipelined) kind = (nvlsUsable(c.wire_dt, c.op, c.deterministic) && nvlsPays()) ? kNvlAllReducePipeNvls : kNvlAllReducePipeP2p;
-  else kind = kNvlAllReduceTwoShot;
+  else if (algo == hlAlgoPipelined) {
+    const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;  // the push kernel does not convert
+    if (nvlsUsable(c.wire_dt, c.op, c.deterministic) && nvlsPays()) kind = kNvlAllReducePipeNvls;
+    else kind = same ? kNvlAllReducePipeP2p : kNvlAllReduceTwoShot;
+  } else kind = kNvlAllReduceTwoShot;
   return launchSliced(kind, b, c, false, s);
 }
 
@@ -269,7 +272,8 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
                     (c.algo == hlAlgoNvls || nvlsPays());
   const bool pipe = c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().pipe_min_bytes);
   int kind = nvls ? kNvlReduceScatterNvls : kNvlReduceScatter;
-  if (pipe) kind = nvls ? kNvlReduceScatterPipeNvls : kNvlReduceScatterPipeP2p;
+  const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
+  if (pipe && (nvls || same)) kind = nvls ? kNvlReduceScatterPipeNvls : kNvlReduceScatterPipeP2p;
   return launchSliced(kind, b, c, true, s);
 }
 
