@@ -99,17 +99,18 @@ def build_nccl_shim(verbose: bool = False) -> Path | None:
     hdr = _newest_header()
     out = None
     plan = [("nccl_shim.cpp", "libhylink_nccl.so", ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static"]),
-            ("cuda_block_shim.cpp", "libhylink_cudashim.so", [])]
+            ("cuda_block_shim.cpp", "libhylink_cudashim.so", []),
+            ("../tools/nccl_trace.cpp", "libhylink_nccltrace.so", ["-L", str(CUDA_HOME / "lib64"), "-lcudart_static"])]
     for src_name, lib_name, extra in plan:
-        src = CSRC / "api" / src_name
+        src = (CSRC / "api" / src_name).resolve()
         if not src.exists():
             continue
-        obj = OBJ / ("shim_" + src_name + ".o")
+        obj = OBJ / ("shim_" + Path(src_name).name + ".o")
         changed = _compile(src, obj, hdr, [])
         target = LIB / lib_name
         if changed or not target.exists():
-            _run(["g++", "-shared", "-o", str(target), str(obj), "-L", str(LIB), "-lhylink_b200", "-Wl,-rpath,$ORIGIN",
-                  *extra, "-lpthread", "-ldl", "-lrt"])
+            core = [] if "nccltrace" in lib_name else ["-L", str(LIB), "-lhylink_b200", "-Wl,-rpath,$ORIGIN"]
+            _run(["g++", "-shared", "-o", str(target), str(obj), *core, *extra, "-lpthread", "-ldl", "-lrt"])
             if verbose:
                 print("linked", target)
         out = out or target

@@ -68,7 +68,8 @@ typedef enum {
   hlAlgoOneShot = 1,     /* every rank reads all peers, one barrier pair */
   hlAlgoTwoShotP2p = 2,  /* pull-reduce of the owned shard, pull all-gather; fixed sum order */
   hlAlgoNvls = 3,        /* multimem.ld_reduce + multimem.st through NVSwitch */
-  hlAlgoPipelined = 4    /* warp-specialised tiles: copy-in, link exchange and copy-out overlap */
+  hlAlgoPipelined = 4,   /* warp-specialised tiles: copy-in, link exchange and copy-out overlap */
+  hlAlgoPush = 5         /* peer stores only: push shards to their owner, fold locally, push results */
 } hlAlgo_t;
 
 #define HL_UNIQUE_ID_BYTES 128

@@ -211,7 +211,9 @@ __device__ __forceinline__ bool blockBarrier(const HlCommDev& c, uint64_t target
   __syncthreads();  // also orders every thread's earlier accesses before the signal below
   const int t = threadIdx.x;
   if (t < c.nranks) {
-    __threadfence_system();
+    // st.release.sys orders this thread's earlier accesses — and, through the
+    // bar.sync above, those of the whole CTA — before the flag; no separate
+    // (sequentially consistent) fence is needed.
     uint64_t* remote = c.flags[t] + (size_t)blockIdx.x * HL_MAX_RANKS + c.rank;
     stReleaseSys(remote, target);
     const uint64_t* mine = c.flags[c.rank] + (size_t)blockIdx.x * HL_MAX_RANKS + t;

@@ -295,7 +295,6 @@ __device__ __forceinline__ void groupSync(int id, int threads) {
 
 __device__ __forceinline__ void tileSignal(const HlCommDev& c, int kind, uint64_t value, int gtid) {
   if (gtid < c.nranks) {
-    __threadfence_system();
     stReleaseSys(c.flags[gtid] + ((size_t)kind * HL_MAX_BLOCKS + blockIdx.x) * HL_MAX_RANKS + c.rank, value);
   }
 }
@@ -540,6 +539,59 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
   }
 }
 
+// ------------------------------------------------------------------ push all-reduce / reduce-scatter over peer pointers
+// Every NVLink access is a posted store and every load is local:
+//   1. push: each rank streams, straight from the caller's buffer, shard s of
+//      its input into slot `rank` of shard s's owner (nothing is staged locally);
+//   barrier
+//   2. fold: the owner adds its own shard (read from the caller's buffer) and
+//      the n-1 landed slots in ascending rank order, writes its part of the
+//      result to the caller's output and (all-reduce) pushes it into every
+//      peer's result area;
+//   barrier
+//   3. (all-reduce) copy the other owners' results from the local result area
+//      to the caller's output.
+// All 512 threads of every CTA work in every phase, so each phase has the
+// whole grid's loads and stores in flight. The caller's element type is the
+// wire type (converting calls use the staged kernels).
+template <typename W, bool kAllReduce>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kPush(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  const HlCallArgs& a = calls.c[blockIdx.y];
+  if (!entryOk(c)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t np = (a.count + N - 1) / N;
+  const uint64_t sp = kAllReduce ? (np + n - 1) / n : np;
+  const uint64_t in_stride = kAllReduce ? sp * N : a.in_seg_stride;
+  const uint64_t res_off = sp * (uint64_t)n;
+  const W* in = reinterpret_cast<const W*>(a.in);
+  W* out = reinterpret_cast<W*>(a.out);
+  auto shardElems = [&](int s) -> uint64_t {
+    if constexpr (kAllReduce) return segElems(a.count, (uint64_t)s * sp * N, sp * N);
+    else return a.count;
+  };
+  for (int k = 1; k < n; ++k) {
+    const int s = (r + k) % n;
+    pushTile<W, W>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp, in + (uint64_t)s * in_stride, shardElems(s), x);
+  }
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  {
+    const uint64_t cnt = shardElems(r);
+    const uint64_t first = kAllReduce ? (uint64_t)r * sp * N : 0;
+    foldTile<W, W, W, kAllReduce>(c, a, in + (uint64_t)r * in_stride, cnt, out + first, cnt, sp, 0, (cnt + N - 1) / N, res_off, x);
+  }
+  if (!blockBarrier(c, a.seq + 2, 2)) return;
+  if constexpr (kAllReduce) {
+    const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
+    for (int k = 1; k < n; ++k) {
+      const int s = (r + k) % n;
+      segCopyOut<W, W>(out + (uint64_t)s * sp * N, mine + res_off + (uint64_t)s * sp, shardElems(s), x);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ reduce-scatter
 // `in` holds n segments (stride in_seg_stride); the first `count` elements of
 // each are handled. copy-in | barrier | pull-reduce segment r from every peer
@@ -702,6 +754,8 @@ static const void* pickKernelT(int kind) {
     case kNvlAllToAll: return (const void*)kAllToAll<W>;
     case kNvlAllGatherNvls: return (const void*)kAllGather<W, true>;
     case kNvlBroadcastNvls: return (const void*)kBroadcast<W, true>;
+    case kNvlAllReducePush: return (const void*)kPush<W, true>;
+    case kNvlReduceScatterPush: return (const void*)kPush<W, false>;
     case kNvlAllReducePipeP2p: return (const void*)kPipelined<W, false, true>;
     case kNvlReduceScatterPipeP2p: return (const void*)kPipelined<W, false, false>;
     default: break;
@@ -748,6 +802,8 @@ const char* kernelName(int kind) {
     case kNvlAllToAll: return "alltoall_p2p";
     case kNvlAllGatherNvls: return "allgather_nvls";
     case kNvlBroadcastNvls: return "broadcast_nvls";
+    case kNvlAllReducePush: return "allreduce_push";
+    case kNvlReduceScatterPush: return "reducescatter_push";
     case kNvlAllReducePipeP2p: return "allreduce_pipelined_p2p";
     case kNvlAllReducePipeNvls: return "allreduce_pipelined_nvls";
     case kNvlReduceScatterPipeP2p: return "reducescatter_pipelined_p2p";
@@ -786,7 +842,8 @@ hlResult_t prepareKernels() {
   static const int kinds[] = {kNvlBarrier, kNvlAllReduceOneShot, kNvlAllReduceTwoShot, kNvlAllReduceNvls,
                               kNvlReduceScatter, kNvlReduceScatterNvls, kNvlAllGather, kNvlBroadcast,
                               kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls, kNvlAllReducePipeP2p,
-                              kNvlAllReducePipeNvls, kNvlReduceScatterPipeP2p, kNvlReduceScatterPipeNvls};
+                              kNvlAllReducePipeNvls, kNvlReduceScatterPipeP2p, kNvlReduceScatterPipeNvls, kNvlAllReducePush,
+                              kNvlReduceScatterPush};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
       const void* fn = kernelFor(k, dt);

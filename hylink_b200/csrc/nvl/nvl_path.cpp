@@ -157,8 +157,8 @@ int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool dete
   if (requested == hlAlgoNvls && !nvls_ok) requested = hlAlgoAuto;
   if (requested != hlAlgoAuto) return requested;
   if (wire_bytes <= Config::get().oneshot_max_bytes) return hlAlgoOneShot;
-  if (wire_bytes >= Config::get().pipe_min_bytes) return hlAlgoPipelined;
-  return (nvls_ok && nvlsPays()) ? hlAlgoNvls : hlAlgoTwoShotP2p;
+  if (nvls_ok && nvlsPays()) return wire_bytes >= Config::get().pipe_min_bytes ? hlAlgoPipelined : hlAlgoNvls;
+  return hlAlgoPush;  // peer pointers: stores only (falls back to the staged two-shot when the call converts types)
 }
 
 int NvlPath::blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const {
@@ -194,9 +194,9 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
   const bool pipe = kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePipeNvls || kind == kNvlReduceScatterPipeP2p ||
                     kind == kNvlReduceScatterPipeNvls;
   const bool pipe_ar = kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePipeNvls;
-  if (segmented || kind == kNvlAllReduceTwoShot || kind == kNvlAllReduceNvls || pipe_ar) {
+  if (segmented || kind == kNvlAllReduceTwoShot || kind == kNvlAllReduceNvls || pipe_ar || kind == kNvlAllReducePush) {
     // the P2P pipelined all-reduce keeps inputs and results in separate halves of the staging region
-    const uint64_t regions = kind == kNvlAllReducePipeP2p ? 2 : 1;
+    const uint64_t regions = (kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePush) ? 2 : 1;
     uint64_t sp = (cap_packets / ((uint64_t)nranks_ * regions)) & ~(uint64_t)63;
     if (sp == 0) return fail(hlInvalidArgument, "staging region too small");
     per_launch = (segmented ? sp : sp * (uint64_t)nranks_) * epp;
@@ -254,11 +254,12 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
   int algo = pickAllReduceAlgo(wire_bytes, c.wire_dt, c.op, c.deterministic, c.algo);
   if (algo == hlAlgoOneShot && wire_bytes > stage_bytes_) algo = hlAlgoTwoShotP2p;
+  const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;  // the push kernels do not convert
   int kind;
   if (algo == hlAlgoOneShot) kind = kNvlAllReduceOneShot;
   else if (algo == hlAlgoNvls) kind = kNvlAllReduceNvls;
+  else if (algo == hlAlgoPush) kind = same ? kNvlAllReducePush : kNvlAllReduceTwoShot;
   else if (algo == hlAlgoPipelined) {
-    const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;  // the push kernel does not convert
     if (nvlsUsable(c.wire_dt, c.op, c.deterministic) && nvlsPays()) kind = kNvlAllReducePipeNvls;
     else kind = same ? kNvlAllReducePipeP2p : kNvlAllReduceTwoShot;
   } else kind = kNvlAllReduceTwoShot;
@@ -270,10 +271,13 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
   const bool nvls = nvlsUsable(c.wire_dt, c.op, c.deterministic) && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot &&
                     (c.algo == hlAlgoNvls || nvlsPays());
-  const bool pipe = c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().pipe_min_bytes);
-  int kind = nvls ? kNvlReduceScatterNvls : kNvlReduceScatter;
   const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
-  if (pipe && (nvls || same)) kind = nvls ? kNvlReduceScatterPipeNvls : kNvlReduceScatterPipeP2p;
+  int kind = nvls ? kNvlReduceScatterNvls : kNvlReduceScatter;
+  if (nvls) {
+    if (c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().pipe_min_bytes)) kind = kNvlReduceScatterPipeNvls;
+  } else if (same && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot) {
+    kind = c.algo == hlAlgoPipelined ? kNvlReduceScatterPipeP2p : kNvlReduceScatterPush;
+  }
   return launchSliced(kind, b, c, true, s);
 }
 

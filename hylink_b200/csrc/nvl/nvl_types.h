@@ -73,4 +73,6 @@ enum HlNvlKernel {
   kNvlAllReducePipeNvls = 12,
   kNvlReduceScatterPipeP2p = 13,
   kNvlReduceScatterPipeNvls = 14,
+  kNvlAllReducePush = 15,
+  kNvlReduceScatterPush = 16,
 };

@@ -11,7 +11,7 @@ import ctypes as C
 from .._native import CallOpts, CommStats, OPS, UniqueId, check, lib, torch_dtype_code
 
 PATHS = {"auto": 0, "nvlink": 1, "pcie": 2, "split": 3}
-ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4}
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5}
 
 
 def unique_id() -> bytes:

@@ -276,3 +276,31 @@ def test_pipelined_wait_is_bounded():
     torch.cuda.synchronize()
     assert torch.equal(outs[0], ins[0] + ins[1])
     g.close()
+
+
+@pytest.mark.parametrize("n", [2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+def test_push_allreduce_bitwise(n, dtype):
+    """Stores-only peer kernel: shards pushed to their owner, folded locally, results pushed back."""
+    g = _group(n, stage_bytes=32 << 20)
+    for count in [1, 17, 4099, 300001, (1 << 20) + 7]:
+        ins = [_rand(count, dtype, 11 * r + count % 83) for r in range(n)]
+        outs = [torch.full((count + 8,), 3, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("all_reduce", ins, [o[:count] for o in outs], count, algo="push")
+        torch.cuda.synchronize()
+        acc = torch.float32 if dtype.is_floating_point else dtype
+        ref = _ordered_sum(ins, acc).to(dtype)
+        for r in range(n):
+            assert torch.equal(outs[r][:count], ref), (n, dtype, count, r)
+            assert torch.all(outs[r][count:] == 3)
+    # in place, back to back, sliced over a small staging region
+    g2 = _group(n, stage_bytes=2 << 20)
+    for it in range(3):
+        bufs = [_rand(700001, torch.float32, 5 * it + r) for r in range(n)]
+        ref = _ordered_sum([b.clone() for b in bufs], torch.float32)
+        g2.run("all_reduce", bufs, bufs, 700001, algo="push")
+        torch.cuda.synchronize()
+        for b in bufs:
+            assert torch.equal(b, ref)
+    g.close()
+    g2.close()
