@@ -114,4 +114,4 @@ def smoke_step() -> float:
     torch.cuda.synchronize()
     assert torch.equal(outs[0], ((flat.float() + flat.float()) * 0.5).to(torch.bfloat16))
     g.close()
-    return float(loss)
+    return float(loss.detach())
