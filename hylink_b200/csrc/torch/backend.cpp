@@ -251,6 +251,7 @@ class HylinkBackend : public c10d::Backend {
       hlCheck(hlAllGather(in.data_ptr(), flat.data_ptr(), (size_t)in.numel(), toHl(in.scalar_type()), c, s), "allgather");
       c10::OptionalStreamGuard sg;
       if (in.is_cuda()) sg.reset_stream(*comm_stream_);
+      else hlCheck(hlCommDrain(c), "hlCommDrain");  // host path: the gather must have landed before it is split up
       for (int q = 0; q < getSize(); ++q) dst[q].copy_(flat.narrow(0, (int64_t)q * in.numel(), in.numel()).view_as(dst[q]), true);
     });
   }
