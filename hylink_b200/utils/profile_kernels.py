@@ -1,0 +1,68 @@
+"""A small single-GPU workload for profilers: each collective kernel once or twice.
+
+    python -m hylink_b200.utils.profile_kernels [--ranks 4] [--mib 48]
+
+Runs, on ONE device: the two-shot pull all-reduce, the push all-reduce, the
+pipelined all-reduce, the push reduce-scatter and the all-gather with `--ranks`
+emulated ranks (one cooperative launch each; `--mib` MiB of bf16 per rank, so
+the working set is larger than the 126 MB L2 while staying within a few
+hundred MB), and the landing-reduce kernel over four 128 MiB sources. Prints the
+CUDA-event time of every launch and the HBM traffic it implies. Meant to be run
+plainly first and then under ``ncu -k regex:... -c N --clock-control none``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--ranks", type=int, default=4)
+    ap.add_argument("--mib", type=int, default=48)
+    ap.add_argument("--reps", type=int, default=2)
+    a = ap.parse_args(argv)
+    from hylink_b200.ops import EmuGroup, reduce_landing
+
+    torch.cuda.set_device(0)
+    n, count = a.ranks, a.mib * (1 << 20) // 2
+    g = EmuGroup(n, stage_bytes=2 * a.mib << 20, timeout_ms=5000)
+    ins = [torch.randn(count, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    outs = [torch.empty_like(t) for t in ins]
+    seg = count // n
+    gathered = [torch.empty(count, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    results = []
+
+    def timed(name, fn, bytes_moved):
+        fn()  # warm-up
+        torch.cuda.synchronize()
+        for _ in range(a.reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            results.append({"kernel": name, "ms": round(ms, 4), "hbm_GBs": round(bytes_moved / ms / 1e6, 1)})
+
+    nb = count * 2
+    # HBM bytes per launch, all emulated ranks together (reads + writes of every phase)
+    timed("allreduce_twoshot_pull", lambda: g.run("all_reduce", ins, outs, count, algo="twoshot"), n * nb * (2 + 1 + 1.0 / n + 1 + 1))
+    timed("allreduce_push", lambda: g.run("all_reduce", ins, outs, count, algo="push"), n * nb * (2.0 * (n - 1) / n + 1 + 2.0 / n + 2.0 * (n - 1) / n + 2.0 * (n - 1) / n))
+    timed("allreduce_pipelined_push", lambda: g.run("all_reduce", ins, outs, count, algo="pipelined"), n * nb * (2.0 * (n - 1) / n + 1 + 2.0 / n + 2.0 * (n - 1) / n + 2.0 * (n - 1) / n))
+    timed("reducescatter_push", lambda: g.run("reduce_scatter", ins, [o[:seg] for o in outs], seg, in_seg_stride=seg),
+          n * nb * (2.0 * (n - 1) / n + 1 + 1.0 / n))
+    timed("allgather_pull", lambda: g.run("all_gather", [t[:seg] for t in ins], gathered, seg, out_seg_stride=seg), n * (2 * seg * 2 + 2 * count * 2))
+    srcs = [torch.randn(64 << 20, device="cuda").to(torch.bfloat16) for _ in range(4)]
+    dst = torch.empty_like(srcs[0])
+    timed("reduce_landing_4way", lambda: reduce_landing(dst, srcs), 5 * srcs[0].numel() * 2)
+    g.close()
+    for r in results:
+        print(json.dumps(r), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
