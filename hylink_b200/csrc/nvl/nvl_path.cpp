@@ -226,10 +226,14 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
     const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls ? nranks_ : 1);
     int blocks = blocksFor(kind, wire_bytes, c.max_blocks);
     if (pipe) {
-      // tiles: up to 2048 packets (32 KiB) of every shard, at least four tiles per CTA so the stages overlap
+      // Tiles: as large as possible (every tile costs two flag round trips) while each CTA still gets
+      // about eight of them, evenly, so that its three stages overlap: measured on 8 GPUs, 1 GiB moves at
+      // 728 GB/s with 8192-packet tiles against 669 GB/s with 2048, while 256 MiB drops to 548 GB/s when
+      // 8192-packet tiles leave fewer than two tiles per CTA.
       const uint64_t np = (len + epp - 1) / epp;
       const uint64_t sp = pipe_ar ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;
-      uint64_t tps = std::min<uint64_t>(2048, std::max<uint64_t>(256, (sp / ((uint64_t)blocks * 4)) & ~(uint64_t)63));
+      uint64_t tps = (sp + (uint64_t)blocks * 8 - 1) / ((uint64_t)blocks * 8);
+      tps = std::min<uint64_t>(8192, std::max<uint64_t>(256, (tps + 63) & ~(uint64_t)63));
       const char* forced = getenv("HYLINK_PIPE_TILE_PACKETS");
       if (forced) tps = std::max<uint64_t>(64, (uint64_t)atoll(forced) & ~(uint64_t)63);
       const uint64_t tiles = (sp + tps - 1) / tps;

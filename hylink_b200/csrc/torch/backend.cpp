@@ -162,7 +162,9 @@ class HylinkBackend : public c10d::Backend {
     if (cuda) {
       device = t.device().index();
       cuda_device_ = device;
-      comm_stream_ = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/true, device));
+      // Normal priority by default: a high-priority collective grabs SMs ahead of the backward pass it overlaps with.
+      const char* hp = getenv("HYLINK_TORCH_HIGH_PRIORITY");
+      comm_stream_ = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/hp && atoi(hp) != 0, device));
     }
     hlCheck(hlCommInitRankDevice(&slot, getSize(), id, getRank(), device), "hlCommInitRankDevice");
     return slot;

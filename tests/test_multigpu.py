@@ -64,3 +64,8 @@ def test_nccl_symbol_layer_serves_an_unmodified_nccl_program():
     line = [l for l in out.splitlines() if l.startswith("NCCL_SHIM_CHECK")][-1]
     served = int(line.split("served=")[1].split()[0])
     assert served >= 7, line
+
+
+def test_deterministic_sum_order_against_host_oracles():
+    out = _torchrun(2, ["-m", "hylink_b200.utils.determinism", "--bytes-from", "256K", "--bytes-to", "16M"])
+    assert '"failures": 0' in out, out[-3000:]
