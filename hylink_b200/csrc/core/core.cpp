@@ -181,7 +181,8 @@ static Config* loadConfig() {
   c->nvls = (int)envInt({"HYLINK_NVLS"}, -1);
   c->symm_mode = envStr({"HYLINK_SYMM_MODE"}, "auto");
   c->oneshot_max_bytes = (size_t)envInt({"HYLINK_ONESHOT_MAX_BYTES"}, 128LL << 10);
-  c->pipe_min_bytes = (size_t)envInt({"HYLINK_PIPE_MIN_BYTES"}, 32LL << 20);
+  c->pipe_min_bytes = (size_t)envInt({"HYLINK_PIPE_MIN_BYTES"}, 0);
+  c->push_min_bytes = (size_t)envInt({"HYLINK_PUSH_MIN_BYTES"}, 32LL << 20);
   c->nvls_min_ranks = (int)envInt({"HYLINK_NVLS_MIN_RANKS"}, 4);
   c->nvl_max_blocks = (int)envInt({"HYLINK_NVL_MAX_BLOCKS"}, 0);
 

@@ -103,7 +103,8 @@ struct Config {
   int nvls;                      // -1 auto, 0 off, 1 require
   std::string symm_mode;         // auto | vmm | ipc
   size_t oneshot_max_bytes;
-  size_t pipe_min_bytes;         // from this size on the pipelined kernels are used
+  size_t pipe_min_bytes;         // from this size on the pipelined NVLS kernels are used (0 = by rank count)
+  size_t push_min_bytes;         // with NVLS available: from this size on the stores-only kernels are used
   int nvls_min_ranks;            // NVLS kernels are preferred from this rank count on
   int nvl_max_blocks;
   // --- orchestrator

@@ -144,10 +144,11 @@ hlResult_t hlAllToAllEx(const void* send, void* recv, size_t count_per_peer, hlD
 /* Device-side barrier over the NVLink flags (an 8-byte exchange). */
 hlResult_t hlBarrier(hlComm_t comm, hlStream_t stream);
 
-/* ---- symmetric memory -------------------------------------------------- */
-/* Memory that every rank of the communicator maps: collectives whose buffers
- * come from here skip the staging copies. Collective call (all ranks, same
- * sizes, same order). */
+/* ---- device memory ------------------------------------------------------ */
+/* Device memory tied to the communicator's device (host memory with the
+ * host-memory device). Collectives stage user buffers through the
+ * communicator's own symmetric region, so any device pointer works as an
+ * argument; this pair exists for NCCL-style callers that expect an allocator. */
 hlResult_t hlMemAlloc(hlComm_t comm, size_t bytes, void** ptr);
 hlResult_t hlMemFree(hlComm_t comm, void* ptr);
 

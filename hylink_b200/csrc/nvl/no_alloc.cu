@@ -21,7 +21,7 @@ constexpr int kMaxBlocks = 16;                                  // CTAs per buff
 constexpr size_t kTableBytes = 256;                             // one HlCommDev, padded
 constexpr size_t kTablesOff = 0;                                // [nranks 1..8][rank 0..7] pointer tables
 constexpr size_t kTablesBytes = kMaxRanks * kMaxRanks * kTableBytes;
-constexpr size_t kWordsOff = kTablesOff + kTablesBytes;         // per rank: status (64 B) + poison word (64 B)
+constexpr size_t kWordsOff = kTablesOff + kTablesBytes;         // per rank: status (64 B), poison word, sequence words
 constexpr size_t kWordsBytes = kMaxRanks * 128;
 constexpr size_t kFlagsOff = kWordsOff + kWordsBytes;           // per rank: kMaxBlocks x 8 flag words
 constexpr size_t kFlagsPerRank = (size_t)kMaxBlocks * HL_MAX_RANKS * sizeof(uint64_t);
@@ -66,6 +66,7 @@ hlResult_t setUp(int device, unsigned char** base_out) {
         c.mc_stage = nullptr;
         c.status = reinterpret_cast<uint64_t*>(ptr + kWordsOff + r * 128);
         c.abort_word = reinterpret_cast<uint32_t*>(ptr + kWordsOff + r * 128 + 64);
+        c.seq_words = reinterpret_cast<uint64_t*>(ptr + kWordsOff + r * 128 + 80);  // three words, cleared with the flags
         c.stage_bytes = kStagePerRank;
         c.timeout_ns = 2000000000ull;  // 2 s: generous for a 256 KiB reduction, still bounded
       }
@@ -113,7 +114,6 @@ extern "C" hlResult_t hlAllReduceLocalNoAlloc(int nranks, const void* const* ins
     a.in = ins[i];
     a.out = outs[i];
     a.count = count;
-    a.seq = 0;
     a.scale = op == hlAvg ? 1.0f / (float)nranks : 1.0f;
     a.op = op;
     a.in_dt = dtype;

@@ -192,13 +192,41 @@ __device__ __forceinline__ uint64_t globalTimerNs() {
   return t;
 }
 
-// Uniform entry test: a poisoned communicator (an earlier wait ran out) makes
-// every later kernel a no-op instead of a second hang candidate.
-__device__ __forceinline__ bool entryOk(const HlCommDev& c) {
+// Uniform entry: a poisoned communicator (an earlier wait ran out) makes every
+// later kernel a no-op instead of a second hang candidate. The call's flag
+// bases are read here from device memory rather than passed by the host, so a
+// launch carries no per-call counter and can be captured in a CUDA graph and
+// replayed: each replay picks up where the previous launch left off.
+__device__ __forceinline__ bool entryOk(const HlCommDev& c, HlCallArgs& a) {
   __shared__ int s_entry;
-  if (threadIdx.x == 0) s_entry = (*reinterpret_cast<volatile uint32_t*>(c.abort_word) == 0) ? 1 : 0;
+  __shared__ uint64_t s_seq[2];
+  if (threadIdx.x == 0) {
+    s_entry = (*reinterpret_cast<volatile uint32_t*>(c.abort_word) == 0) ? 1 : 0;
+    s_seq[0] = reinterpret_cast<volatile uint64_t*>(c.seq_words)[0];
+    s_seq[1] = reinterpret_cast<volatile uint64_t*>(c.seq_words)[1];
+  }
   __syncthreads();
+  a.seq = s_seq[0];
+  a.pipe_seq = s_seq[1];
   return s_entry != 0;
+}
+
+// Normal exit of a call: the last CTA to get here advances the bases for the
+// next launch. No CTA of this launch can still be about to read them: every
+// CTA reads at entry and counts itself here.
+__device__ __forceinline__ void callDone(const HlCommDev& c, uint64_t pipe_tiles) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned long long prev = atomicAdd(reinterpret_cast<unsigned long long*>(c.seq_words + 2), 1ull);
+    if (prev + 1 == gridDim.x) {
+      volatile uint64_t* w = c.seq_words;
+      w[2] = 0;
+      w[0] = w[0] + HL_SEQ_STRIDE;
+      w[1] = w[1] + pipe_tiles;
+      __threadfence();
+    }
+  }
 }
 
 // Cross-GPU barrier of block blockIdx.x with the same block of every peer.

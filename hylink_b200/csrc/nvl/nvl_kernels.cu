@@ -149,9 +149,10 @@ __device__ __forceinline__ uint64_t segElems(uint64_t count, uint64_t first, uin
 // ------------------------------------------------------------------ barrier
 __global__ void __launch_bounds__(HL_NVL_THREADS) kBarrier(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   blockBarrier(c, a.seq + 1, 1);
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ all-reduce, one-shot
@@ -160,8 +161,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kBarrier(const HlCommDev* comm
 template <typename W>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceOneShot(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks;
   const Ctx x = makeCtx();
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceOneShot(const HlComm
     HL_USER_TYPE_SWITCH(W, a.out_dt, D, storeUserPacket<W, D>(reinterpret_cast<D*>(a.out), i * N, a.count, vec, r));
   }
   blockBarrier(c, a.seq + 2, 2);
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ all-reduce, two-shot over P2P
@@ -187,8 +189,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceOneShot(const HlComm
 template <typename W>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceTwoShot(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const Ctx x = makeCtx();
@@ -221,6 +223,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceTwoShot(const HlComm
                   segElems(a.count, s * sp * N, sp * N), x);
   }
   blockBarrier(c, a.seq + 3, 3);
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ all-reduce through NVSwitch (NVLS)
@@ -230,8 +233,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceTwoShot(const HlComm
 template <typename W>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceNvls(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const Ctx x = makeCtx();
@@ -270,6 +273,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceNvls(const HlCommDev
   if (!blockBarrier(c, a.seq + 2, 2)) return;
   for (int s = 0; s < n; ++s)
     copyOutAny<W>(a.out, a.out_dt, s * sp * N, mine + s * sp, segElems(a.count, s * sp * N, sp * N), x);
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ pipelined all-reduce / reduce-scatter
@@ -409,8 +413,8 @@ __device__ __forceinline__ void foldTile(const HlCommDev& c, const HlCallArgs& a
 template <typename W, bool kNvls, bool kAllReduce>
 __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = 0;
   __syncthreads();
@@ -537,6 +541,7 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
     // the next call's copy-in before everybody is through
     blockBarrier(c, a.seq + 1, 3);
   }
+  callDone(c, (tiles + gridDim.x - 1) / gridDim.x);
 }
 
 // ------------------------------------------------------------------ push all-reduce / reduce-scatter over peer pointers
@@ -557,8 +562,8 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
 template <typename W, bool kAllReduce>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kPush(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const Ctx x = makeCtx();
@@ -590,6 +595,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPush(const HlCommDev* comms, 
       segCopyOut<W, W>(out + (uint64_t)s * sp * N, mine + res_off + (uint64_t)s * sp, shardElems(s), x);
     }
   }
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ reduce-scatter
@@ -599,8 +605,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPush(const HlCommDev* comms, 
 template <typename W, bool kNvls>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kReduceScatter(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const Ctx x = makeCtx();
@@ -653,6 +659,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kReduceScatter(const HlCommDev
     }
   }
   blockBarrier(c, a.seq + 2, 2);
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ all-gather
@@ -664,8 +671,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kReduceScatter(const HlCommDev
 template <typename W, bool kNvls>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kAllGather(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const Ctx x = makeCtx();
@@ -686,14 +693,15 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllGather(const HlCommDev* co
     }
     blockBarrier(c, a.seq + 2, 2);
   }
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ broadcast
 template <typename W, bool kNvls>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int r = c.rank;
   const Ctx x = makeCtx();
@@ -713,6 +721,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* co
       copyOutAny<W>(a.out, a.out_dt, 0, reinterpret_cast<const uint4*>(c.stage[a.root]), a.count, x);
     blockBarrier(c, a.seq + 2, 2);
   }
+  callDone(c, 0);
 }
 
 // ------------------------------------------------------------------ all-to-all
@@ -720,8 +729,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* co
 template <typename W>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kAllToAll(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
-  const HlCallArgs& a = calls.c[blockIdx.y];
-  if (!entryOk(c)) return;
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const Ctx x = makeCtx();
@@ -735,6 +744,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllToAll(const HlCommDev* com
                   a.count, x);
   }
   blockBarrier(c, a.seq + 2, 2);
+  callDone(c, 0);
 }
 
 }  // namespace dev

@@ -16,6 +16,7 @@ NvlPath::~NvlPath() {
   if (order_ev_) cudaEventDestroy(order_ev_);
   if (dcomm_) cudaFree(dcomm_);
   if (abort_dev_) cudaFree(abort_dev_);
+  if (seq_dev_) cudaFree(seq_dev_);
   if (status_host_) cudaFreeHost(status_host_);
   if (emu_) {
     for (int q = 0; q < nranks_; ++q)
@@ -35,6 +36,8 @@ hlResult_t NvlPath::finishInit(int timeout_ms) {
   HL_CUDA(cudaHostGetDevicePointer((void**)&status_dev, status_host_, 0));
   HL_CUDA(cudaMalloc((void**)&abort_dev_, sizeof(uint32_t) * 16 * nl));
   HL_CUDA(cudaMemset(abort_dev_, 0, sizeof(uint32_t) * 16 * nl));
+  HL_CUDA(cudaMalloc((void**)&seq_dev_, sizeof(uint64_t) * 8 * nl));
+  HL_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint64_t) * 8 * nl));
   HlCommDev h[HL_MAX_RANKS];
   memset(h, 0, sizeof(h));
   for (int i = 0; i < nl; ++i) {
@@ -50,6 +53,7 @@ hlResult_t NvlPath::finishInit(int timeout_ms) {
     c.mc_stage = emu_ ? nullptr : (uint8_t*)region_.mc;
     c.status = status_dev + 8 * i;
     c.abort_word = abort_dev_ + 16 * i;
+    c.seq_words = seq_dev_ + 8 * i;
     c.stage_bytes = stage_bytes_;
     c.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
   }
@@ -119,10 +123,9 @@ hlResult_t NvlPath::resetAfterError() {
     HL_CUDA(cudaMemset((uint8_t*)region_.ptr[rank_] + stage_bytes_, 0, flagAreaBytes()));
   }
   HL_CUDA(cudaMemset(abort_dev_, 0, sizeof(uint32_t) * 16 * nl));
+  HL_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint64_t) * 8 * nl));
   memset(status_host_, 0, sizeof(uint64_t) * 8 * nl);
   HL_CUDA(cudaDeviceSynchronize());
-  seq_ = 0;
-  pipe_seq_ = 0;
   if (!emu_ && bs_) HL_CHECK(bs_->barrier(kBarSymm));
   return hlSuccess;
 }
@@ -147,6 +150,12 @@ bool NvlPath::nvlsPays() const {
   return has_mc_ && nranks_ >= Config::get().nvls_min_ranks;
 }
 
+size_t NvlPath::pipeMinBytes() const {
+  const size_t forced = Config::get().pipe_min_bytes;
+  if (forced) return forced;
+  return nranks_ >= 8 ? ((size_t)256 << 20) : ((size_t)512 << 20);
+}
+
 bool NvlPath::nvlsUsable(int wire_dt, int op, bool deterministic) const {
   return has_mc_ && (wire_dt == hlFloat32 || wire_dt == hlFloat16 || wire_dt == hlBfloat16) && (op == hlSum || op == hlAvg) &&
          !deterministic;
@@ -157,7 +166,16 @@ int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool dete
   if (requested == hlAlgoNvls && !nvls_ok) requested = hlAlgoAuto;
   if (requested != hlAlgoAuto) return requested;
   if (wire_bytes <= Config::get().oneshot_max_bytes) return hlAlgoOneShot;
-  if (nvls_ok && nvlsPays()) return wire_bytes >= Config::get().pipe_min_bytes ? hlAlgoPipelined : hlAlgoNvls;
+  if (nvls_ok && nvlsPays()) {
+    // Measured on B200 (bf16, busbw GB/s): the switch kernels win below 32 MiB (one launch, two barriers); from
+    // there the stores-only kernel is ahead (8 GPUs, 128 MiB: 568 push / 557 NVLS / 529 pipelined; 4 GPUs,
+    // 256 MiB: 586 push / 540 pipelined) until the message is long enough for the pipelined NVLS kernel's large
+    // tiles (8 GPUs, 1 GiB: 728 pipelined / 601 push; 4 GPUs, 1 GiB: 625 / 599).
+    const size_t pipe_min = pipeMinBytes();
+    if (wire_bytes >= pipe_min) return hlAlgoPipelined;
+    if (wire_bytes >= Config::get().push_min_bytes) return hlAlgoPush;
+    return hlAlgoNvls;
+  }
   return hlAlgoPush;  // peer pointers: stores only (falls back to the staged two-shot when the call converts types)
 }
 
@@ -215,7 +233,6 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       a.count = len;
       a.in_seg_stride = c.in_seg_stride ? c.in_seg_stride : c.count;
       a.out_seg_stride = c.out_seg_stride ? c.out_seg_stride : c.count;
-      a.seq = seq_;
       a.scale = (c.scale == 0.0f ? 1.0f : c.scale) * (c.op == hlAvg ? 1.0f / (float)nranks_ : 1.0f);
       a.op = c.op;
       a.in_dt = c.in_dt;
@@ -238,13 +255,8 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       if (forced) tps = std::max<uint64_t>(64, (uint64_t)atoll(forced) & ~(uint64_t)63);
       const uint64_t tiles = (sp + tps - 1) / tps;
       blocks = (int)std::min<uint64_t>((uint64_t)blocks, tiles);
-      for (int i = 0; i < nl; ++i) {
-        calls.c[i].tile_packets = tps;
-        calls.c[i].pipe_seq = pipe_seq_;
-      }
-      pipe_seq_ += (tiles + (uint64_t)blocks - 1) / (uint64_t)blocks;
+      for (int i = 0; i < nl; ++i) calls.c[i].tile_packets = tps;
     }
-    seq_ += HL_SEQ_STRIDE;
     const int rows = emu_ ? emu_active_ : 1;
     HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, rows, blocks, s));
     ++launches_;
@@ -274,11 +286,12 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
   if (c.count == 0) return hlSuccess;
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
   const bool nvls = nvlsUsable(c.wire_dt, c.op, c.deterministic) && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot &&
-                    (c.algo == hlAlgoNvls || nvlsPays());
+                    (c.algo == hlAlgoNvls || c.algo == hlAlgoPipelined || nvlsPays());
   const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
   int kind = nvls ? kNvlReduceScatterNvls : kNvlReduceScatter;
   if (nvls) {
-    if (c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().pipe_min_bytes)) kind = kNvlReduceScatterPipeNvls;
+    if (c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= pipeMinBytes())) kind = kNvlReduceScatterPipeNvls;
+    else if (same && (c.algo == hlAlgoPush || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().push_min_bytes))) kind = kNvlReduceScatterPush;
   } else if (same && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot) {
     kind = c.algo == hlAlgoPipelined ? kNvlReduceScatterPipeP2p : kNvlReduceScatterPush;
   }
@@ -308,8 +321,6 @@ hlResult_t NvlPath::barrier(cudaStream_t s) {
   HL_CHECK(orderAfterPrevious(s));
   HlEmuCalls calls;
   memset(&calls, 0, sizeof(calls));
-  for (int i = 0; i < localRanks(); ++i) calls.c[i].seq = seq_;
-  seq_ += HL_SEQ_STRIDE;
   ++launches_;
   return nvl::launch(kNvlBarrier, hlFloat32, dcomm_, calls, emu_ ? emu_active_ : 1, 1, s);
 }

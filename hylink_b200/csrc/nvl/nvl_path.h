@@ -67,6 +67,7 @@ class NvlPath {
   hlResult_t resetAfterError();
   int pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const;
   bool nvlsPays() const;
+  size_t pipeMinBytes() const;
   bool nvlsUsable(int wire_dt, int op, bool deterministic) const;
   int blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const;
 
@@ -86,8 +87,7 @@ class NvlPath {
   HlCommDev* dcomm_ = nullptr;     // device array: 1 entry (real) or nranks (emu)
   uint64_t* status_host_ = nullptr; // pinned, mapped; 8 words per local rank
   uint32_t* abort_dev_ = nullptr;   // one word per local rank
-  uint64_t seq_ = 0;
-  uint64_t pipe_seq_ = 0;
+  uint64_t* seq_dev_ = nullptr;    // per local rank: flag base, tile base, finished-CTA counter (advanced by the kernels)
   uint64_t launches_ = 0;
   cudaEvent_t order_ev_ = nullptr;
   cudaStream_t last_stream_ = nullptr;

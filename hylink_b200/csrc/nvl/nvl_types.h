@@ -28,6 +28,8 @@ struct HlCommDev {
   uint8_t* mc_stage;               // NVSwitch multicast alias of stage (null without NVLS)
   uint64_t* status;                // host-visible: [0] code, [1] detail (step<<32 | peer), [2] block
   uint32_t* abort_word;            // device word: non-zero poisons the communicator
+  uint64_t* seq_words;             // device words: [0] flag base of the next call, [1] tile base of the next pipelined
+                                   // call, [2] CTAs of the running call that have finished
   uint64_t stage_bytes;
   uint64_t timeout_ns;
 };
@@ -39,14 +41,14 @@ struct HlCallArgs {
   uint64_t count;           // elements: AR/bcast total; AG/RS/A2A the handled prefix of one segment
   uint64_t in_seg_stride;   // elements between segments of `in`  (RS, A2A)
   uint64_t out_seg_stride;  // elements between segments of `out` (AG, A2A)
-  uint64_t seq;             // flag base of this call; barrier k waits for seq + k
+  uint64_t seq;             // flag base of this call (filled in on the device from seq_words); barrier k waits for seq + k
   float scale;              // applied to the reduced value (floating types)
   int op;                   // hlRedOp_t
   int in_dt;                // hlDataType_t of `in`
   int out_dt;               // hlDataType_t of `out`
   int root;
   int int_div;              // integer types: divide the sum (hlAvg), 0 = off
-  uint64_t pipe_seq;        // pipelined kernels: tile k of a block is announced as pipe_seq + k + 1
+  uint64_t pipe_seq;        // pipelined kernels (filled in on the device): tile k of a block is announced as pipe_seq + k + 1
   uint64_t tile_packets;    // pipelined kernels: 16-byte packets of one shard handled per tile
 };
 

@@ -6,7 +6,7 @@ Runs, on ONE device: the two-shot pull all-reduce, the push all-reduce, the
 pipelined all-reduce, the push reduce-scatter and the all-gather with `--ranks`
 emulated ranks (one cooperative launch each; `--mib` MiB of bf16 per rank, so
 the working set is larger than the 126 MB L2 while staying within a few
-hundred MB), and the landing-reduce kernel over four 128 MiB sources. Prints the
+hundred MB), and the landing-reduce kernel over four `--landing-mib` MiB sources. Prints the
 CUDA-event time of every launch and the HBM traffic it implies. Meant to be run
 plainly first and then under ``ncu -k regex:... -c N --clock-control none``.
 """
@@ -22,7 +22,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--mib", type=int, default=48)
-    ap.add_argument("--reps", type=int, default=2)
+    ap.add_argument("--reps", type=int, default=2, help="timed launches after the warm-up launch (0: warm-up only)")
+    ap.add_argument("--landing-mib", type=int, default=128)
     a = ap.parse_args(argv)
     from hylink_b200.ops import EmuGroup, reduce_landing
 
@@ -55,7 +56,7 @@ def main(argv=None) -> int:
     timed("reducescatter_push", lambda: g.run("reduce_scatter", ins, [o[:seg] for o in outs], seg, in_seg_stride=seg),
           n * nb * (2.0 * (n - 1) / n + 1 + 1.0 / n))
     timed("allgather_pull", lambda: g.run("all_gather", [t[:seg] for t in ins], gathered, seg, out_seg_stride=seg), n * (2 * seg * 2 + 2 * count * 2))
-    srcs = [torch.randn(64 << 20, device="cuda").to(torch.bfloat16) for _ in range(4)]
+    srcs = [torch.randn(a.landing_mib << 19, device="cuda").to(torch.bfloat16) for _ in range(4)]
     dst = torch.empty_like(srcs[0])
     timed("reduce_landing_4way", lambda: reduce_landing(dst, srcs), 5 * srcs[0].numel() * 2)
     g.close()

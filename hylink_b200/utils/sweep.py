@@ -117,8 +117,7 @@ def main(argv=None) -> int:
                     ours = lambda i: comm.all_reduce(bufs(i)[0], bufs(i)[1], **kw)
                     ref = lambda i: (bufs(i)[1].copy_(bufs(i)[0]), dist.all_reduce(bufs(i)[1]))
                 elif coll == "reducescatter":
-                    ours = lambda i: comm.reduce_scatter(bufs(i)[0], bufs(i)[1][:seg], path=a.path, max_blocks=a.max_blocks,
-                                                         deterministic=a.deterministic)
+                    ours = lambda i: comm.reduce_scatter(bufs(i)[0], bufs(i)[1][:seg], **kw)
                     ref = lambda i: dist.reduce_scatter_tensor(bufs(i)[1][:seg], bufs(i)[0])
                 elif coll == "allgather":
                     ours = lambda i: comm.all_gather(bufs(i)[0][:seg], bufs(i)[1], path=a.path, max_blocks=a.max_blocks)

@@ -304,3 +304,35 @@ def test_push_allreduce_bitwise(n, dtype):
             assert torch.equal(b, ref)
     g.close()
     g2.close()
+
+
+def test_collectives_replay_from_a_cuda_graph():
+    """The kernels keep their flag sequence in device memory, so a captured launch can be replayed."""
+    n, count = 4, 200003
+    g = _group(n, stage_bytes=16 << 20)
+    ins = [_rand(count, torch.float32, r) for r in range(n)]
+    outs = [torch.zeros(count, device="cuda") for _ in range(n)]
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        g.run("all_reduce", ins, outs, count, algo="push")  # first use outside the capture
+        g.run("all_reduce", ins, outs, count, algo="pipelined")
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        g.run("all_reduce", ins, outs, count, algo="push")
+        g.run("all_reduce", outs, outs, count, algo="pipelined", scale=1.0 / n)
+    for it in range(3):
+        for r in range(n):
+            ins[r].copy_(_rand(count, torch.float32, 100 * it + r))
+        ref = _ordered_sum(ins, torch.float32)
+        ref = _ordered_sum([ref] * n, torch.float32) * (1.0 / n)
+        graph.replay()
+        torch.cuda.synchronize()
+        for o in outs:
+            assert torch.equal(o, ref), it
+    # and eager calls still line up with the replays
+    g.run("all_reduce", ins, outs, count, algo="twoshot")
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], _ordered_sum(ins, torch.float32))
+    assert g.status(0)[0] == 0
+    g.close()
