@@ -208,3 +208,80 @@ def test_dead_peer_is_detected():
     for p in ps:
         p.join(20)
     assert (r, status, val) == (0, "ok", "detected"), val
+
+
+def test_single_process_mode_threads_as_ranks_and_peer_device_reads():
+    """Zeroed unique id: the ranks are threads of one process (the reference's SP mode). A schedule may then read a
+    peer's device buffer directly (`src_rank`), which multi-process mode refuses."""
+    import threading
+
+    from hylink_b200._native import UniqueId, check, lib
+    from hylink_b200.utils import schedule as S
+
+    lib.hlConfigReload()
+    n, count = 2, 30000
+    # all-gather where every rank copies the peer's input straight out of the peer's buffer
+    s = S.Schedule("allgather", n, topology="direct test", variant="direct")
+    for r in range(n):
+        s.d2d(r, 0, r)
+        s.d2d(r, 0, 1 - r, src_rank=1 - r)
+    xml = s.to_xml().encode()
+    errors, outs = [], {}
+
+    def run(rank):
+        try:
+            h = C.c_void_p()
+            lib.pcclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+            check(lib.pcclCommInitRank(C.byref(h), n, UniqueId(), rank), "pcclCommInitRank")
+            x = torch.full((count,), float(rank + 1))
+            out = torch.zeros(count)
+            lib.pcclAllReduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+            check(lib.pcclAllReduce(x.data_ptr(), out.data_ptr(), count, h, None), "pcclAllReduce")
+            check(lib.hlCommDrain(h), "drain")
+            assert torch.all(out == 3.0)
+            g = torch.zeros(count * n)
+            check(lib.hlSubmitIr(h, xml, x.data_ptr(), g.data_ptr(), count, 0, 1, n, 7, 0, None), "hlSubmitIr")
+            check(lib.hlCommDrain(h), "drain")
+            outs[rank] = g
+            lib.pcclCommDestroy.argtypes = [C.c_void_p]
+            check(lib.pcclCommDestroy(h), "destroy")
+        except BaseException as e:  # noqa: BLE001
+            errors.append((rank, repr(e)))
+
+    import os
+
+    os.environ.update(SMALL_POOLS)
+    lib.hlConfigReload()
+    ts = [threading.Thread(target=run, args=(r,)) for r in range(n)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join(120)
+    for k in SMALL_POOLS:
+        os.environ.pop(k, None)
+    lib.hlConfigReload()
+    assert not errors, errors
+    for r in range(n):
+        assert torch.all(outs[r][:count] == 1.0) and torch.all(outs[r][count:] == 2.0)
+
+
+def _refuse_peer_reads_worker(rank, n, uid):
+    import hylink_b200._native as N
+    from hylink_b200.utils import schedule as S
+
+    c = _comm(rank, n, uid)
+    s = S.Schedule("allgather", n)
+    for r in range(n):
+        s.d2d(r, 0, r)
+        s.d2d(r, 0, 1 - r, src_rank=1 - r)
+    x, g = torch.ones(100), torch.zeros(200)
+    rc = N.lib.hlSubmitIr(c._h, s.to_xml().encode(), x.data_ptr(), g.data_ptr(), 100, 0, 1, n, 7, 0, None)
+    msg = N.lib.hlGetLastError().decode()
+    c.close()
+    return rc, msg
+
+
+def test_peer_device_reads_are_refused_between_processes():
+    res = run_ranks(_refuse_peer_reads_worker, 2, env=SMALL_POOLS)
+    for rc, msg in res:
+        assert rc == 7 and "threads of one process" in msg, (rc, msg)  # hlUnsupported
