@@ -27,10 +27,12 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-REF_UNAVAILABLE = ("reference cannot run this config here: it has no torch.distributed backend and no installable Python "
-                   "package (pip install of the tree fails: no setup.py/pyproject); its multipath build libampccl_nccl.so "
-                   "needs the typed PCCL API that only the Ascend PCCL provides, and the CUDA PCCL ships no schedule for "
-                   "this box's GPU->NUMA pattern")
+REF_UNAVAILABLE = ("the reference cannot run this configuration on this image: it is not a Python project (pip install of the tree: "
+                   "'Neither setup.py nor pyproject.toml found'), its multipath build libampccl_nccl.so does not compile against its "
+                   "CUDA PCCL ('pcclDataType_t has not been declared'), and its only PyTorch route, LD_PRELOAD=libpccl.so under "
+                   "backend=nccl, stops at communicator set-up on a B200 box ('sysfs reports invalid NUMA node -1', then with "
+                   "PCCL_GPU_NUMA_MAP 'NCCL error invalid argument, NCCL version 2.17.1' under PyTorch 2.11); record: "
+                   "profiles/reference_arm_probe.md")
 
 
 class ClockSampler:

@@ -285,3 +285,35 @@ def test_peer_device_reads_are_refused_between_processes():
     res = run_ranks(_refuse_peer_reads_worker, 2, env=SMALL_POOLS)
     for rc, msg in res:
         assert rc == 7 and "threads of one process" in msg, (rc, msg)  # hlUnsupported
+
+
+def _eight_rank_worker(rank, n, uid):
+    c = _comm(rank, n, uid)
+    count = 80008
+    x = _data(rank, count, torch.float32, seed=2)
+    out = torch.zeros(count)
+    c.all_reduce(x, out)
+    c.drain()
+    ref = sum(_data(r, count, torch.float32, seed=2).double() for r in range(n))
+    assert torch.allclose(out.double(), ref, atol=1e-4)
+    seg = 5000
+    full = torch.zeros(seg * n)
+    mine = _data(rank, seg, torch.float32, seed=4)  # the call is asynchronous: inputs must outlive it
+    c.all_gather(mine, full)
+    c.drain()
+    for q in range(n):
+        assert torch.equal(full[q * seg:(q + 1) * seg], _data(q, seg, torch.float32, seed=4))
+    rs = torch.zeros(seg)
+    parts = torch.cat([_data(rank, seg, torch.float32, seed=30 + q) for q in range(n)])
+    c.reduce_scatter(parts, rs)
+    c.drain()
+    want = sum(_data(r, seg, torch.float32, seed=30 + rank).double() for r in range(n))
+    assert torch.allclose(rs.double(), want, atol=1e-4)
+    c.close()
+    return True
+
+
+def test_eight_ranks_two_numa_nodes():
+    """The 8-GPU board layout (pattern 00001111): 72 host chunks per all-reduce, generated schedules."""
+    env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP="00001111", HYLINK_HOST_BUFFER_SIZE="32M", HYLINK_H2H_WORKERS="1")
+    run_ranks(_eight_rank_worker, 8, env=env, timeout=300)
