@@ -189,8 +189,8 @@ static Config* loadConfig() {
   c->orch_enable = envBool({"HYLINK_ORCH_ENABLE", "AMPCCL_ENABLE"}, false);
   c->algo = envStr({"HYLINK_ALGO", "AMPCCL_ALGO"}, "split_ratio");
   c->static_alpha = envDouble({"HYLINK_STATIC_ALPHA", "AMPCCL_STATIC_ALPHA"}, 0.05);
-  c->min_msg_bytes = (size_t)envInt({"HYLINK_MIN_MSG_SIZE", "AMPCCL_MIN_MSG_SIZE"}, 4LL << 20);
-  c->min_msg_bytes_8 = (size_t)envInt({"HYLINK_MIN_MSG_SIZE_8", "AMPCCL_MIN_MSG_SIZE_8RANKS"}, 256LL << 20);
+  c->min_msg_bytes = (size_t)envInt({"HYLINK_MIN_MSG_SIZE", "AMPCCL_MIN_MSG_SIZE"}, 256LL << 20);
+  c->min_msg_bytes_8 = (size_t)envInt({"HYLINK_MIN_MSG_SIZE_8", "AMPCCL_MIN_MSG_SIZE_8RANKS"}, 1LL << 30);
   c->min_chunk_bytes = (size_t)envInt({"HYLINK_MIN_CHUNK_SIZE", "AMPCCL_MIN_CHUNK_SIZE"}, 4096);
   c->node_scope_wait_ms = (int)envInt({"HYLINK_NODE_SCOPE_WAIT_MS", "AMPCCL_NODE_SCOPE_WAIT_MS"}, 200);
   c->avg_bw_log = envBool({"HYLINK_AVG_BW_LOG", "AMPCCL_AVG_BW_LOG"}, false);

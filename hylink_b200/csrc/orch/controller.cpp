@@ -218,6 +218,10 @@ AdaptiveController::Entry& AdaptiveController::entry(const OpKey& key) {
 double AdaptiveController::suggestAlpha(const OpKey& key) {
   Entry& e = entry(key);
   if (!e.value.use_pcie) return 0.0;
+  if (e.value.cooldown > 0) {  // the split was not paying: stay on the dedicated link for a while, then probe again
+    --e.value.cooldown;
+    return 0.0;
+  }
   e.value.alpha = e.algo->suggest(e.value);
   return e.value.alpha;
 }
@@ -232,6 +236,23 @@ void AdaptiveController::update(const OpKey& key, const ExecStat& s) {
   e.value.alpha = e.algo->alpha();
   e.value.updates++;
   if (!s.pcie_ok) e.value.use_pcie = false;  // degrade to the dedicated link for this key
+  // No-gain guard (not in the reference): the host-staged path has a latency floor of several hundred microseconds
+  // on this class of machine; when a forked call keeps finishing later than the dedicated link alone would have
+  // (estimated from this call's own link bandwidth), stop forking this key for a while instead of paying every call.
+  static const bool guard = envBool({"HYLINK_ORCH_GUARD"}, true);
+  if (guard && s.fast_ok && s.pcie_ok && s.pcie_bytes && s.fast_bytes && s.fast_time > 0) {
+    const double alone = s.fast_time * (double)(s.fast_bytes + s.pcie_bytes) / (double)s.fast_bytes;
+    if (std::max(s.fast_time, s.pcie_time) > 1.05 * alone) {
+      // The streak is long enough for the controllers to re-balance after a change of conditions first.
+      static const int streak = (int)envInt({"HYLINK_ORCH_GUARD_STREAK"}, 16);
+      if (++e.value.losing_streak >= streak) {
+        e.value.losing_streak = 0;
+        e.value.cooldown = (int)envInt({"HYLINK_ORCH_COOLDOWN_CALLS"}, 200);
+      }
+    } else {
+      e.value.losing_streak = 0;
+    }
+  }
   if (s.fast_ok && s.pcie_ok) {
     const double t = std::max(s.fast_time, s.pcie_time);
     const double bw = t > 0 ? (double)(s.fast_bytes + s.pcie_bytes) / t : 0;

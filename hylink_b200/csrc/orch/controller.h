@@ -75,6 +75,8 @@ struct ParamValue {
   double best_bandwidth = 0;   // bytes/s of the best total seen
   uint64_t updates = 0;
   bool use_pcie = true;        // latched off after a PCIe failure
+  int losing_streak = 0;       // consecutive forked calls that were slower than the dedicated link alone would have been
+  int cooldown = 0;            // forked calls to skip before the PCIe path is tried again
 };
 
 class AdaptiveAlgo {

@@ -73,17 +73,53 @@ OpInfo toHlOp(const c10d::ReduceOp& op) {
   }
 }
 
+// Events are recycled: creating and destroying two CUDA events per collective
+// costs more host time than the rest of the launch path, and in a launch-bound
+// training step every microsecond on the autograd thread is step time.
+class EventPool {
+ public:
+  ~EventPool() {
+    for (auto e : free_) cudaEventDestroy(e);
+  }
+  cudaEvent_t acquire() {
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      if (!free_.empty()) {
+        cudaEvent_t e = free_.back();
+        free_.pop_back();
+        return e;
+      }
+    }
+    cudaEvent_t e = nullptr;
+    C10_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    return e;
+  }
+  void release(cudaEvent_t e) {
+    std::lock_guard<std::mutex> lk(mu_);
+    free_.push_back(e);
+  }
+
+ private:
+  std::mutex mu_;
+  std::vector<cudaEvent_t> free_;
+};
+
 class HylinkWork : public c10d::Work {
  public:
   HylinkWork(int rank, OpType op, std::vector<at::Tensor> outputs, std::vector<at::Tensor> keep)
       : c10d::Work(rank, op), outputs_(std::move(outputs)), keep_(std::move(keep)) {}
 
+  ~HylinkWork() override {
+    if (event_ && pool_) pool_->release(event_);
+  }
+
   // CUDA flavour: call with the communication stream current.
-  void armCuda(c10::cuda::CUDAStream comm_stream) {
+  void armCuda(c10::cuda::CUDAStream comm_stream, const std::shared_ptr<EventPool>& pool) {
     cuda_ = true;
     device_ = comm_stream.device();
-    event_ = std::make_shared<at::cuda::CUDAEvent>(cudaEventDisableTiming);
-    event_->record(comm_stream);
+    pool_ = pool;
+    event_ = pool->acquire();
+    C10_CUDA_CHECK(cudaEventRecord(event_, comm_stream.stream()));
     future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()),
                                                        std::vector<c10::Device>{device_});
     c10::cuda::CUDAStreamGuard g(comm_stream);
@@ -94,10 +130,18 @@ class HylinkWork : public c10d::Work {
     future_->markCompleted(at::IValue(outputs_));
   }
 
-  bool isCompleted() override { return cuda_ ? event_->query() : true; }
+  bool isCompleted() override {
+    if (!cuda_) return true;
+    const cudaError_t e = cudaEventQuery(event_);
+    if (e == cudaErrorNotReady) {
+      (void)cudaGetLastError();
+      return false;
+    }
+    return true;
+  }
   bool isSuccess() const override { return true; }
   void synchronize() override {
-    if (cuda_) event_->block(c10::cuda::getCurrentCUDAStream(device_.index()));
+    if (cuda_) C10_CUDA_CHECK(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream(device_.index()).stream(), event_, 0));
   }
   bool wait(std::chrono::milliseconds /*timeout*/) override {
     synchronize();
@@ -112,7 +156,8 @@ class HylinkWork : public c10d::Work {
   std::vector<at::Tensor> keep_;  // inputs kept alive until the caller has waited
   bool cuda_ = false;
   c10::Device device_{c10::kCPU};
-  std::shared_ptr<at::cuda::CUDAEvent> event_;
+  cudaEvent_t event_ = nullptr;
+  std::shared_ptr<EventPool> pool_;
   c10::intrusive_ptr<c10::ivalue::Future> future_;
 };
 
@@ -167,6 +212,11 @@ class HylinkBackend : public c10d::Backend {
       comm_stream_ = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/hp && atoi(hp) != 0, device));
     }
     hlCheck(hlCommInitRankDevice(&slot, getSize(), id, getRank(), device), "hlCommInitRankDevice");
+    if (cuda && ready_ring_.empty()) {
+      c10::cuda::CUDAGuard dg(t.device());
+      ready_ring_.resize(64);
+      for (auto& e : ready_ring_) C10_CUDA_CHECK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    }
     return slot;
   }
 
@@ -178,11 +228,11 @@ class HylinkBackend : public c10d::Backend {
     if (probe.is_cuda()) {
       c10::cuda::CUDAGuard dg(probe.device());
       auto cur = c10::cuda::getCurrentCUDAStream(probe.device().index());
-      at::cuda::CUDAEvent ready(cudaEventDisableTiming);
-      ready.record(cur);
-      ready.block(*comm_stream_);
+      cudaEvent_t ready = ready_ring_[ready_next_++ % ready_ring_.size()];
+      C10_CUDA_CHECK(cudaEventRecord(ready, cur.stream()));
+      C10_CUDA_CHECK(cudaStreamWaitEvent(comm_stream_->stream(), ready, 0));
       body(comm, (hlStream_t)comm_stream_->stream());
-      work->armCuda(*comm_stream_);
+      work->armCuda(*comm_stream_, events_);
       ++collectives_;
     } else {
       body(comm, nullptr);
@@ -396,6 +446,9 @@ class HylinkBackend : public c10d::Backend {
   int generation_ = 0;
   std::unique_ptr<c10::cuda::CUDAStream> comm_stream_;
   uint64_t collectives_ = 0;
+  std::vector<cudaEvent_t> ready_ring_;   // "inputs are ready" markers; a slot is reused 64 collectives later
+  size_t ready_next_ = 0;
+  std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
   float fused_scale_ = 0.0f;
   int max_blocks_ = 0;
 };

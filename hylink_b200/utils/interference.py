@@ -100,6 +100,7 @@ def main(argv=None) -> int:
     os.environ["HYLINK_ORCH_ENABLE"] = "1"
     os.environ["HYLINK_ALGO"] = a.controller
     os.environ["HYLINK_STATIC_ALPHA"] = str(a.static_alpha)
+    os.environ.setdefault("HYLINK_ORCH_GUARD", "0")  # keep forking so that the retuning itself can be observed
     os.environ.setdefault("HYLINK_MIN_MSG_SIZE", "4M")
     os.environ.setdefault("HYLINK_MIN_MSG_SIZE_8", "4M")
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

@@ -174,3 +174,18 @@ def test_path_timing_overlap():
     assert abs(eff - 2.25 / 3.0) < 1e-12
     lib.hlPathTiming(0.0, 1.0, 2.0, 3.0, out)                      # disjoint: no overlap
     assert out[2] == 0.0
+
+
+def test_no_gain_guard_pauses_a_split_that_keeps_losing():
+    c = Ctl("split_ratio")
+    a = c.suggest()
+    assert a > 0
+    nbytes = 256 * MB
+    for _ in range(16):  # PCIe half takes 3x as long as the whole message would take on the link alone
+        fb, pb, _ = plan(nbytes, a)
+        lib.hlCtlUpdate(c.h, AR, nbytes, BF16, 8, fb / 700e9, 3 * nbytes / 700e9, fb, pb, 1, 1)
+    assert c.suggest() == 0.0 and lib.hlCtlUsePcie(c.h, AR, nbytes, BF16, 8) == 1   # paused, not latched off
+    for _ in range(198):
+        assert c.suggest() == 0.0
+    c.suggest()
+    assert c.suggest() > 0.0                                                       # probes again after the cool-down
