@@ -96,13 +96,13 @@ __device__ __forceinline__ void segCopyOut(D* dst, const uint4* stage_seg, uint6
 // Reduction over the same packet of every rank's staging, ranks visited in
 // ascending order whatever the caller's rank: the sum order is fixed, so the
 // result is bitwise identical on every rank and from run to run.
-template <typename W>
+template <typename W, int MR = HL_MAX_RANKS>
 __device__ __forceinline__ uint4 reducePackets(const uint4* v, int n, int op, float scale, int int_div) {
   constexpr int N = Packet<W>::N;
   typename Wire<W>::Acc acc[N], b[N];
   Packet<W>::unpack(v[0], acc);
 #pragma unroll
-  for (int q = 1; q < HL_MAX_RANKS; ++q) {
+  for (int q = 1; q < MR; ++q) {
     if (q < n) {
       Packet<W>::unpack(v[q], b);
 #pragma unroll
@@ -336,6 +336,7 @@ template <bool kNvls> struct PipeShape {
   static constexpr int A = 4, B = 4, C = 4;
 };
 constexpr int kPipeCopyUnroll = 4;
+constexpr int kPushUnroll = 8;      // 16-byte packets in flight per thread in the copy phases of the push kernels
 constexpr int kPipeNvlsUnroll = 8;  // 16-byte multimem.ld_reduce in flight per exchange thread
 constexpr int kPipeThreads = 384;  // 12 warps: leaves ~170 registers per thread for the deep unrolls
 
@@ -349,63 +350,58 @@ constexpr int kPipeThreads = 384;  // 12 warps: leaves ~170 registers per thread
 // with the landed slots — all local reads, ascending rank order — and pushes
 // the result to every peer's result area (its own part goes directly to the
 // caller's output); stage C copies the other owners' results out locally.
-template <typename S, typename W>
+template <typename S, typename W, int U = kPipeCopyUnroll>
 __device__ __forceinline__ void pushTile(uint4* remote_slot, const S* src, uint64_t cnt, const Ctx& x) {
   constexpr int N = Packet<W>::N;
   const uint64_t np = (cnt + N - 1) / N;
   const bool vec = aligned16(src);
-  for (uint64_t i = x.g0; i < np; i += x.gstride * kPipeCopyUnroll) {
-    uint4 v[kPipeCopyUnroll];
+  for (uint64_t i = x.g0; i < np; i += x.gstride * U) {
+    uint4 v[U];
 #pragma unroll
-    for (int u = 0; u < kPipeCopyUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
       if (j < np) v[u] = loadUserPacket<S, W>(src, j * N, cnt, vec);
     }
 #pragma unroll
-    for (int u = 0; u < kPipeCopyUnroll; ++u) {
+    for (int u = 0; u < U; ++u) {
       const uint64_t j = i + (uint64_t)u * x.gstride;
       if (j < np) remote_slot[j] = v[u];
     }
   }
 }
 
-template <typename S, typename W, typename D, bool kAllReduce>
+// U packets per thread and per source are in flight at once; MR bounds the rank count the
+// unrolled source loop is compiled for (registers: U * MR * 4 for the landed packets).
+template <typename S, typename W, typename D, bool kAllReduce, int U = 2, int MR = HL_MAX_RANKS>
 __device__ __forceinline__ void foldTile(const HlCommDev& c, const HlCallArgs& a, const S* own, uint64_t own_cnt, D* out,
                                          uint64_t out_cnt, uint64_t sp, uint64_t p0, uint64_t tp, uint64_t res_off, const Ctx& x) {
   constexpr int N = Packet<W>::N;
   const int n = c.nranks, r = c.rank;
   const uint4* slots = reinterpret_cast<const uint4*>(c.stage[r]);
   const bool vin = aligned16(own), vout = aligned16(out);
-  for (uint64_t i = x.g0; i < tp; i += x.gstride * 2) {
-    const uint64_t j = i + x.gstride;
-    const bool two = j < tp;
-    uint4 v0[HL_MAX_RANKS], v1[HL_MAX_RANKS];
+  for (uint64_t i = x.g0; i < tp; i += x.gstride * U) {
+    uint4 v[U][MR];
 #pragma unroll
-    for (int q = 0; q < HL_MAX_RANKS; ++q)
-      if (q < n) {
-        if (q == r) {
-          v0[q] = loadUserPacket<S, W>(own, i * N, own_cnt, vin);
-          if (two) v1[q] = loadUserPacket<S, W>(own, j * N, own_cnt, vin);
-        } else {
-          v0[q] = slots[(uint64_t)q * sp + p0 + i];
-          if (two) v1[q] = slots[(uint64_t)q * sp + p0 + j];
+    for (int u = 0; u < U; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < tp) {
+#pragma unroll
+        for (int q = 0; q < MR; ++q)
+          if (q < n) v[u][q] = q == r ? loadUserPacket<S, W>(own, j * N, own_cnt, vin) : slots[(uint64_t)q * sp + p0 + j];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint64_t j = i + (uint64_t)u * x.gstride;
+      if (j < tp) {
+        const uint4 red = reducePackets<W, MR>(v[u], n, a.op, a.scale, a.int_div);
+        storeUserPacket<W, D>(out, j * N, out_cnt, vout, red);
+        if constexpr (kAllReduce) {
+#pragma unroll
+          for (int q = 0; q < MR; ++q)
+            if (q < n && q != r) (reinterpret_cast<uint4*>(c.stage[q]) + res_off + (uint64_t)r * sp + p0)[j] = red;
         }
       }
-    const uint4 r0 = reducePackets<W>(v0, n, a.op, a.scale, a.int_div);
-    storeUserPacket<W, D>(out, i * N, out_cnt, vout, r0);
-    uint4 r1 = r0;
-    if (two) {
-      r1 = reducePackets<W>(v1, n, a.op, a.scale, a.int_div);
-      storeUserPacket<W, D>(out, j * N, out_cnt, vout, r1);
-    }
-    if constexpr (kAllReduce) {
-#pragma unroll
-      for (int q = 0; q < HL_MAX_RANKS; ++q)
-        if (q < n && q != r) {
-          uint4* dst = reinterpret_cast<uint4*>(c.stage[q]) + res_off + (uint64_t)r * sp + p0;
-          dst[i] = r0;
-          if (two) dst[j] = r1;
-        }
     }
   }
 }
@@ -579,20 +575,26 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPush(const HlCommDev* comms, 
   };
   for (int k = 1; k < n; ++k) {
     const int s = (r + k) % n;
-    pushTile<W, W>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp, in + (uint64_t)s * in_stride, shardElems(s), x);
+    pushTile<W, W, kPushUnroll>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp, in + (uint64_t)s * in_stride, shardElems(s), x);
   }
   if (!blockBarrier(c, a.seq + 1, 1)) return;
   {
     const uint64_t cnt = shardElems(r);
     const uint64_t first = kAllReduce ? (uint64_t)r * sp * N : 0;
-    foldTile<W, W, W, kAllReduce>(c, a, in + (uint64_t)r * in_stride, cnt, out + first, cnt, sp, 0, (cnt + N - 1) / N, res_off, x);
+    // about a dozen landed packets per thread in flight whatever the rank count (more spills registers)
+    if (n <= 2)
+      foldTile<W, W, W, kAllReduce, 6, 2>(c, a, in + (uint64_t)r * in_stride, cnt, out + first, cnt, sp, 0, (cnt + N - 1) / N, res_off, x);
+    else if (n <= 4)
+      foldTile<W, W, W, kAllReduce, 3, 4>(c, a, in + (uint64_t)r * in_stride, cnt, out + first, cnt, sp, 0, (cnt + N - 1) / N, res_off, x);
+    else
+      foldTile<W, W, W, kAllReduce, 2, HL_MAX_RANKS>(c, a, in + (uint64_t)r * in_stride, cnt, out + first, cnt, sp, 0, (cnt + N - 1) / N, res_off, x);
   }
   if (!blockBarrier(c, a.seq + 2, 2)) return;
   if constexpr (kAllReduce) {
     const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
     for (int k = 1; k < n; ++k) {
       const int s = (r + k) % n;
-      segCopyOut<W, W>(out + (uint64_t)s * sp * N, mine + res_off + (uint64_t)s * sp, shardElems(s), x);
+      segCopyOut<W, W, kPushUnroll>(out + (uint64_t)s * sp * N, mine + res_off + (uint64_t)s * sp, shardElems(s), x);
     }
   }
   callDone(c, 0);
