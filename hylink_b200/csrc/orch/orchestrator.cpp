@@ -109,6 +109,7 @@ class OrchImpl {
   int64_t applied_ = 0;
   CallRecord ring_[kRing];
   cudaStream_t pcie_stream_ = nullptr;
+  cudaStream_t notify_stream_ = nullptr;  // carries the completion callbacks, so that they never sit in the caller's stream
   cudaEvent_t ev_fork_[kRing] = {nullptr}, ev_join_[kRing] = {nullptr};
   std::mutex mu_;
   std::condition_variable cv_;
@@ -131,6 +132,7 @@ hlResult_t OrchImpl::init() {
   int lo = 0, hi = 0;
   HL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
   HL_CUDA(cudaStreamCreateWithPriority(&pcie_stream_, cudaStreamNonBlocking, hi));
+  HL_CUDA(cudaStreamCreateWithFlags(&notify_stream_, cudaStreamNonBlocking));
   for (int i = 0; i < kRing; ++i) {
     for (int k = 0; k < 4; ++k) HL_CUDA(cudaEventCreate(&ring_[i].ev[k]));
     HL_CUDA(cudaEventCreateWithFlags(&ev_fork_[i], cudaEventDisableTiming));
@@ -157,6 +159,7 @@ OrchImpl::~OrchImpl() {
     if (ev_join_[i]) cudaEventDestroy(ev_join_[i]);
   }
   if (pcie_stream_) cudaStreamDestroy(pcie_stream_);
+  if (notify_stream_) cudaStreamDestroy(notify_stream_);
   if (Config::get().avg_bw_log && comm_->rank == 0 && logged_)
     logAlways("average busbw over %llu forked collectives: %.3f GB/s", (unsigned long long)logged_, sum_busbw_ / (double)logged_);
 }
@@ -275,8 +278,12 @@ hlResult_t OrchImpl::join(const Split& s, cudaStream_t user, bool fast_ok, bool 
   HL_CUDA(cudaEventRecord(s.rec->ev[3], pcie_stream_));
   HL_CUDA(cudaEventRecord(ev_join_[slot], pcie_stream_));
   HL_CUDA(cudaStreamWaitEvent(user, ev_join_[slot], 0));
+  // The callback runs in a stream of its own behind both halves: a host function in the caller's stream would
+  // hold back the caller's next kernel until the driver thread has run it.
+  HL_CUDA(cudaStreamWaitEvent(notify_stream_, s.rec->ev[1], 0));
+  HL_CUDA(cudaStreamWaitEvent(notify_stream_, ev_join_[slot], 0));
   Done* d = new Done{this, s.idx, fast_ok, pcie_ok};
-  HL_CUDA(cudaLaunchHostFunc(user, hostCallback, d));
+  HL_CUDA(cudaLaunchHostFunc(notify_stream_, hostCallback, d));
   comm_->stats.calls++;
   comm_->stats.bytes += s.rec->alg_bytes;
   comm_->stats.nvl_bytes += s.plan.fast_bytes;

@@ -128,12 +128,18 @@ def main(argv=None) -> int:
         print(json.dumps({"event": "link", "d2h_GBs": round(d2h, 1), "h2d_GBs": round(h2d, 1), "world": world,
                           "controller": a.controller}), flush=True)
     factor = 2.0 * (world - 1) / world if a.coll == "allreduce" else (world - 1) / world
+    align = torch.zeros(1, device=dev)
     it = 0
     for level in [int(v) for v in a.levels.split(",")]:
         bg.percent = level
         dist.barrier()
         for _ in range(a.iters):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            # Line the ranks up on the device before the timed call: a delay long enough for the host to queue
+            # everything behind it, then a tiny NCCL all-reduce that ends on all GPUs within microseconds. Without
+            # this the maximum over ranks also counts how much earlier one rank reached the call than another.
+            torch.cuda._sleep(2_000_000)
+            dist.all_reduce(align)
             e0.record()
             if a.coll == "allreduce":
                 comm.all_reduce(x, y, path="auto")
