@@ -12,6 +12,8 @@ Produces, under ``hylink_b200/lib/``:
   interposers of host-blocking CUDA runtime calls.
 * ``_hylink_c10d.so`` — the ``torch.distributed`` backend extension.
 
+and ``hylink_b200/bin/hl_perf``, the stand-alone test executable.
+
 Objects are rebuilt only when a source or any header is newer.
 """
 from __future__ import annotations
@@ -144,10 +146,27 @@ def build_torch_ext(verbose: bool = False) -> Path | None:
     return target
 
 
+def build_tools(verbose: bool = False) -> Path:
+    """hylink_b200/bin/hl_perf: stand-alone correctness + bandwidth test executable."""
+    bindir = ROOT / "bin"
+    bindir.mkdir(parents=True, exist_ok=True)
+    src = CSRC / "tools" / "hl_perf.cpp"
+    obj = OBJ / "tools_hl_perf.cpp.o"
+    changed = _compile(src, obj, _newest_header(), [])
+    target = bindir / "hl_perf"
+    if changed or not target.exists():
+        _run(["g++", "-o", str(target), str(obj), "-L", str(LIB), "-lhylink_b200", "-Wl,-rpath,$ORIGIN/../lib",
+              "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+        if verbose:
+            print("linked", target)
+    return target
+
+
 def build_all(verbose: bool = False) -> None:
     build_core(verbose)
     build_nccl_shim(verbose)
     build_torch_ext(verbose)
+    build_tools(verbose)
 
 
 if __name__ == "__main__":

@@ -69,3 +69,18 @@ def test_nccl_symbol_layer_serves_an_unmodified_nccl_program():
 def test_deterministic_sum_order_against_host_oracles():
     out = _torchrun(2, ["-m", "hylink_b200.utils.determinism", "--bytes-from", "256K", "--bytes-to", "16M"])
     assert '"failures": 0' in out, out[-3000:]
+
+
+def test_native_perf_tool_threads_and_fork():
+    """hl_perf on two GPUs: ranks as threads over the NVLink kernels, ranks as processes over the PCIe path."""
+    tool = os.path.join(ROOT, "hylink_b200", "bin", "hl_perf")
+    for args, env in (
+        (["--coll", "allreduce", "--ranks", "2", "--mode", "threads", "--path", "nvlink", "--dtype", "bf16",
+          "--bytes-from", "4K", "--bytes-to", "64M", "--factor", "16", "--iters", "5"], {}),
+        (["--coll", "reducescatter", "--ranks", "2", "--mode", "fork", "--path", "pcie", "--strided",
+          "--bytes-from", "1M", "--bytes-to", "1M", "--iters", "3"],
+         {"HYLINK_PCIE_ENABLE": "1", "HYLINK_HOST_BUFFER_SIZE": "256M", "HYLINK_INTERNAL_BUFFER_BYTES": "128M"}),
+    ):
+        p = subprocess.run([tool] + args, env=dict(os.environ, **env), stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                           text=True, timeout=300)
+        assert p.returncode == 0 and "Test PASSED." in p.stdout, p.stdout[-3000:]
