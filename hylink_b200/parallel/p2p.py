@@ -18,7 +18,8 @@ def p2p_group():
     """The NCCL group used for send/recv (created collectively on first use)."""
     global _p2p_group
     if _p2p_group is None:
-        _p2p_group = dist.new_group(backend="nccl")
+        # NCCL between GPUs; gloo when the job runs on CPU tensors (tests on a machine without a GPU)
+        _p2p_group = dist.new_group(backend="nccl" if torch.cuda.is_available() else "gloo")
     return _p2p_group
 
 

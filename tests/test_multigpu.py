@@ -84,3 +84,9 @@ def test_native_perf_tool_threads_and_fork():
         p = subprocess.run([tool] + args, env=dict(os.environ, **env), stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                            text=True, timeout=300)
         assert p.returncode == 0 and "Test PASSED." in p.stdout, p.stdout[-3000:]
+
+
+def test_parallel_schemes_match_dense_math():
+    """Tensor/sequence parallel, sharded optimizer, MoE all-to-all, Ulysses / context-parallel attention, GPipe."""
+    out = _torchrun(2, ["-m", "hylink_b200.utils.parallel_selftest"])
+    assert "PARALLEL SELFTEST PASSED" in out, out[-3000:]
