@@ -60,6 +60,11 @@ hlResult_t hlCommNumaPattern(hlComm_t comm, char* buf, size_t* len);
 int hlHostReduce(void* dst, const void* a, const void* b, size_t count, int dtype, int op, int level_cap);
 void hlHostCopy(void* dst, const void* src, size_t bytes, int non_temporal);
 int hlHostSimdLevel(void);
+/* Copy (reduce = 0) or three-address sum (reduce = 1) of `bytes` through `threads` pool workers pinned to dst_numa,
+ * sources placed on src_numa (-1 = wherever). *gbs = mean rate over `iters` runs in GB/s of destination bytes. */
+hlResult_t hlHostBench(int reduce, size_t bytes, int threads, int src_numa, int dst_numa, int iters, int non_temporal,
+                       int dtype, double* gbs, double* best_gbs);
+int hlHostNumaNodes(void);
 
 /* ---- tracing and configuration --------------------------------------------- */
 void hlTraceOpen(const char* path, int rank);

@@ -1,5 +1,6 @@
 """Host SIMD kernels of the PCIe path against PyTorch references (no GPU)."""
 import ctypes as C
+import os
 
 import pytest
 import torch
@@ -55,3 +56,19 @@ def test_copy_any_alignment(nt):
         lib.hlHostCopy(dst.data_ptr() + off_d, src.data_ptr() + off_s, n, nt)
         assert torch.equal(dst[off_d:off_d + n], src[off_s:off_s + n])
         assert dst[off_d + n:].sum() == 0 and dst[:off_d].sum() == 0
+
+
+def test_host_micro_benchmark_runs_through_the_worker_pool():
+    """`microbench h2h`: copy and reduce through the NUMA worker pool, one JSON line per configuration."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.run([sys.executable, "-m", "hylink_b200.utils.microbench", "h2h", "--bytes", "4M", "--threads", "1,2",
+                        "--iters", "2", "--dtype", "bf16"], cwd=root, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                       text=True, timeout=120, env=dict(os.environ, PYTHONPATH=root))
+    assert p.returncode == 0, p.stdout[-2000:]
+    rows = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
+    assert {(r["op"], r["threads"]) for r in rows} >= {("copy", 1), ("copy", 2), ("reduce", 1), ("reduce", 2)}
+    assert all(r["GBs"] > 0 for r in rows)
