@@ -52,3 +52,44 @@ def test_nccl_trace_parser(tmp_path):
     assert out.returncode == 0
     line = [l for l in out.stdout.splitlines() if l.startswith("ncclAllReduce")][0].split()
     assert line[1] == str(2 << 20) and line[2] == "4" and line[5] == "2"
+
+
+def test_orchestrator_log_lines_parse_into_per_call_rows(tmp_path):
+    from hylink_b200.utils import compare
+
+    log = """[hylink] (max) fast_time=0.000498s
+[hylink] (max) pcie_time=0.000626s
+[hylink] aggregate op=AllReduce op_key_bytes=268435456 base_bytes=268435456 alg_bytes=268435456 n=2 | fast_bytes=264865280 pcie_bytes=3570176 split_fast=0.9867 split_pcie=0.0133 | fast_bw(GB/s,decimal)=531.858 pcie_bw(GB/s,decimal)=5.703 | algbw(GB/s,decimal)=428.811 busbw(GB/s,decimal)=428.811 bus_factor=1.0000
+[hylink] Total bw is 428.811000 GB/s
+noise line
+[hylink] (max) fast_time=0.000500s
+[hylink] (max) pcie_time=0.000600s
+[hylink] aggregate op=AllGather op_key_bytes=1048576 base_bytes=1048576 alg_bytes=2097152 n=2 | fast_bytes=1000000 pcie_bytes=48576 split_fast=0.9537 split_pcie=0.0463 | fast_bw(GB/s,decimal)=2.000 pcie_bw(GB/s,decimal)=0.081 | algbw(GB/s,decimal)=3.495 busbw(GB/s,decimal)=1.748 bus_factor=0.5000
+[hylink] Total bw is 1.748000 GB/s
+"""
+    recs = compare.parse_log(log.splitlines())
+    assert [r["op"] for r in recs] == ["AllReduce", "AllGather"]
+    assert recs[0]["pcie_bytes"] == 3570176 and abs(recs[0]["split_pcie"] - 0.0133) < 1e-9
+    assert abs(recs[0]["fast_time_s"] - 0.000498) < 1e-12 and abs(recs[1]["pcie_time_s"] - 0.0006) < 1e-12
+    assert recs[1]["total_bw_GBs"] == 1.748
+    f = tmp_path / "run.log"
+    f.write_text(log)
+    assert compare.main(["logs", str(f), "--csv", str(tmp_path / "calls.csv")]) == 0
+    assert (tmp_path / "calls.csv").read_text().count("\n") == 3
+
+
+def test_sweep_files_merge_into_one_table(tmp_path):
+    import json
+
+    from hylink_b200.utils import compare
+
+    def row(busbw, nccl):
+        return json.dumps({"coll": "allreduce", "dtype": "bf16", "bytes": 1 << 20, "n": 2, "ms": 0.1, "busbw_GBs": busbw,
+                           "nccl_ms": 0.1, "nccl_busbw_GBs": nccl, "speedup": 1.0, "ok": True, "algo": "auto", "path": "x"})
+
+    (tmp_path / "nvlink_2gpu.jsonl").write_text(row(50.0, 40.0) + "\n")
+    (tmp_path / "adaptive_2gpu.jsonl").write_text(row(30.0, 41.0) + "\n")
+    labels, table = compare.merge_sweeps([str(tmp_path / "nvlink_2gpu.jsonl"), str(tmp_path / "adaptive_2gpu.jsonl")])
+    rows = compare.write_sweep_tables(labels, table, str(tmp_path / "s.csv"), str(tmp_path / "s.md"))
+    assert rows == [["allreduce", "bf16", 1 << 20, 2, 50.0, 30.0, 41.0, round(50 / 41, 3), round(30 / 41, 3)]]
+    assert "nvlink_2gpu/NCCL" in (tmp_path / "s.md").read_text()
