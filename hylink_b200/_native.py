@@ -114,6 +114,7 @@ _sig("hlCommDrain", _i, _vp)
 _sig("hlHostReduce", _i, _vp, _vp, _vp, _sz, _i, _i, _i)
 _sig("hlHostCopy", None, _vp, _vp, _sz, _i)
 _sig("hlHostSimdLevel", _i)
+_sig("hlNvlLinkProbe", _i, _vp, _i, _i, _i, _i, _i, _sz, _vp)
 _sig("hlHostBench", _i, _i, _sz, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_double), C.POINTER(C.c_double))
 _sig("hlHostNumaNodes", _i)
 _sig("hlTraceOpen", None, C.c_char_p, _i)

@@ -392,6 +392,13 @@ hlResult_t hlBarrier(hlComm_t comm, hlStream_t stream) {
   return comm->nvl->barrier((cudaStream_t)stream);
 }
 
+hlResult_t hlNvlLinkProbe(hlComm_t comm, int mode, int blocks, int threads, int unroll, int layout, size_t bytes, hlStream_t stream) {
+  HL_CHECK(precheck(comm));
+  std::lock_guard<std::mutex> lk(comm->mu);
+  if (comm->host_device || !comm->nvl) return fail(hlUnsupported, "link probe needs the NVLink path");
+  return comm->nvl->linkProbe(mode, blocks, threads, unroll, layout, bytes, (cudaStream_t)stream);
+}
+
 hlResult_t hlMemAlloc(hlComm_t comm, size_t bytes, void** ptr) {
   if (!comm || !ptr) return hlInvalidArgument;
   if (comm->host_device) {

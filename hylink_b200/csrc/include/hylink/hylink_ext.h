@@ -56,6 +56,13 @@ hlResult_t hlSubmitIr(hlComm_t comm, const char* xml, const void* send, void* re
                       int send_segs, int recv_segs, hlDataType_t t, hlRedOp_t op, hlStream_t stream);
 hlResult_t hlCommNumaPattern(hlComm_t comm, char* buf, size_t* len);
 
+/* ---- link probe -------------------------------------------------------------
+ * Copies `bytes` between the first half of this rank's staging region and the second half of the next rank's with a
+ * bare kernel of the given shape. mode: 0 push (local load, peer store), 1 pull (peer load, local store), 2 local
+ * copy, 3 peer stores only, 4 peer loads only. layout: 0 grid-strided, 1 one contiguous range per CTA. unroll: 2, 4,
+ * 8 (16 up to 512 threads). Waits on nothing; time it with events on `stream`. */
+hlResult_t hlNvlLinkProbe(hlComm_t comm, int mode, int blocks, int threads, int unroll, int layout, size_t bytes, hlStream_t stream);
+
 /* ---- host SIMD kernels ------------------------------------------------------ */
 int hlHostReduce(void* dst, const void* a, const void* b, size_t count, int dtype, int op, int level_cap);
 void hlHostCopy(void* dst, const void* src, size_t bytes, int non_temporal);

@@ -15,6 +15,10 @@ const char* kernelName(int kind);
 hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCalls& calls, int emu_ranks, int blocks,
                   cudaStream_t stream);
 hlResult_t prepareKernels();
+// Bare copy between this rank's staging and `peer`'s (see link_probe.cu); mode 0 push, 1 pull, 2 local, 3 stores
+// only, 4 loads only; `packets` 16-byte packets from offset 0 to offset dst_off.
+hlResult_t launchLinkProbe(const HlCommDev* dcomm, int mode, int blocks, int threads, int unroll, int layout, uint64_t packets,
+                           uint64_t dst_off, int peer, cudaStream_t stream);
 
 // dst[i] = scale * op(src_0[i], ..., src_{k-1}[i]) with fp32 accumulation for
 // 16-bit floats; when `accumulate` is set dst itself is the first operand.

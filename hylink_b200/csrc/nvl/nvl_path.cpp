@@ -179,6 +179,17 @@ int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool dete
   return hlAlgoPush;  // peer pointers: stores only (falls back to the staged two-shot when the call converts types)
 }
 
+hlResult_t NvlPath::linkProbe(int mode, int blocks, int threads, int unroll, int layout, size_t bytes, cudaStream_t s) {
+  if (emu_) return fail(hlUnsupported, "link probe needs a real communicator");
+  if (nranks_ < 2 && mode != 2) return fail(hlInvalidArgument, "link probe needs a peer");
+  const size_t half = stage_bytes_ / 2 / 16 * 16;
+  if (bytes < 16 || bytes > half) return fail(hlInvalidArgument, "link probe: %zu bytes exceed half of the staging region (%zu)", bytes, half);
+  HL_CHECK(orderAfterPrevious(s));
+  HL_CHECK(nvl::launchLinkProbe(dcomm_, mode, blocks, threads, unroll, layout, bytes / 16, half / 16, (rank_ + 1) % nranks_, s));
+  ++launches_;
+  return hlSuccess;
+}
+
 int NvlPath::blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const {
   int cap = max_blocks > 0 ? max_blocks : (Config::get().nvl_max_blocks > 0 ? Config::get().nvl_max_blocks : 148);
   if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));

@@ -59,6 +59,9 @@ class NvlPath {
   hlResult_t broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
   hlResult_t allToAll(const NvlBufs& b, const NvlCall& c, cudaStream_t s);
   hlResult_t barrier(cudaStream_t s);
+  // Measurement aid: copies `bytes` between the first half of the staging region of this rank and the second half
+  // of the next rank's (direction and launch shape by argument). Real paths only.
+  hlResult_t linkProbe(int mode, int blocks, int threads, int unroll, int layout, size_t bytes, cudaStream_t s);
 
   // Device status of local rank i: HL_DEV_OK or the code a kernel recorded.
   uint64_t deviceStatus(int i = 0, uint64_t* detail = nullptr, uint64_t* block = nullptr) const;

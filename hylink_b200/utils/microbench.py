@@ -11,6 +11,11 @@
 * ``overlap``: all-reduce / all-gather / reduce-scatter time alone and next to a GEMM that keeps the SMs busy, and
   the GEMM's slowdown (pcie-ccl-cuda/tests/dev/test_nccl_compute_overlap.cu:41-59,309-327).
 
+* ``p2p`` (``torchrun --nproc-per-node 2 -m hylink_b200.utils.microbench p2p``): rate of a bare copy kernel
+  between this rank's symmetric staging and the next rank's, for a grid of CTA counts, CTA sizes, unroll depths,
+  directions (posted stores to the peer, loads from the peer, local copy) and address layouts. All ranks run the
+  same configuration at the same time, so the figures are per direction under bidirectional load.
+
 Every line of output is one JSON object.
 """
 from __future__ import annotations
@@ -162,6 +167,63 @@ def overlap(args) -> int:
     return 0
 
 
+def p2p(args) -> int:
+    import torch
+    import torch.distributed as dist
+
+    from hylink_b200._native import check, lib
+    from hylink_b200.parallel.comm import Communicator, unique_id
+
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    box = [unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    comm = Communicator(rank, world, uid=box[0], device=local)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    align = torch.zeros(1, device=dev)
+    modes = {"push": 0, "pull": 1, "local": 2, "store": 3, "load": 4}
+
+    def measure(mode, blocks, threads, unroll, layout):
+        times = []
+        for it in range(args.iters + 1):
+            torch.cuda._sleep(1_000_000)   # lets the host queue everything; the tiny all-reduce then lines the ranks up
+            dist.all_reduce(align)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            check(lib.hlNvlLinkProbe(comm._h, modes[mode], blocks, threads, unroll, layout, args.bytes, stream), "hlNvlLinkProbe")
+            e1.record()
+            torch.cuda.synchronize()
+            if it:
+                times.append(e0.elapsed_time(e1))
+        t = torch.tensor([sum(times) / len(times)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    grid = []
+    for mode in args.modes.split(","):
+        for threads in [int(v) for v in args.threads.split(",")]:
+            for blocks in [int(v) for v in args.blocks.split(",")]:
+                for unroll in [int(v) for v in args.unroll.split(",")]:
+                    if unroll == 16 and threads > 512:
+                        continue
+                    for layout in [int(v) for v in args.layouts.split(",")]:
+                        grid.append((mode, blocks, threads, unroll, layout))
+    for mode, blocks, threads, unroll, layout in grid:
+        ms = measure(mode, blocks, threads, unroll, layout)
+        if rank == 0:
+            print(json.dumps({"bench": "p2p", "mode": mode, "blocks": blocks, "threads": threads, "unroll": unroll,
+                              "layout": "cta-contiguous" if layout else "grid-strided", "bytes": args.bytes, "world": world,
+                              "ms": round(ms, 4), "GBs": round(args.bytes / ms / 1e6, 1),
+                              "GBs_per_cta": round(args.bytes / ms / 1e6 / blocks, 2)}), flush=True)
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -179,8 +241,16 @@ def main(argv=None) -> int:
     p.add_argument("--backend", default="hylink", choices=["hylink", "nccl"])
     p.add_argument("--iters", type=int, default=5)
     p.add_argument("--gemms", type=int, default=4)
+    p = sub.add_parser("p2p")
+    p.add_argument("--bytes", type=_size, default=256 << 20)
+    p.add_argument("--modes", default="push,pull,local,store,load")
+    p.add_argument("--blocks", default="16,37,74,148,296")
+    p.add_argument("--threads", default="256,512,1024")
+    p.add_argument("--unroll", default="4,8")
+    p.add_argument("--layouts", default="0,1")
+    p.add_argument("--iters", type=int, default=3)
     args = ap.parse_args(argv)
-    return {"h2h": h2h, "dma": dma, "overlap": overlap}[args.cmd](args)
+    return {"h2h": h2h, "dma": dma, "overlap": overlap, "p2p": p2p}[args.cmd](args)
 
 
 if __name__ == "__main__":
