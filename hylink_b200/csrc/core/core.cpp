@@ -198,6 +198,28 @@ static Config* loadConfig() {
   c->fast_only_bw_log = envBool({"HYLINK_FAST_ONLY_BW_LOG", "AMPCCL_FAST_ONLY_BW_LOG"}, false);
   c->pcie_child_comms = envBool({"HYLINK_PCIE_CHILD_COMMS", "AMPCCL_PCIE_CHILD_COMMS"}, false);
 
+  c->fault_rank = -1;
+  c->fault_copy_error_at = c->fault_stall_at = 0;
+  c->fault_stall_ms = 0;
+  {
+    const std::string spec = envStr({"HYLINK_FAULT_INJECT"}, "");
+    size_t pos = 0;
+    while (pos < spec.size()) {
+      size_t end = spec.find(',', pos);
+      if (end == std::string::npos) end = spec.size();
+      const std::string item = spec.substr(pos, end - pos);
+      pos = end + 1;
+      const size_t at = item.find('@');
+      const long k = at == std::string::npos ? 1 : atol(item.c_str() + at + 1);
+      if (item.compare(0, 10, "copy_error") == 0) c->fault_copy_error_at = k > 0 ? k : 1;
+      else if (item.compare(0, 9, "stall_ms=") == 0) {
+        c->fault_stall_ms = atoi(item.c_str() + 9);
+        c->fault_stall_at = k > 0 ? k : 1;
+      } else if (item.compare(0, 5, "rank=") == 0) c->fault_rank = atoi(item.c_str() + 5);
+      else if (!item.empty()) fprintf(stderr, "[hylink] HYLINK_FAULT_INJECT: unknown item '%s' ignored\n", item.c_str());
+    }
+  }
+
   c->trace_file = envStr({"HYLINK_TRACE_FILE", "PCCL_TRACE_FILE"}, "");
   c->sigdump = envBool({"HYLINK_SIGDUMP", "PCCL_SIGDUMP"}, false);
   c->sigdump_file = envStr({"HYLINK_SIGDUMP_FILE", "PCCL_SIGDUMP_FILE"}, "");

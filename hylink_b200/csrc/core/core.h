@@ -119,6 +119,13 @@ struct Config {
   int avg_bw_warmup;
   bool fast_only_bw_log;
   bool pcie_child_comms;
+  // --- host-side fault injection (tests): "copy_error@K", "stall_ms=V@K", optionally ",rank=R". The K-th
+  // transfer this rank's executor issues fails with a device error, or is held back for V milliseconds. Nothing is
+  // ever injected on a GPU: the failure is made where the host would have made the call.
+  int fault_rank;                // -1 = every rank
+  long fault_copy_error_at;      // 0 = off
+  long fault_stall_at;           // 0 = off
+  int fault_stall_ms;
   // --- diagnostics
   std::string trace_file;
   bool sigdump;

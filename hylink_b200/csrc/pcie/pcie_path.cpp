@@ -166,6 +166,7 @@ class PcieImpl {
   std::atomic<uint64_t> completed_door_{0};
   std::atomic<int> last_result_{hlSuccess};
   std::atomic<uint64_t> kernel_launches_{0}, copy_ops_{0};
+  long issued_ops_ = 0;  // transfers issued so far (executor thread only; drives host-side fault injection)
   std::map<std::string, std::shared_ptr<const Plan>> plans_;
   cudaEvent_t order_ev_ = nullptr;
   friend class PciePath;
@@ -741,6 +742,16 @@ hlResult_t PcieImpl::runWork(const Work& w) {
         const size_t node_len = std::min(slen, dlen);
         const size_t off = (size_t)k * geo.slice_bytes;
         const size_t len = off >= node_len ? 0 : std::min(geo.slice_bytes, node_len - off);
+        {
+          // host-side fault injection: the failure is made here, where the transfer would have been issued
+          const Config& cfg = Config::get();
+          if ((cfg.fault_copy_error_at || cfg.fault_stall_at) && (cfg.fault_rank < 0 || cfg.fault_rank == rank_)) {
+            const long op_index = ++issued_ops_;
+            if (op_index == cfg.fault_stall_at) std::this_thread::sleep_for(std::chrono::milliseconds(cfg.fault_stall_ms));
+            if (op_index == cfg.fault_copy_error_at)
+              return fail(hlDeviceError, "%s slice: injected failure of transfer %ld (HYLINK_FAULT_INJECT)", ir::opName(n.op), op_index);
+          }
+        }
         InFlight f;
         f.node_slot = (int)i;
         f.t0_ns = nowNs();
