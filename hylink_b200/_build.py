@@ -162,6 +162,34 @@ def build_tools(verbose: bool = False) -> Path:
     return target
 
 
+def build_sanitized(kind: str = "thread", verbose: bool = False) -> Path:
+    """Host code under ``-fsanitize=thread`` or ``address``: a second copy of the library and of ``hl_perf`` in
+    ``hylink_b200/build/san_<kind>/`` (device objects are reused unchanged). Run the tool there with
+    ``--device host`` to check the control plane, the executor and the worker pool for races or bad accesses."""
+    assert kind in ("thread", "address")
+    build_core(verbose)  # device objects come from the regular build
+    out = ROOT / "build" / f"san_{kind}"
+    out.mkdir(parents=True, exist_ok=True)
+    hdr = _newest_header()
+    flags = [f"-fsanitize={kind}", "-O1", "-g", "-fno-omit-frame-pointer", "-DHL_BUILDING=1"]
+    srcs = [s for s in core_sources() if s.suffix == ".cpp"]
+    objs = [out / (s.relative_to(CSRC).as_posix().replace("/", "_") + ".o") for s in srcs]
+    with cf.ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
+        list(ex.map(lambda so: _compile(so[0], so[1], hdr, flags), zip(srcs, objs)))
+    dev_objs = [OBJ / (s.relative_to(CSRC).as_posix().replace("/", "_") + ".o") for s in core_sources() if s.suffix == ".cu"]
+    lib = out / "libhylink_b200.so"
+    _run([NVCC, *ARCH_FLAGS, "-shared", "-o", str(lib), *map(str, objs), *map(str, dev_objs), "-cudart", "static",
+          "-Xcompiler", f"-fsanitize={kind}", "-lpthread", "-ldl", "-lrt"])
+    tool_obj = out / "hl_perf.o"
+    _compile(CSRC / "tools" / "hl_perf.cpp", tool_obj, hdr, flags)
+    tool = out / "hl_perf"
+    _run(["g++", f"-fsanitize={kind}", "-o", str(tool), str(tool_obj), "-L", str(out), "-lhylink_b200", "-Wl,-rpath,$ORIGIN",
+          "-L", str(CUDA_HOME / "lib64"), "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+    if verbose:
+        print("built", tool)
+    return tool
+
+
 def build_all(verbose: bool = False) -> None:
     build_core(verbose)
     build_nccl_shim(verbose)
@@ -170,5 +198,8 @@ def build_all(verbose: bool = False) -> None:
 
 
 if __name__ == "__main__":
+    if len(sys.argv) > 2 and sys.argv[1] == "--sanitize":
+        print(build_sanitized(sys.argv[2], verbose=True))
+        sys.exit(0)
     build_all(verbose=True)
     print("ok")
