@@ -114,6 +114,10 @@ _sig("hlCommDrain", _i, _vp)
 _sig("hlHostReduce", _i, _vp, _vp, _vp, _sz, _i, _i, _i)
 _sig("hlHostCopy", None, _vp, _vp, _sz, _i)
 _sig("hlHostSimdLevel", _i)
+_sig("hlCommKernelTimeline", _i, _vp, _u64p, C.POINTER(_sz))
+_sig("hlEmuKernelTimeline", _i, _vp, _i, _u64p, C.POINTER(_sz))
+_sig("hlNvlStageAccess", _i, _vp, _i, _sz, _vp, _sz)
+_sig("hlNvlStageBytes", _sz, _vp)
 _sig("hlNvlLinkProbe", _i, _vp, _i, _i, _i, _i, _i, _sz, _vp)
 _sig("hlHostBench", _i, _i, _sz, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_double), C.POINTER(C.c_double))
 _sig("hlHostNumaNodes", _i)

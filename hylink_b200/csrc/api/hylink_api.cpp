@@ -392,6 +392,22 @@ hlResult_t hlBarrier(hlComm_t comm, hlStream_t stream) {
   return comm->nvl->barrier((cudaStream_t)stream);
 }
 
+size_t hlNvlStageBytes(hlComm_t comm) { return (comm && comm->nvl) ? comm->nvl->stageBytes() : 0; }
+
+hlResult_t hlNvlStageAccess(hlComm_t comm, int write, size_t offset, void* host, size_t bytes) {
+  HL_CHECK(precheck(comm));
+  std::lock_guard<std::mutex> lk(comm->mu);
+  if (comm->host_device || !comm->nvl) return fail(hlUnsupported, "stage access needs the NVLink path");
+  return comm->nvl->stageAccess(write != 0, offset, host, bytes);
+}
+
+hlResult_t hlCommKernelTimeline(hlComm_t comm, uint64_t* out, size_t* words) {
+  HL_CHECK(precheck(comm));
+  std::lock_guard<std::mutex> lk(comm->mu);
+  if (comm->host_device || !comm->nvl) return fail(hlUnsupported, "the kernel timeline needs the NVLink path");
+  return comm->nvl->readTimeline(0, out, words);
+}
+
 hlResult_t hlNvlLinkProbe(hlComm_t comm, int mode, int blocks, int threads, int unroll, int layout, size_t bytes, hlStream_t stream) {
   HL_CHECK(precheck(comm));
   std::lock_guard<std::mutex> lk(comm->mu);
@@ -504,6 +520,10 @@ hlResult_t hlEmuStatus(hlEmu_t e, int i, uint64_t* code, uint64_t* detail, uint6
   if (!e || i < 0 || i >= e->path->nranks() || !code) return hlInvalidArgument;
   *code = e->path->deviceStatus(i, detail, block);
   return hlSuccess;
+}
+hlResult_t hlEmuKernelTimeline(hlEmu_t e, int i, uint64_t* out, size_t* words) {
+  if (!e) return hlInvalidArgument;
+  return e->path->readTimeline(i, out, words);
 }
 hlResult_t hlEmuReset(hlEmu_t e) { return e ? e->path->resetAfterError() : hlInvalidArgument; }
 hlResult_t hlEmuLaunches(hlEmu_t e, uint64_t* n) {

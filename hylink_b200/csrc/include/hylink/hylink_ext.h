@@ -56,12 +56,28 @@ hlResult_t hlSubmitIr(hlComm_t comm, const char* xml, const void* send, void* re
                       int send_segs, int recv_segs, hlDataType_t t, hlRedOp_t op, hlStream_t stream);
 hlResult_t hlCommNumaPattern(hlComm_t comm, char* buf, size_t* len);
 
+/* ---- kernel timeline ---------------------------------------------------------
+ * With HYLINK_KERNEL_TIMELINE=1 at communicator creation every NVLink-path kernel records, for its first 148 CTAs,
+ * %globaltimer at entry, at arrival at and release from each cross-GPU barrier, and at exit, in a ring of the last 16
+ * launches. Returns the ring (words; call with out == NULL for the length): stamps [call][cta][8], then 4 words per
+ * call (flag base, kind << 32 | CTAs, element count, 0). Synchronises the device. */
+hlResult_t hlCommKernelTimeline(hlComm_t comm, uint64_t* out, size_t* words);
+/* Same for emulated rank i of a single-GPU group. */
+hlResult_t hlEmuKernelTimeline(hlEmu_t e, int i, uint64_t* out, size_t* words);
+
 /* ---- link probe -------------------------------------------------------------
  * Copies `bytes` between the first half of this rank's staging region and the second half of the next rank's with a
  * bare kernel of the given shape. mode: 0 push (local load, peer store), 1 pull (peer load, local store), 2 local
  * copy, 3 peer stores only, 4 peer loads only. layout: 0 grid-strided, 1 one contiguous range per CTA. unroll: 2, 4,
  * 8 (16 up to 512 threads). Waits on nothing; time it with events on `stream`. */
 hlResult_t hlNvlLinkProbe(hlComm_t comm, int mode, int blocks, int threads, int unroll, int layout, size_t bytes, hlStream_t stream);
+/* Modes 5 (to the peer) and 6 (local) run the copy on the bulk-copy engine instead: one thread per CTA drives a
+ * ring of 8 shared-memory tiles with asynchronous bulk loads and stores; `threads` then gives the tile size in
+ * bytes (1 KiB..24 KiB, a multiple of 128), `unroll` and `layout` are ignored. */
+/* Test aid: copies between host memory and this rank's staging region at `offset` (the probe's source is the first
+ * half of the region, its destination the second half; hlNvlStageBytes gives the size). */
+hlResult_t hlNvlStageAccess(hlComm_t comm, int write, size_t offset, void* host, size_t bytes);
+size_t hlNvlStageBytes(hlComm_t comm);
 
 /* ---- host SIMD kernels ------------------------------------------------------ */
 int hlHostReduce(void* dst, const void* a, const void* b, size_t count, int dtype, int op, int level_cap);

@@ -192,6 +192,14 @@ __device__ __forceinline__ uint64_t globalTimerNs() {
   return t;
 }
 
+// Kernel timeline: thread 0 of the first HL_TL_BLOCKS CTAs records when it passes a phase boundary.
+__device__ __forceinline__ void timelineStamp(const HlCommDev& c, uint64_t seq, int phase) {
+  if (c.timeline != nullptr && threadIdx.x == 0 && blockIdx.x < HL_TL_BLOCKS) {
+    const uint64_t slot = (seq / HL_SEQ_STRIDE) % HL_TL_CALLS;
+    c.timeline[(slot * HL_TL_BLOCKS + blockIdx.x) * HL_TL_PHASES + phase] = globalTimerNs();
+  }
+}
+
 // Uniform entry: a poisoned communicator (an earlier wait ran out) makes every
 // later kernel a no-op instead of a second hang candidate. The call's flag
 // bases are read here from device memory rather than passed by the host, so a
@@ -208,6 +216,16 @@ __device__ __forceinline__ bool entryOk(const HlCommDev& c, HlCallArgs& a) {
   __syncthreads();
   a.seq = s_seq[0];
   a.pipe_seq = s_seq[1];
+  if (c.timeline != nullptr && threadIdx.x == 0) {
+    if (blockIdx.x == 0) {
+      uint64_t* meta = c.timeline + (size_t)HL_TL_CALLS * HL_TL_BLOCKS * HL_TL_PHASES + ((a.seq / HL_SEQ_STRIDE) % HL_TL_CALLS) * 4;
+      meta[0] = a.seq;
+      meta[1] = ((uint64_t)(uint32_t)a.kind << 32) | gridDim.x;
+      meta[2] = a.count;
+      meta[3] = 0;
+    }
+    timelineStamp(c, a.seq, 0);
+  }
   return s_entry != 0;
 }
 
@@ -217,6 +235,7 @@ __device__ __forceinline__ bool entryOk(const HlCommDev& c, HlCallArgs& a) {
 __device__ __forceinline__ void callDone(const HlCommDev& c, uint64_t pipe_tiles) {
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (c.timeline != nullptr) timelineStamp(c, reinterpret_cast<volatile uint64_t*>(c.seq_words)[0], 7);  // still this call's base
     __threadfence();
     const unsigned long long prev = atomicAdd(reinterpret_cast<unsigned long long*>(c.seq_words + 2), 1ull);
     if (prev + 1 == gridDim.x) {
@@ -237,6 +256,7 @@ __device__ __forceinline__ bool blockBarrier(const HlCommDev& c, uint64_t target
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();  // also orders every thread's earlier accesses before the signal below
+  if (step >= 1 && step <= 3) timelineStamp(c, target, 2 * step - 1);  // target / HL_SEQ_STRIDE == base / HL_SEQ_STRIDE
   const int t = threadIdx.x;
   if (t < c.nranks) {
     // st.release.sys orders this thread's earlier accesses — and, through the
@@ -268,6 +288,7 @@ __device__ __forceinline__ bool blockBarrier(const HlCommDev& c, uint64_t target
     }
   }
   __syncthreads();
+  if (step >= 1 && step <= 3) timelineStamp(c, target, 2 * step);
   return s_ok != 0;
 }
 

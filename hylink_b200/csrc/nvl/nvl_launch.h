@@ -33,6 +33,9 @@ struct ReduceLandingArgs {
   int op;
   float scale;
 };
+// The same copy through the bulk-copy engine: one thread per CTA, a ring of shared-memory tiles of `tile_bytes`.
+hlResult_t launchLinkProbeBulk(const HlCommDev* dcomm, int to_peer, int blocks, uint32_t tile_bytes, uint64_t bytes, uint64_t dst_off_bytes,
+                               int peer, cudaStream_t stream);
 hlResult_t launchReduceLanding(const ReduceLandingArgs& a, int blocks, cudaStream_t stream);
 hlResult_t prepareReduceLanding();
 

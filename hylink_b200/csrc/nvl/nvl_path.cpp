@@ -17,6 +17,7 @@ NvlPath::~NvlPath() {
   if (dcomm_) cudaFree(dcomm_);
   if (abort_dev_) cudaFree(abort_dev_);
   if (seq_dev_) cudaFree(seq_dev_);
+  if (timeline_dev_) cudaFree(timeline_dev_);
   if (status_host_) cudaFreeHost(status_host_);
   if (emu_) {
     for (int q = 0; q < nranks_; ++q)
@@ -38,6 +39,10 @@ hlResult_t NvlPath::finishInit(int timeout_ms) {
   HL_CUDA(cudaMemset(abort_dev_, 0, sizeof(uint32_t) * 16 * nl));
   HL_CUDA(cudaMalloc((void**)&seq_dev_, sizeof(uint64_t) * 8 * nl));
   HL_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint64_t) * 8 * nl));
+  if (envBool({"HYLINK_KERNEL_TIMELINE"}, false)) {
+    HL_CUDA(cudaMalloc((void**)&timeline_dev_, sizeof(uint64_t) * HL_TL_WORDS * nl));
+    HL_CUDA(cudaMemset(timeline_dev_, 0, sizeof(uint64_t) * HL_TL_WORDS * nl));
+  }
   HlCommDev h[HL_MAX_RANKS];
   memset(h, 0, sizeof(h));
   for (int i = 0; i < nl; ++i) {
@@ -54,6 +59,7 @@ hlResult_t NvlPath::finishInit(int timeout_ms) {
     c.status = status_dev + 8 * i;
     c.abort_word = abort_dev_ + 16 * i;
     c.seq_words = seq_dev_ + 8 * i;
+    c.timeline = timeline_dev_ ? timeline_dev_ + (size_t)HL_TL_WORDS * i : nullptr;
     c.stage_bytes = stage_bytes_;
     c.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
   }
@@ -179,12 +185,42 @@ int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool dete
   return hlAlgoPush;  // peer pointers: stores only (falls back to the staged two-shot when the call converts types)
 }
 
+hlResult_t NvlPath::stageAccess(bool write, size_t offset, void* host, size_t bytes) {
+  if (emu_) return fail(hlUnsupported, "stage access needs a real communicator");
+  if (!host || offset + bytes > stage_bytes_) return fail(hlInvalidArgument, "stage access out of range");
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CUDA(cudaDeviceSynchronize());
+  char* p = (char*)region_.ptr[rank_] + offset;
+  HL_CUDA(write ? cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice) : cudaMemcpy(host, p, bytes, cudaMemcpyDeviceToHost));
+  return hlSuccess;
+}
+
+hlResult_t NvlPath::readTimeline(int local_rank, uint64_t* out, size_t* words) {
+  if (!words) return fail(hlInvalidArgument, "timeline: null length");
+  if (!timeline_dev_) return fail(hlUnsupported, "the kernel timeline is off (HYLINK_KERNEL_TIMELINE=1 before the communicator is created)");
+  if (local_rank < 0 || local_rank >= localRanks()) return fail(hlInvalidArgument, "timeline: bad local rank %d", local_rank);
+  if (!out || *words < (size_t)HL_TL_WORDS) {
+    *words = HL_TL_WORDS;
+    return out ? fail(hlInvalidArgument, "timeline: buffer too small") : hlSuccess;
+  }
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CUDA(cudaDeviceSynchronize());
+  HL_CUDA(cudaMemcpy(out, timeline_dev_ + (size_t)HL_TL_WORDS * local_rank, sizeof(uint64_t) * HL_TL_WORDS, cudaMemcpyDeviceToHost));
+  *words = HL_TL_WORDS;
+  return hlSuccess;
+}
+
 hlResult_t NvlPath::linkProbe(int mode, int blocks, int threads, int unroll, int layout, size_t bytes, cudaStream_t s) {
   if (emu_) return fail(hlUnsupported, "link probe needs a real communicator");
-  if (nranks_ < 2 && mode != 2) return fail(hlInvalidArgument, "link probe needs a peer");
+  if (nranks_ < 2 && mode != 2 && mode != 6) return fail(hlInvalidArgument, "link probe needs a peer");
   const size_t half = stage_bytes_ / 2 / 16 * 16;
   if (bytes < 16 || bytes > half) return fail(hlInvalidArgument, "link probe: %zu bytes exceed half of the staging region (%zu)", bytes, half);
   HL_CHECK(orderAfterPrevious(s));
+  if (mode == 5 || mode == 6) {  // bulk-copy engine: 5 to the peer, 6 local; `threads` carries the tile size in bytes
+    HL_CHECK(nvl::launchLinkProbeBulk(dcomm_, mode == 5, blocks, (uint32_t)threads, bytes / 16 * 16, half, (rank_ + 1) % nranks_, s));
+    ++launches_;
+    return hlSuccess;
+  }
   HL_CHECK(nvl::launchLinkProbe(dcomm_, mode, blocks, threads, unroll, layout, bytes / 16, half / 16, (rank_ + 1) % nranks_, s));
   ++launches_;
   return hlSuccess;
@@ -253,6 +289,7 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       a.out_dt = c.out_dt;
       a.root = c.root;
       a.int_div = (c.op == hlAvg) ? nranks_ : 0;
+      a.kind = kind;
     }
     const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls ? nranks_ : 1);
     int blocks = blocksFor(kind, wire_bytes, c.max_blocks);

@@ -63,6 +63,11 @@ class NvlPath {
   // of the next rank's (direction and launch shape by argument). Real paths only.
   hlResult_t linkProbe(int mode, int blocks, int threads, int unroll, int layout, size_t bytes, cudaStream_t s);
 
+  // Test aid of the link probe: host copy into / out of this rank's staging region (synchronises the device).
+  hlResult_t stageAccess(bool write, size_t offset, void* host, size_t bytes);
+  // Copies the kernel timeline ring of local rank i (HL_TL_WORDS words; layout in nvl_types.h) after a device
+  // synchronize. With out == nullptr only the needed length is returned.
+  hlResult_t readTimeline(int local_rank, uint64_t* out, size_t* words);
   // Device status of local rank i: HL_DEV_OK or the code a kernel recorded.
   uint64_t deviceStatus(int i = 0, uint64_t* detail = nullptr, uint64_t* block = nullptr) const;
   // Clears the poison after a recorded timeout (all ranks, collectively, with
@@ -90,6 +95,7 @@ class NvlPath {
   HlCommDev* dcomm_ = nullptr;     // device array: 1 entry (real) or nranks (emu)
   uint64_t* status_host_ = nullptr; // pinned, mapped; 8 words per local rank
   uint32_t* abort_dev_ = nullptr;   // one word per local rank
+  uint64_t* timeline_dev_ = nullptr;  // kernel timeline ring per local rank, null when off
   uint64_t* seq_dev_ = nullptr;    // per local rank: flag base, tile base, finished-CTA counter (advanced by the kernels)
   uint64_t launches_ = 0;
   cudaEvent_t order_ev_ = nullptr;

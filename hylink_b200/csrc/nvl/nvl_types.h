@@ -8,6 +8,14 @@
 #define HL_NVL_THREADS 512
 #define HL_SEQ_STRIDE 4       // flag values consumed per collective call
 #define HL_FLAG_KINDS 3       // 0: block barriers; 1, 2: tile hand-offs of the pipelined kernels
+// Kernel timeline (off unless the communicator was created with it): a ring of the last HL_TL_CALLS launches, for
+// the first HL_TL_BLOCKS CTAs of each, HL_TL_PHASES %globaltimer stamps: 0 entry, 2k-1 / 2k arrival at / release
+// from the k-th cross-GPU barrier (k = 1..3), 7 exit. Behind the stamps, 4 words per call: flag base, kernel kind
+// << 32 | CTAs, element count, 0.
+#define HL_TL_CALLS 16
+#define HL_TL_BLOCKS 148
+#define HL_TL_PHASES 8
+#define HL_TL_WORDS (HL_TL_CALLS * HL_TL_BLOCKS * HL_TL_PHASES + HL_TL_CALLS * 4)
 
 // Device status codes written by a kernel whose bounded wait ran out.
 #define HL_DEV_OK 0
@@ -32,6 +40,7 @@ struct HlCommDev {
                                    // call, [2] CTAs of the running call that have finished
   uint64_t stage_bytes;
   uint64_t timeout_ns;
+  uint64_t* timeline;              // device ring of HL_TL_WORDS words, null when the timeline is off
 };
 
 // Per-call arguments (by value in the launch).
@@ -50,6 +59,8 @@ struct HlCallArgs {
   int int_div;              // integer types: divide the sum (hlAvg), 0 = off
   uint64_t pipe_seq;        // pipelined kernels (filled in on the device): tile k of a block is announced as pipe_seq + k + 1
   uint64_t tile_packets;    // pipelined kernels: 16-byte packets of one shard handled per tile
+  int kind;                 // HlNvlKernel, recorded in the kernel timeline
+  int pad0;
 };
 
 // One argument block per emulated rank: on a single GPU the N ranks of a test

@@ -55,6 +55,16 @@ class EmuGroup:
                                   out_seg_stride, in_dt, out_dt, wire_dt, OPS[op], scale, root, ALGOS[algo],
                                   max_blocks, C.c_void_p(stream)), f"emu {kind}")
 
+    def kernel_timeline(self, i: int = 0):
+        """Decoded kernel timeline of emulated rank ``i`` (needs ``HYLINK_KERNEL_TIMELINE=1`` when the group is made)."""
+        from ..utils.kernel_timeline import decode
+
+        n = C.c_size_t(0)
+        check(lib.hlEmuKernelTimeline(self._h, i, None, C.byref(n)), "hlEmuKernelTimeline")
+        buf = (C.c_uint64 * n.value)()
+        check(lib.hlEmuKernelTimeline(self._h, i, buf, C.byref(n)), "hlEmuKernelTimeline")
+        return decode(list(buf))
+
     def set_active_ranks(self, k: int):
         check(lib.hlEmuSetActiveRanks(self._h, k), "hlEmuSetActiveRanks")
 

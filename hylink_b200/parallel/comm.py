@@ -118,6 +118,16 @@ class Communicator:
         check(lib.hlCommGetAsyncError(self._h, C.byref(e)), "hlCommGetAsyncError")
         return e.value
 
+    def kernel_timeline(self):
+        """Decoded kernel timeline (needs ``HYLINK_KERNEL_TIMELINE=1`` when the communicator is made)."""
+        from ..utils.kernel_timeline import decode
+
+        n = C.c_size_t(0)
+        check(lib.hlCommKernelTimeline(self._h, None, C.byref(n)), "hlCommKernelTimeline")
+        buf = (C.c_uint64 * n.value)()
+        check(lib.hlCommKernelTimeline(self._h, buf, C.byref(n)), "hlCommKernelTimeline")
+        return decode(list(buf))
+
     def dump_tuning(self) -> str:
         n = C.c_size_t(0)
         check(lib.hlCommDumpTuning(self._h, None, C.byref(n)), "hlCommDumpTuning")

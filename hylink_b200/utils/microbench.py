@@ -184,7 +184,7 @@ def p2p(args) -> int:
     comm = Communicator(rank, world, uid=box[0], device=local)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     align = torch.zeros(1, device=dev)
-    modes = {"push": 0, "pull": 1, "local": 2, "store": 3, "load": 4}
+    modes = {"push": 0, "pull": 1, "local": 2, "store": 3, "load": 4, "bulk": 5, "bulk-local": 6}
 
     def measure(mode, blocks, threads, unroll, layout):
         times = []
@@ -204,6 +204,11 @@ def p2p(args) -> int:
 
     grid = []
     for mode in args.modes.split(","):
+        if mode.startswith("bulk"):   # bulk-copy engine: the "threads" slot carries the tile size
+            for tile in [_size(v) for v in args.tiles.split(",")]:
+                for blocks in [int(v) for v in args.blocks.split(",")]:
+                    grid.append((mode, blocks, tile, 0, 0))
+            continue
         for threads in [int(v) for v in args.threads.split(",")]:
             for blocks in [int(v) for v in args.blocks.split(",")]:
                 for unroll in [int(v) for v in args.unroll.split(",")]:
@@ -214,8 +219,9 @@ def p2p(args) -> int:
     for mode, blocks, threads, unroll, layout in grid:
         ms = measure(mode, blocks, threads, unroll, layout)
         if rank == 0:
-            print(json.dumps({"bench": "p2p", "mode": mode, "blocks": blocks, "threads": threads, "unroll": unroll,
-                              "layout": "cta-contiguous" if layout else "grid-strided", "bytes": args.bytes, "world": world,
+            shape = ({"tile_bytes": threads} if mode.startswith("bulk") else
+                     {"threads": threads, "unroll": unroll, "layout": "cta-contiguous" if layout else "grid-strided"})
+            print(json.dumps({"bench": "p2p", "mode": mode, "blocks": blocks, **shape, "bytes": args.bytes, "world": world,
                               "ms": round(ms, 4), "GBs": round(args.bytes / ms / 1e6, 1),
                               "GBs_per_cta": round(args.bytes / ms / 1e6 / blocks, 2)}), flush=True)
     dist.barrier()
@@ -243,7 +249,8 @@ def main(argv=None) -> int:
     p.add_argument("--gemms", type=int, default=4)
     p = sub.add_parser("p2p")
     p.add_argument("--bytes", type=_size, default=256 << 20)
-    p.add_argument("--modes", default="push,pull,local,store,load")
+    p.add_argument("--modes", default="push,pull,local,store,load,bulk,bulk-local")
+    p.add_argument("--tiles", default="4K,8K,16K,24K", help="tile sizes of the bulk-copy-engine modes")
     p.add_argument("--blocks", default="16,37,74,148,296")
     p.add_argument("--threads", default="256,512,1024")
     p.add_argument("--unroll", default="4,8")

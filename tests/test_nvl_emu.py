@@ -336,3 +336,30 @@ def test_collectives_replay_from_a_cuda_graph():
     assert torch.equal(outs[0], _ordered_sum(ins, torch.float32))
     assert g.status(0)[0] == 0
     g.close()
+
+
+def test_kernel_timeline_records_phases_in_order(monkeypatch):
+    """With the timeline on, every CTA's stamps of a launch are monotonic: entry, barrier arrivals and releases, exit."""
+    from hylink_b200.utils.kernel_timeline import summarise
+
+    monkeypatch.setenv("HYLINK_KERNEL_TIMELINE", "1")
+    g = EmuGroup(2, stage_bytes=16 << 20)
+    try:
+        n = 1 << 20
+        ins = [torch.full((n,), float(r + 1), device="cuda", dtype=torch.bfloat16) for r in range(2)]
+        outs = [torch.empty_like(t) for t in ins]
+        for algo in ("push", "twoshot"):
+            g.run("all_reduce", ins, outs, n, algo=algo)
+        torch.cuda.synchronize()
+        assert float(outs[1][-1]) == 3.0
+        launches = g.kernel_timeline(0)
+        assert [l["kind"] for l in launches[-2:]] == ["allreduce_push", "allreduce_twoshot"]
+        for l in launches[-2:]:
+            assert l["count"] == n and l["blocks"] >= 1
+            for s in l["stamps"]:
+                taken = [v for v in (s[0], s[1], s[2], s[3], s[4], s[7]) if v]
+                assert len(taken) == 6 and taken == sorted(taken), s
+            summary = summarise(l)
+            assert summary["total_us"] > 0 and "entry->arrive1" in summary["phases"]
+    finally:
+        g.close()

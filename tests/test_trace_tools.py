@@ -93,3 +93,21 @@ def test_sweep_files_merge_into_one_table(tmp_path):
     rows = compare.write_sweep_tables(labels, table, str(tmp_path / "s.csv"), str(tmp_path / "s.md"))
     assert rows == [["allreduce", "bf16", 1 << 20, 2, 50.0, 30.0, 41.0, round(50 / 41, 3), round(30 / 41, 3)]]
     assert "nvlink_2gpu/NCCL" in (tmp_path / "s.md").read_text()
+
+
+def test_kernel_timeline_decoder_on_a_synthetic_ring():
+    from hylink_b200.utils import kernel_timeline as kt
+
+    words = [0] * (kt.TL_CALLS * kt.TL_BLOCKS * kt.TL_PHASES + kt.TL_CALLS * 4)
+    slot, blocks = 3, 2
+    meta = kt.TL_CALLS * kt.TL_BLOCKS * kt.TL_PHASES + 4 * slot
+    words[meta:meta + 4] = [12, (15 << 32) | blocks, 4096, 0]
+    for b in range(blocks):
+        base = (slot * kt.TL_BLOCKS + b) * kt.TL_PHASES
+        t0 = 1_000_000 + 100 * b
+        words[base:base + 8] = [t0, t0 + 5000, t0 + 6000, t0 + 9000, t0 + 9500, 0, 0, t0 + 12000]
+    launches = kt.decode(words)
+    assert len(launches) == 1 and launches[0]["kind"] == "allreduce_push" and launches[0]["blocks"] == 2
+    s = kt.summarise(launches[0])
+    assert s["phases"]["entry->arrive1"]["median_us"] == 5.0 and s["phases"]["leave2->exit"]["median_us"] == 2.5
+    assert s["entry_spread_us"] == 0.1 and s["total_us"] == 12.1
