@@ -186,11 +186,12 @@ int NvlPath::pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool dete
 }
 
 hlResult_t NvlPath::stageAccess(bool write, size_t offset, void* host, size_t bytes) {
-  if (emu_) return fail(hlUnsupported, "stage access needs a real communicator");
+  // a one-rank communicator is built on the single-device flavour of the path: its only staging region serves
+  if (emu_ && nranks_ > 1) return fail(hlUnsupported, "stage access needs a real communicator");
   if (!host || offset + bytes > stage_bytes_) return fail(hlInvalidArgument, "stage access out of range");
   HL_CUDA(cudaSetDevice(device_));
   HL_CUDA(cudaDeviceSynchronize());
-  char* p = (char*)region_.ptr[rank_] + offset;
+  char* p = (char*)(emu_ ? emu_mem_[0] : region_.ptr[rank_]) + offset;
   HL_CUDA(write ? cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice) : cudaMemcpy(host, p, bytes, cudaMemcpyDeviceToHost));
   return hlSuccess;
 }
@@ -211,7 +212,7 @@ hlResult_t NvlPath::readTimeline(int local_rank, uint64_t* out, size_t* words) {
 }
 
 hlResult_t NvlPath::linkProbe(int mode, int blocks, int threads, int unroll, int layout, size_t bytes, cudaStream_t s) {
-  if (emu_) return fail(hlUnsupported, "link probe needs a real communicator");
+  if (emu_ && nranks_ > 1) return fail(hlUnsupported, "link probe needs a real communicator");
   if (nranks_ < 2 && mode != 2 && mode != 6) return fail(hlInvalidArgument, "link probe needs a peer");
   const size_t half = stage_bytes_ / 2 / 16 * 16;
   if (bytes < 16 || bytes > half) return fail(hlInvalidArgument, "link probe: %zu bytes exceed half of the staging region (%zu)", bytes, half);

@@ -343,7 +343,7 @@ def test_kernel_timeline_records_phases_in_order(monkeypatch):
     from hylink_b200.utils.kernel_timeline import summarise
 
     monkeypatch.setenv("HYLINK_KERNEL_TIMELINE", "1")
-    g = EmuGroup(2, stage_bytes=16 << 20)
+    g = _group(2, stage_bytes=16 << 20)
     try:
         n = 1 << 20
         ins = [torch.full((n,), float(r + 1), device="cuda", dtype=torch.bfloat16) for r in range(2)]
