@@ -297,16 +297,19 @@ __device__ __forceinline__ void groupSync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-__device__ __forceinline__ void tileSignal(const HlCommDev& c, int kind, uint64_t value, int gtid) {
+// `lane` selects the flag word: the CTA index when the stages of a tile are warp groups of one CTA, the index of
+// the CTA triple (or pair) when they are CTAs of their own.
+__device__ __forceinline__ void tileSignal(const HlCommDev& c, int kind, uint64_t value, int gtid, unsigned lane) {
   if (gtid < c.nranks) {
-    stReleaseSys(c.flags[gtid] + ((size_t)kind * HL_MAX_BLOCKS + blockIdx.x) * HL_MAX_RANKS + c.rank, value);
+    stReleaseSys(c.flags[gtid] + ((size_t)kind * HL_MAX_BLOCKS + lane) * HL_MAX_RANKS + c.rank, value);
   }
 }
 
 // Returns through *abort_flag (shared memory) whether the wait was abandoned.
-__device__ __forceinline__ void tileWait(const HlCommDev& c, int kind, uint64_t value, int gtid, volatile int* abort_flag, int step) {
+__device__ __forceinline__ void tileWait(const HlCommDev& c, int kind, uint64_t value, int gtid, volatile int* abort_flag, int step,
+                                         unsigned lane) {
   if (gtid < c.nranks) {
-    const uint64_t* mine = c.flags[c.rank] + ((size_t)kind * HL_MAX_BLOCKS + blockIdx.x) * HL_MAX_RANKS + gtid;
+    const uint64_t* mine = c.flags[c.rank] + ((size_t)kind * HL_MAX_BLOCKS + lane) * HL_MAX_RANKS + gtid;
     uint64_t t0 = 0;
     uint32_t spins = 0;
     while (ldAcquireSys(mine) < value) {
@@ -459,9 +462,9 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
         }
       }
       groupSync(1, gthreads);
-      tileSignal(c, 1, target, gtid);
+      tileSignal(c, 1, target, gtid, blockIdx.x);
     } else if (role == 1) {
-      tileWait(c, 1, target, gtid, &s_abort, 1);
+      tileWait(c, 1, target, gtid, &s_abort, 1, blockIdx.x);
       groupSync(2, gthreads);
       if (s_abort) break;
       const uint64_t first = (uint64_t)r * sp + p0;
@@ -513,11 +516,11 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
       }
       if constexpr (kAllReduce) {
         groupSync(2, gthreads);
-        tileSignal(c, 2, target, gtid);
+        tileSignal(c, 2, target, gtid, blockIdx.x);
       }
     } else {
       if constexpr (kAllReduce) {
-        tileWait(c, 2, target, gtid, &s_abort, 2);
+        tileWait(c, 2, target, gtid, &s_abort, 2, blockIdx.x);
         groupSync(3, gthreads);
         if (s_abort) break;
         for (int s = 0; s < n; ++s) {
@@ -538,6 +541,104 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
     blockBarrier(c, a.seq + 1, 3);
   }
   callDone(c, (tiles + gridDim.x - 1) / gridDim.x);
+}
+
+// ------------------------------------------------------------------ pipelined push all-reduce / reduce-scatter, one CTA per stage
+// The stores-only scheme of kPush below, cut into tiles whose stages run at the same time on CTAs of their own.
+// Measured on the link (2 GPUs, both directions loaded): posted 16-byte stores from 16 to 37 CTAs already fill a
+// direction (~690 GB/s) and a fold is HBM-bound, so a stage gains nothing from more than a third of the SMs, while
+// the phases of kPush — push | wait | fold | wait | copy-out, each with the whole grid — leave the link idle for a
+// fifth (all-reduce) to a third (reduce-scatter) of the call. CTAs form lanes of three (all-reduce: push, fold,
+// copy-out) or two (reduce-scatter: push, fold); lane L handles tiles L, L + lanes, ...; its stages hand a tile
+// on — across GPUs — through the tile flag words [kind][lane][source rank], exactly as the warp groups of
+// kPipelined do. Nothing waits for space (staging holds the whole sliced message), so the only waits are for data.
+// Valid elements of a shard (all-reduce: it starts at element `shard_first` of the buffer) or of a segment
+// (reduce-scatter: `count` elements each) that fall into the tile of `tp` packets starting at packet p0.
+template <bool kAllReduce, int N>
+__device__ __forceinline__ uint64_t tileElems(uint64_t count, uint64_t shard_first, uint64_t p0, uint64_t tp) {
+  const uint64_t e0 = p0 * N;
+  const uint64_t g = kAllReduce ? shard_first + e0 : e0;
+  return g >= count ? 0 : (count - g < tp * N ? count - g : tp * N);
+}
+
+// The fold of one tile of the owned shard. MR bounds the rank count the unrolled source loop is compiled for; one
+// kernel carries one such variant (three of them side by side push the register allocator into local memory).
+template <typename W, bool kAllReduce, int MR>
+__device__ __forceinline__ void foldStage(const HlCommDev& c, const HlCallArgs& a, uint64_t in_stride, uint64_t sp, uint64_t p0, uint64_t tp,
+                                       uint64_t res_off, const Ctx& x) {
+  constexpr int N = Packet<W>::N;
+  const int r = c.rank;
+  const uint64_t cnt = tileElems<kAllReduce, N>(a.count, (uint64_t)r * in_stride, p0, tp);
+  const W* own = reinterpret_cast<const W*>(a.in) + (uint64_t)r * in_stride + p0 * N;
+  W* res = reinterpret_cast<W*>(a.out) + (kAllReduce ? (uint64_t)r * in_stride : 0) + p0 * N;
+  const uint64_t tpk = (cnt + N - 1) / N;
+  constexpr int U = MR <= 2 ? 6 : (MR <= 4 ? 3 : 2);   // about a dozen landed packets per thread in flight
+  foldTile<W, W, W, kAllReduce, U, MR>(c, a, own, cnt, res, cnt, sp, p0, tpk, res_off, x);
+}
+
+template <typename W, bool kAllReduce, int MR>
+__global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  constexpr int N = Packet<W>::N;
+  constexpr unsigned kRoles = kAllReduce ? 3 : 2;
+  const int n = c.nranks, r = c.rank;
+  const uint64_t np = (a.count + N - 1) / N;
+  const uint64_t sp = kAllReduce ? (np + n - 1) / n : np;   // packets per shard (all-reduce) or per segment (reduce-scatter)
+  const uint64_t tps = a.tile_packets;
+  const uint64_t tiles = (sp + tps - 1) / tps;
+  const uint64_t in_stride = kAllReduce ? sp * N : a.in_seg_stride;
+  const uint64_t res_off = sp * (uint64_t)n;                // results live behind the n slots
+  const unsigned role = blockIdx.x % kRoles, lane = blockIdx.x / kRoles, lanes = gridDim.x / kRoles;
+  const int gtid = (int)threadIdx.x;
+  Ctx x;
+  x.g0 = threadIdx.x;
+  x.gstride = blockDim.x;
+  const W* in = reinterpret_cast<const W*>(a.in);
+  W* out = reinterpret_cast<W*>(a.out);
+  uint64_t k = 0;
+  for (uint64_t t = lane; lane < lanes && t < tiles; t += lanes, ++k) {
+    const uint64_t target = a.pipe_seq + k + 1;
+    const uint64_t p0 = t * tps;
+    const uint64_t tp = sp - p0 < tps ? sp - p0 : tps;
+    if (role == 0) {
+      for (int k2 = 1; k2 < n; ++k2) {
+        const int s = (r + k2) % n;   // start at the next rank: the owners are loaded evenly
+        pushTile<W, W, kPipeCopyUnroll>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp + p0, in + (uint64_t)s * in_stride + p0 * N,
+                                    tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
+      }
+      __syncthreads();
+      tileSignal(c, 1, target, gtid, lane);
+    } else if (role == 1) {
+      tileWait(c, 1, target, gtid, &s_abort, 1, lane);
+      __syncthreads();
+      if (s_abort) break;
+      foldStage<W, kAllReduce, MR>(c, a, in_stride, sp, p0, tp, res_off, x);
+      if constexpr (kAllReduce) {
+        __syncthreads();
+        tileSignal(c, 2, target, gtid, lane);
+      }
+    } else {
+      tileWait(c, 2, target, gtid, &s_abort, 2, lane);
+      __syncthreads();
+      if (s_abort) break;
+      const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
+      for (int k2 = 1; k2 < n; ++k2) {
+        const int s = (r + k2) % n;
+        segCopyOut<W, W, kPipeCopyUnroll>(out + (uint64_t)s * in_stride + p0 * N, mine + res_off + (uint64_t)s * sp + p0, tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
+      }
+    }
+  }
+  if constexpr (!kAllReduce) {
+    // a pusher of the next call may overwrite slots that a slower peer is still folding: nobody leaves before
+    // every peer's CTA of the same index is through
+    blockBarrier(c, a.seq + 1, 3);
+  }
+  callDone(c, lanes ? (tiles + lanes - 1) / lanes : 0);
 }
 
 // ------------------------------------------------------------------ push all-reduce / reduce-scatter over peer pointers
@@ -755,7 +856,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllToAll(const HlCommDev* com
 namespace nvl {
 
 template <typename W>
-static const void* pickKernelT(int kind) {
+static const void* pickKernelT(int kind, int nranks) {
   using namespace dev;
   switch (kind) {
     case kNvlAllReduceOneShot: return (const void*)kAllReduceOneShot<W>;
@@ -768,8 +869,10 @@ static const void* pickKernelT(int kind) {
     case kNvlBroadcastNvls: return (const void*)kBroadcast<W, true>;
     case kNvlAllReducePush: return (const void*)kPush<W, true>;
     case kNvlReduceScatterPush: return (const void*)kPush<W, false>;
-    case kNvlAllReducePipeP2p: return (const void*)kPipelined<W, false, true>;
-    case kNvlReduceScatterPipeP2p: return (const void*)kPipelined<W, false, false>;
+    case kNvlAllReducePipeP2p:   // one variant per rank-count class (the unrolled source loop of the fold)
+      return nranks <= 2 ? (const void*)kPipeCta<W, true, 2> : (nranks <= 4 ? (const void*)kPipeCta<W, true, 4> : (const void*)kPipeCta<W, true, HL_MAX_RANKS>);
+    case kNvlReduceScatterPipeP2p:
+      return nranks <= 2 ? (const void*)kPipeCta<W, false, 2> : (nranks <= 4 ? (const void*)kPipeCta<W, false, 4> : (const void*)kPipeCta<W, false, HL_MAX_RANKS>);
     default: break;
   }
   if constexpr (dev::IsFloatTrio<W>::value) {
@@ -784,19 +887,19 @@ static const void* pickKernelT(int kind) {
   return nullptr;
 }
 
-const void* kernelFor(int kind, int wire_dt) {
+const void* kernelFor(int kind, int wire_dt, int nranks) {
   if (kind == kNvlBarrier) return (const void*)dev::kBarrier;
   switch (wire_dt) {
-    case hlInt8: return pickKernelT<int8_t>(kind);
-    case hlUint8: return pickKernelT<uint8_t>(kind);
-    case hlInt32: return pickKernelT<int32_t>(kind);
-    case hlUint32: return pickKernelT<uint32_t>(kind);
-    case hlInt64: return pickKernelT<long long>(kind);
-    case hlUint64: return pickKernelT<unsigned long long>(kind);
-    case hlFloat16: return pickKernelT<__half>(kind);
-    case hlFloat32: return pickKernelT<float>(kind);
-    case hlFloat64: return pickKernelT<double>(kind);
-    case hlBfloat16: return pickKernelT<__nv_bfloat16>(kind);
+    case hlInt8: return pickKernelT<int8_t>(kind, nranks);
+    case hlUint8: return pickKernelT<uint8_t>(kind, nranks);
+    case hlInt32: return pickKernelT<int32_t>(kind, nranks);
+    case hlUint32: return pickKernelT<uint32_t>(kind, nranks);
+    case hlInt64: return pickKernelT<long long>(kind, nranks);
+    case hlUint64: return pickKernelT<unsigned long long>(kind, nranks);
+    case hlFloat16: return pickKernelT<__half>(kind, nranks);
+    case hlFloat32: return pickKernelT<float>(kind, nranks);
+    case hlFloat64: return pickKernelT<double>(kind, nranks);
+    case hlBfloat16: return pickKernelT<__nv_bfloat16>(kind, nranks);
     default: return nullptr;
   }
 }
@@ -825,13 +928,13 @@ const char* kernelName(int kind) {
 }
 
 hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCalls& calls, int emu_ranks, int blocks,
-                  cudaStream_t stream) {
-  const void* fn = kernelFor(kind, wire_dt);
+                  cudaStream_t stream, int nranks) {
+  const void* fn = kernelFor(kind, wire_dt, nranks);
   if (!fn) return fail(hlUnsupported, "no %s kernel for wire type %d", kernelName(kind), wire_dt);
   if (blocks < 1) blocks = 1;
   if (blocks > HL_MAX_BLOCKS) blocks = HL_MAX_BLOCKS;
   dim3 grid((unsigned)blocks, (unsigned)(emu_ranks > 1 ? emu_ranks : 1), 1);
-  const bool pipe = kind >= kNvlAllReducePipeP2p && kind <= kNvlReduceScatterPipeNvls;
+  const bool pipe = kind == kNvlAllReducePipeNvls || kind == kNvlReduceScatterPipeNvls;  // warp-group stages: 384 threads
   dim3 block(pipe ? dev::kPipeThreads : HL_NVL_THREADS, 1, 1);
   void* args[2] = {(void*)&dcomms, (void*)&calls};
   cudaError_t e;
@@ -858,11 +961,13 @@ hlResult_t prepareKernels() {
                               kNvlReduceScatterPush};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
-      const void* fn = kernelFor(k, dt);
-      if (!fn) continue;
-      cudaFuncAttributes at;
-      cudaError_t e = cudaFuncGetAttributes(&at, fn);
-      if (e != cudaSuccess) return fail(hlDeviceError, "cudaFuncGetAttributes: %s", cudaGetErrorString(e));
+      for (int nr : {2, 4, HL_MAX_RANKS}) {   // rank-count classes (only the pipelined push kernels differ by it)
+        const void* fn = kernelFor(k, dt, nr);
+        if (!fn) continue;
+        cudaFuncAttributes at;
+        cudaError_t e = cudaFuncGetAttributes(&at, fn);
+        if (e != cudaSuccess) return fail(hlDeviceError, "cudaFuncGetAttributes: %s", cudaGetErrorString(e));
+      }
       if (k == kNvlBarrier) break;
     }
   return hlSuccess;

@@ -9,11 +9,12 @@
 namespace hl {
 namespace nvl {
 
-const void* kernelFor(int kind, int wire_dt);
+// nranks picks the variant of the kernels that are compiled per rank-count class (<= 2, <= 4, <= 8).
+const void* kernelFor(int kind, int wire_dt, int nranks = HL_MAX_RANKS);
 const char* kernelName(int kind);
 // emu_ranks > 1: cooperative launch with one grid row per emulated rank.
 hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCalls& calls, int emu_ranks, int blocks,
-                  cudaStream_t stream);
+                  cudaStream_t stream, int nranks = HL_MAX_RANKS);
 hlResult_t prepareKernels();
 // Bare copy between this rank's staging and `peer`'s (see link_probe.cu); mode 0 push, 1 pull, 2 local, 3 stores
 // only, 4 loads only; `packets` 16-byte packets from offset 0 to offset dst_off.

@@ -301,16 +301,22 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       // 8192-packet tiles leave fewer than two tiles per CTA.
       const uint64_t np = (len + epp - 1) / epp;
       const uint64_t sp = pipe_ar ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;
-      uint64_t tps = (sp + (uint64_t)blocks * 8 - 1) / ((uint64_t)blocks * 8);
+      // Peer-pointer variants give every stage of a tile CTAs of its own (three for all-reduce: push, fold,
+      // copy-out; two for reduce-scatter); a "lane" is one such group and walks tiles lane, lane + lanes, ...
+      const bool cta_roles = kind == kNvlAllReducePipeP2p || kind == kNvlReduceScatterPipeP2p;
+      const int roles = !cta_roles ? 1 : (pipe_ar ? 3 : 2);
+      uint64_t lanes = std::max(1, blocks / roles);
+      uint64_t tps = (sp + lanes * 8 - 1) / (lanes * 8);
       tps = std::min<uint64_t>(8192, std::max<uint64_t>(256, (tps + 63) & ~(uint64_t)63));
       const char* forced = getenv("HYLINK_PIPE_TILE_PACKETS");
       if (forced) tps = std::max<uint64_t>(64, (uint64_t)atoll(forced) & ~(uint64_t)63);
       const uint64_t tiles = (sp + tps - 1) / tps;
-      blocks = (int)std::min<uint64_t>((uint64_t)blocks, tiles);
+      lanes = std::min<uint64_t>(lanes, tiles);
+      blocks = (int)lanes * roles;
       for (int i = 0; i < nl; ++i) calls.c[i].tile_packets = tps;
     }
     const int rows = emu_ ? emu_active_ : 1;
-    HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, rows, blocks, s));
+    HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, rows, blocks, s, nranks_));
     ++launches_;
     done += len;
   } while (done < c.count);
