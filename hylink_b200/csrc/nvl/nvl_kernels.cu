@@ -600,6 +600,18 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
   x.gstride = blockDim.x;
   const W* in = reinterpret_cast<const W*>(a.in);
   W* out = reinterpret_cast<W*>(a.out);
+  // Kernel timeline: thread 0 adds up what this CTA spent waiting for a tile, handing one on (the release store
+  // has to see the CTA's posted stores acknowledged) and working; the sums land in stamp slots 1 to 3 at exit.
+  const bool timed = c.timeline != nullptr && threadIdx.x == 0;
+  uint64_t t_wait = 0, t_hand = 0, t_mark = timed ? globalTimerNs() : 0, t_begin = t_mark;
+  auto lap = [&](uint64_t& sum) {
+    if (timed) {
+      const uint64_t now = globalTimerNs();
+      sum += now - t_mark;
+      t_mark = now;
+    }
+  };
+  uint64_t t_work = 0;
   uint64_t k = 0;
   for (uint64_t t = lane; lane < lanes && t < tiles; t += lanes, ++k) {
     const uint64_t target = a.pipe_seq + k + 1;
@@ -612,19 +624,25 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
                                     tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
       }
       __syncthreads();
+      lap(t_work);
       tileSignal(c, 1, target, gtid, lane);
+      lap(t_hand);
     } else if (role == 1) {
       tileWait(c, 1, target, gtid, &s_abort, 1, lane);
       __syncthreads();
+      lap(t_wait);
       if (s_abort) break;
       foldStage<W, kAllReduce, MR>(c, a, in_stride, sp, p0, tp, res_off, x);
       if constexpr (kAllReduce) {
         __syncthreads();
+        lap(t_work);
         tileSignal(c, 2, target, gtid, lane);
+        lap(t_hand);
       }
     } else {
       tileWait(c, 2, target, gtid, &s_abort, 2, lane);
       __syncthreads();
+      lap(t_wait);
       if (s_abort) break;
       const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
       for (int k2 = 1; k2 < n; ++k2) {
@@ -637,6 +655,16 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
     // a pusher of the next call may overwrite slots that a slower peer is still folding: nobody leaves before
     // every peer's CTA of the same index is through
     blockBarrier(c, a.seq + 1, 3);
+  }
+  if (timed && blockIdx.x < HL_TL_BLOCKS) {
+    lap(t_work);
+    // slots 1..3 hold entry + duration, so that the decoder's "time since entry" reads as the three sums;
+    // slot 4 carries the stage (0 push, 1 fold, 2 copy-out) the same way, in microseconds
+    uint64_t* st = c.timeline + (((a.seq / HL_SEQ_STRIDE) % HL_TL_CALLS) * HL_TL_BLOCKS + blockIdx.x) * HL_TL_PHASES;
+    st[1] = t_begin + t_wait;
+    st[2] = t_begin + t_hand;
+    st[3] = t_begin + t_work;
+    st[4] = t_begin + (uint64_t)role * 1000;
   }
   callDone(c, lanes ? (tiles + lanes - 1) / lanes : 0);
 }

@@ -47,6 +47,8 @@ def decode(words):
 def summarise(launch):
     """Median, over the recorded CTAs, of the time between consecutive stamps that the kernel took (microseconds)."""
     st = launch["stamps"]
+    if launch["kind"].endswith("pipelined_p2p"):
+        return _summarise_lanes(launch)
     entry0 = min(s[0] for s in st if s[0])
     used = [p for p in range(TL_PHASES) if all(s[p] >= s[0] and s[p] != 0 for s in st)]
     # a stamp of an earlier launch in the same ring slot is older than this launch's entry: the filter above drops it
@@ -59,6 +61,24 @@ def summarise(launch):
     return {"kind": launch["kind"], "blocks": launch["blocks"], "count": launch["count"],
             "entry_spread_us": round((max(s[0] for s in st) - entry0) / 1e3, 2),
             "total_us": round(max(total), 2), "phases": phases}
+
+
+def _summarise_lanes(launch):
+    """The lane kernels record sums instead of boundaries: per CTA, the time spent waiting for tiles, handing tiles
+    on and working, and which stage the CTA ran (slots 1-4 as entry + value)."""
+    roles = {0: "push", 1: "fold", 2: "copy-out"}
+    per_role = {}
+    for s in launch["stamps"]:
+        if not s[0] or not s[7]:
+            continue
+        role = roles.get(round((s[4] - s[0]) / 1000), "?")
+        per_role.setdefault(role, []).append(((s[1] - s[0]) / 1e3, (s[2] - s[0]) / 1e3, (s[3] - s[0]) / 1e3, (s[7] - s[0]) / 1e3))
+    out = {"kind": launch["kind"], "blocks": launch["blocks"], "count": launch["count"], "stages": {}}
+    for role, rows in per_role.items():
+        med = lambda i: round(statistics.median(r[i] for r in rows), 2)  # noqa: E731
+        out["stages"][role] = {"ctas": len(rows), "waiting_us": med(0), "handing_on_us": med(1), "working_us": med(2), "total_us": med(3)}
+    out["total_us"] = round(max(r[3] for rows in per_role.values() for r in rows), 2) if per_role else 0.0
+    return out
 
 
 def main(argv=None) -> int:

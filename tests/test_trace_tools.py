@@ -111,3 +111,18 @@ def test_kernel_timeline_decoder_on_a_synthetic_ring():
     s = kt.summarise(launches[0])
     assert s["phases"]["entry->arrive1"]["median_us"] == 5.0 and s["phases"]["leave2->exit"]["median_us"] == 2.5
     assert s["entry_spread_us"] == 0.1 and s["total_us"] == 12.1
+
+
+def test_kernel_timeline_decoder_reads_lane_kernel_sums():
+    from hylink_b200.utils import kernel_timeline as kt
+
+    words = [0] * (kt.TL_CALLS * kt.TL_BLOCKS * kt.TL_PHASES + kt.TL_CALLS * 4)
+    meta = kt.TL_CALLS * kt.TL_BLOCKS * kt.TL_PHASES
+    words[meta:meta + 4] = [0, (13 << 32) | 4, 1 << 20, 0]   # reducescatter_pipelined_p2p, 4 CTAs = 2 lanes of push + fold
+    for b in range(4):
+        t0, role = 5_000_000, b % 2
+        base = b * kt.TL_PHASES
+        words[base:base + 8] = [t0, t0 + (3000 if role else 0), t0 + (0 if role else 40000), t0 + 60000, t0 + role * 1000, 0, 0, t0 + 100000]
+    s = kt.summarise(kt.decode(words)[0])
+    assert s["stages"]["push"] == {"ctas": 2, "waiting_us": 0.0, "handing_on_us": 40.0, "working_us": 60.0, "total_us": 100.0}
+    assert s["stages"]["fold"]["waiting_us"] == 3.0 and s["total_us"] == 100.0
