@@ -576,13 +576,27 @@ __device__ __forceinline__ void foldStage(const HlCommDev& c, const HlCallArgs& 
   foldTile<W, W, W, kAllReduce, U, MR>(c, a, own, cnt, res, cnt, sp, p0, tpk, res_off, x);
 }
 
+__device__ __forceinline__ void barArrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Hand-off without a stall. The release store that announces a tile has to see the CTA's posted stores acknowledged;
+// under load that takes longer than pushing a 128 KiB tile (measured: 8 us against 5 us), and a CTA that does it
+// itself idles its share of the link meanwhile. Stages that announce tiles therefore give up their last warp as a
+// signaller: the working warps arrive on named barrier 1 when a tile's stores are issued and go on with the next
+// tile; the signaller picks the tile up there, acknowledges the pick-up on named barrier 2 (the workers wait for
+// that before they arrive again, so the two never run more than one tile apart) and only then pays for the release.
 template <typename W, bool kAllReduce, int MR>
 __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
   HlCallArgs a = calls.c[blockIdx.y];
   if (!entryOk(c, a)) return;
   __shared__ int s_abort;
-  if (threadIdx.x == 0) s_abort = 0;
+  __shared__ unsigned long long s_stop_at;   // tile (ordinal within this lane) at which the workers gave up
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    s_stop_at = ~0ull;
+  }
   __syncthreads();
   constexpr int N = Packet<W>::N;
   constexpr unsigned kRoles = kAllReduce ? 3 : 2;
@@ -594,16 +608,20 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
   const uint64_t in_stride = kAllReduce ? sp * N : a.in_seg_stride;
   const uint64_t res_off = sp * (uint64_t)n;                // results live behind the n slots
   const unsigned role = blockIdx.x % kRoles, lane = blockIdx.x / kRoles, lanes = gridDim.x / kRoles;
+  const bool announces = role == 0 || (kAllReduce && role == 1);
+  const int workers = announces ? (int)blockDim.x - 32 : (int)blockDim.x;
+  const bool signaller = announces && (int)threadIdx.x >= workers;
   const int gtid = (int)threadIdx.x;
+  const uint64_t my_tiles = lane < lanes && lane < tiles ? (tiles - lane + lanes - 1) / lanes : 0;
   Ctx x;
   x.g0 = threadIdx.x;
-  x.gstride = blockDim.x;
+  x.gstride = (uint64_t)workers;
   const W* in = reinterpret_cast<const W*>(a.in);
   W* out = reinterpret_cast<W*>(a.out);
-  // Kernel timeline: thread 0 adds up what this CTA spent waiting for a tile, handing one on (the release store
-  // has to see the CTA's posted stores acknowledged) and working; the sums land in stamp slots 1 to 3 at exit.
+  // Kernel timeline: thread 0 adds up what this CTA spent waiting for a tile, held back by the hand-off and
+  // working; the sums land in stamp slots 1 to 3 at exit.
   const bool timed = c.timeline != nullptr && threadIdx.x == 0;
-  uint64_t t_wait = 0, t_hand = 0, t_mark = timed ? globalTimerNs() : 0, t_begin = t_mark;
+  uint64_t t_wait = 0, t_hand = 0, t_work = 0, t_mark = timed ? globalTimerNs() : 0;
   auto lap = [&](uint64_t& sum) {
     if (timed) {
       const uint64_t now = globalTimerNs();
@@ -611,44 +629,56 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
       t_mark = now;
     }
   };
-  uint64_t t_work = 0;
-  uint64_t k = 0;
-  for (uint64_t t = lane; lane < lanes && t < tiles; t += lanes, ++k) {
-    const uint64_t target = a.pipe_seq + k + 1;
-    const uint64_t p0 = t * tps;
-    const uint64_t tp = sp - p0 < tps ? sp - p0 : tps;
-    if (role == 0) {
-      for (int k2 = 1; k2 < n; ++k2) {
-        const int s = (r + k2) % n;   // start at the next rank: the owners are loaded evenly
-        pushTile<W, W, kPipeCopyUnroll>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp + p0, in + (uint64_t)s * in_stride + p0 * N,
-                                    tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
-      }
-      __syncthreads();
-      lap(t_work);
-      tileSignal(c, 1, target, gtid, lane);
-      lap(t_hand);
-    } else if (role == 1) {
-      tileWait(c, 1, target, gtid, &s_abort, 1, lane);
-      __syncthreads();
-      lap(t_wait);
-      if (s_abort) break;
-      foldStage<W, kAllReduce, MR>(c, a, in_stride, sp, p0, tp, res_off, x);
-      if constexpr (kAllReduce) {
-        __syncthreads();
+  if (signaller) {
+    const int kind = role == 0 ? 1 : 2;
+    for (uint64_t k = 0; k < my_tiles; ++k) {
+      groupSync(1, (int)blockDim.x);                          // tile k's stores are issued (or the workers gave up at k)
+      // not s_abort: that may already be set for tile k + 1 while tile k still has to be picked up and announced
+      if (*reinterpret_cast<volatile unsigned long long*>(&s_stop_at) == k) break;
+      if (k + 1 < my_tiles) barArrive(2, (int)blockDim.x);    // picked up: the workers may announce the next one
+      tileSignal(c, kind, a.pipe_seq + k + 1, gtid - workers, lane);
+    }
+  } else {
+    for (uint64_t k = 0; k < my_tiles; ++k) {
+      const uint64_t t = lane + k * lanes;
+      const uint64_t target = a.pipe_seq + k + 1;
+      const uint64_t p0 = t * tps;
+      const uint64_t tp = sp - p0 < tps ? sp - p0 : tps;
+      bool gave_up = false;
+      if (role == 0) {
+        for (int k2 = 1; k2 < n; ++k2) {
+          const int s = (r + k2) % n;   // start at the next rank: the owners are loaded evenly
+          pushTile<W, W, kPipeCopyUnroll>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp + p0, in + (uint64_t)s * in_stride + p0 * N,
+                                          tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
+        }
         lap(t_work);
-        tileSignal(c, 2, target, gtid, lane);
+      } else if (role == 1) {
+        tileWait(c, 1, target, gtid, &s_abort, 1, lane);
+        groupSync(3, workers);
+        lap(t_wait);
+        gave_up = s_abort != 0;
+        if (!gave_up) foldStage<W, kAllReduce, MR>(c, a, in_stride, sp, p0, tp, res_off, x);
+        lap(t_work);
+      } else {
+        tileWait(c, 2, target, gtid, &s_abort, 2, lane);
+        groupSync(3, workers);
+        lap(t_wait);
+        if (s_abort) break;
+        const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
+        for (int k2 = 1; k2 < n; ++k2) {
+          const int s = (r + k2) % n;
+          segCopyOut<W, W, kPipeCopyUnroll>(out + (uint64_t)s * in_stride + p0 * N, mine + res_off + (uint64_t)s * sp + p0,
+                                            tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
+        }
+        lap(t_work);
+      }
+      if (announces) {
+        if (k > 0) groupSync(2, (int)blockDim.x);             // the signaller has picked up tile k - 1
+        if (gave_up && threadIdx.x == 0) s_stop_at = k;       // ordered before the arrival below
+        barArrive(1, (int)blockDim.x);                        // tile k is ready (or: nothing more comes)
         lap(t_hand);
       }
-    } else {
-      tileWait(c, 2, target, gtid, &s_abort, 2, lane);
-      __syncthreads();
-      lap(t_wait);
-      if (s_abort) break;
-      const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
-      for (int k2 = 1; k2 < n; ++k2) {
-        const int s = (r + k2) % n;
-        segCopyOut<W, W, kPipeCopyUnroll>(out + (uint64_t)s * in_stride + p0 * N, mine + res_off + (uint64_t)s * sp + p0, tileElems<kAllReduce, N>(a.count, (uint64_t)s * in_stride, p0, tp), x);
-      }
+      if (gave_up) break;
     }
   }
   if constexpr (!kAllReduce) {
@@ -658,13 +688,14 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
   }
   if (timed && blockIdx.x < HL_TL_BLOCKS) {
     lap(t_work);
-    // slots 1..3 hold entry + duration, so that the decoder's "time since entry" reads as the three sums;
-    // slot 4 carries the stage (0 push, 1 fold, 2 copy-out) the same way, in microseconds
+    // slots 1..3 hold entry + duration, so that "time since entry" reads as the three sums; slot 4 carries the
+    // stage (0 push, 1 fold, 2 copy-out) the same way, in milliseconds
     uint64_t* st = c.timeline + (((a.seq / HL_SEQ_STRIDE) % HL_TL_CALLS) * HL_TL_BLOCKS + blockIdx.x) * HL_TL_PHASES;
-    st[1] = t_begin + t_wait;
-    st[2] = t_begin + t_hand;
-    st[3] = t_begin + t_work;
-    st[4] = t_begin + (uint64_t)role * 1000;
+    const uint64_t e = st[0];
+    st[1] = e + t_wait;
+    st[2] = e + t_hand;
+    st[3] = e + t_work;
+    st[4] = e + (uint64_t)role * 1000000ull;
   }
   callDone(c, lanes ? (tiles + lanes - 1) / lanes : 0);
 }

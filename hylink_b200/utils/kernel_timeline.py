@@ -71,7 +71,7 @@ def _summarise_lanes(launch):
     for s in launch["stamps"]:
         if not s[0] or not s[7]:
             continue
-        role = roles.get(round((s[4] - s[0]) / 1000), "?")
+        role = roles.get(round((s[4] - s[0]) / 1e6), "?")
         per_role.setdefault(role, []).append(((s[1] - s[0]) / 1e3, (s[2] - s[0]) / 1e3, (s[3] - s[0]) / 1e3, (s[7] - s[0]) / 1e3))
     out = {"kind": launch["kind"], "blocks": launch["blocks"], "count": launch["count"], "stages": {}}
     for role, rows in per_role.items():

@@ -122,7 +122,7 @@ def test_kernel_timeline_decoder_reads_lane_kernel_sums():
     for b in range(4):
         t0, role = 5_000_000, b % 2
         base = b * kt.TL_PHASES
-        words[base:base + 8] = [t0, t0 + (3000 if role else 0), t0 + (0 if role else 40000), t0 + 60000, t0 + role * 1000, 0, 0, t0 + 100000]
+        words[base:base + 8] = [t0, t0 + (3000 if role else 0), t0 + (0 if role else 40000), t0 + 60000, t0 + role * 1000000, 0, 0, t0 + 100000]
     s = kt.summarise(kt.decode(words)[0])
     assert s["stages"]["push"] == {"ctas": 2, "waiting_us": 0.0, "handing_on_us": 40.0, "working_us": 60.0, "total_us": 100.0}
     assert s["stages"]["fold"]["waiting_us"] == 3.0 and s["total_us"] == 100.0
