@@ -858,6 +858,53 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllGather(const HlCommDev* co
   callDone(c, 0);
 }
 
+// Stores-only all-gather over peer pointers: every rank pushes its prefix straight from the caller's buffer into
+// slot `rank` of every peer's staging (no local staging copy, and posted stores run ~7 % above loads from a peer on
+// this link), copies its own prefix to its place in the output while the peers' data is on its way, and after the
+// barrier copies the landed slots out locally. The caller's element type is the wire type.
+template <typename W>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kAllGatherPush(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  const uint64_t sp = (a.count + N - 1) / N;
+  const W* in = reinterpret_cast<const W*>(a.in);
+  W* out = reinterpret_cast<W*>(a.out);
+  for (int k = 1; k < n; ++k) {
+    const int s = (r + k) % n;
+    pushTile<W, W, kPushUnroll>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp, in, a.count, x);
+  }
+  W* own = out + (uint64_t)r * a.out_seg_stride;
+  if (own != in) {  // in place (the input already sits in its segment of the output): nothing to copy
+    const bool vin = aligned16(in), vout = aligned16(own);
+    for (uint64_t i = x.g0; i < sp; i += x.gstride * kPipeCopyUnroll) {
+      uint4 v[kPipeCopyUnroll];
+#pragma unroll
+      for (int u = 0; u < kPipeCopyUnroll; ++u) {
+        const uint64_t j = i + (uint64_t)u * x.gstride;
+        if (j < sp) v[u] = loadUserPacket<W, W>(in, j * N, a.count, vin);
+      }
+#pragma unroll
+      for (int u = 0; u < kPipeCopyUnroll; ++u) {
+        const uint64_t j = i + (uint64_t)u * x.gstride;
+        if (j < sp) storeUserPacket<W, W>(own, j * N, a.count, vout, v[u]);
+      }
+    }
+  }
+  if (!blockBarrier(c, a.seq + 1, 1)) return;
+  const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
+  for (int k = 1; k < n; ++k) {
+    const int s = (r + k) % n;
+    segCopyOut<W, W, kPushUnroll>(out + (uint64_t)s * a.out_seg_stride, mine + (uint64_t)s * sp, a.count, x);
+  }
+  // the peers' next pushes may land in these slots: nobody leaves before every peer has copied out
+  blockBarrier(c, a.seq + 2, 2);
+  callDone(c, 0);
+}
+
 // ------------------------------------------------------------------ broadcast
 template <typename W, bool kNvls>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* comms, HlEmuCalls calls) {
@@ -928,6 +975,7 @@ static const void* pickKernelT(int kind, int nranks) {
     case kNvlBroadcastNvls: return (const void*)kBroadcast<W, true>;
     case kNvlAllReducePush: return (const void*)kPush<W, true>;
     case kNvlReduceScatterPush: return (const void*)kPush<W, false>;
+    case kNvlAllGatherPush: return (const void*)kAllGatherPush<W>;
     case kNvlAllReducePipeP2p:   // one variant per rank-count class (the unrolled source loop of the fold)
       return nranks <= 2 ? (const void*)kPipeCta<W, true, 2> : (nranks <= 4 ? (const void*)kPipeCta<W, true, 4> : (const void*)kPipeCta<W, true, HL_MAX_RANKS>);
     case kNvlReduceScatterPipeP2p:
@@ -978,6 +1026,7 @@ const char* kernelName(int kind) {
     case kNvlBroadcastNvls: return "broadcast_nvls";
     case kNvlAllReducePush: return "allreduce_push";
     case kNvlReduceScatterPush: return "reducescatter_push";
+    case kNvlAllGatherPush: return "allgather_push";
     case kNvlAllReducePipeP2p: return "allreduce_pipelined_p2p";
     case kNvlAllReducePipeNvls: return "allreduce_pipelined_nvls";
     case kNvlReduceScatterPipeP2p: return "reducescatter_pipelined_p2p";
@@ -1017,7 +1066,7 @@ hlResult_t prepareKernels() {
                               kNvlReduceScatter, kNvlReduceScatterNvls, kNvlAllGather, kNvlBroadcast,
                               kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls, kNvlAllReducePipeP2p,
                               kNvlAllReducePipeNvls, kNvlReduceScatterPipeP2p, kNvlReduceScatterPipeNvls, kNvlAllReducePush,
-                              kNvlReduceScatterPush};
+                              kNvlReduceScatterPush, kNvlAllGatherPush};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
       for (int nr : {2, 4, HL_MAX_RANKS}) {   // rank-count classes (only the pipelined push kernels differ by it)

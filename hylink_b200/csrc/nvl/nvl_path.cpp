@@ -292,7 +292,7 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       a.int_div = (c.op == hlAvg) ? nranks_ : 0;
       a.kind = kind;
     }
-    const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls ? nranks_ : 1);
+    const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls && kind != kNvlAllGatherPush ? nranks_ : 1);
     int blocks = blocksFor(kind, wire_bytes, c.max_blocks);
     if (pipe) {
       // Tiles: as large as possible (every tile costs two flag round trips) while each CTA still gets
@@ -359,7 +359,11 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
 hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   const bool nvls = has_mc_ && c.algo == hlAlgoNvls;
-  return launchSliced(nvls ? kNvlAllGatherNvls : kNvlAllGather, b, c, true, s);
+  if (nvls) return launchSliced(kNvlAllGatherNvls, b, c, true, s);
+  // peer pointers: the stores-only kernel unless the call converts types or asks for the pull kernel by name
+  const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
+  const bool push = same && c.algo != hlAlgoTwoShotP2p && envBool({"HYLINK_AG_PUSH"}, true);
+  return launchSliced(push ? kNvlAllGatherPush : kNvlAllGather, b, c, true, s);
 }
 
 hlResult_t NvlPath::broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {

@@ -88,4 +88,5 @@ enum HlNvlKernel {
   kNvlReduceScatterPipeNvls = 14,
   kNvlAllReducePush = 15,
   kNvlReduceScatterPush = 16,
+  kNvlAllGatherPush = 17,
 };
