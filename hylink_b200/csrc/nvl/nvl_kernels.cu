@@ -599,7 +599,11 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
   }
   __syncthreads();
   constexpr int N = Packet<W>::N;
-  constexpr unsigned kRoles = kAllReduce ? 3 : 2;
+  // CTAs per lane. All-reduce: push, fold (which pushes the result on), copy-out. Reduce-scatter: one pusher and
+  // three folders that each take a third of the tile — 16 to 37 CTAs of posted stores fill the link, while the
+  // fold is the stage that needs the SMs (measured with one folder per pusher: push 183 us, fold 247 us).
+  constexpr unsigned kRoles = kAllReduce ? 3 : 4;
+  constexpr unsigned kFoldParts = kAllReduce ? 1 : 3;
   const int n = c.nranks, r = c.rank;
   const uint64_t np = (a.count + N - 1) / N;
   const uint64_t sp = kAllReduce ? (np + n - 1) / n : np;   // packets per shard (all-reduce) or per segment (reduce-scatter)
@@ -607,7 +611,9 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
   const uint64_t tiles = (sp + tps - 1) / tps;
   const uint64_t in_stride = kAllReduce ? sp * N : a.in_seg_stride;
   const uint64_t res_off = sp * (uint64_t)n;                // results live behind the n slots
-  const unsigned role = blockIdx.x % kRoles, lane = blockIdx.x / kRoles, lanes = gridDim.x / kRoles;
+  const unsigned member = blockIdx.x % kRoles, lane = blockIdx.x / kRoles, lanes = gridDim.x / kRoles;
+  const unsigned role = kAllReduce ? member : (member == 0 ? 0u : 1u);   // 0 push, 1 fold, 2 copy-out
+  const unsigned part = kAllReduce ? 0u : (member == 0 ? 0u : member - 1);
   const bool announces = role == 0 || (kAllReduce && role == 1);
   const int workers = announces ? (int)blockDim.x - 32 : (int)blockDim.x;
   const bool signaller = announces && (int)threadIdx.x >= workers;
@@ -657,7 +663,11 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
         groupSync(3, workers);
         lap(t_wait);
         gave_up = s_abort != 0;
-        if (!gave_up) foldStage<W, kAllReduce, MR>(c, a, in_stride, sp, p0, tp, res_off, x);
+        if (!gave_up) {
+          const uint64_t chunk = (tp + kFoldParts - 1) / kFoldParts;   // this folder's share of the tile
+          const uint64_t f0 = (uint64_t)part * chunk;
+          if (f0 < tp) foldStage<W, kAllReduce, MR>(c, a, in_stride, sp, p0 + f0, tp - f0 < chunk ? tp - f0 : chunk, res_off, x);
+        }
         lap(t_work);
       } else {
         tileWait(c, 2, target, gtid, &s_abort, 2, lane);

@@ -302,9 +302,9 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       const uint64_t np = (len + epp - 1) / epp;
       const uint64_t sp = pipe_ar ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;
       // Peer-pointer variants give every stage of a tile CTAs of its own (three for all-reduce: push, fold,
-      // copy-out; two for reduce-scatter); a "lane" is one such group and walks tiles lane, lane + lanes, ...
+      // copy-out; four for reduce-scatter: push and three folders); a "lane" is one such group and walks tiles lane, lane + lanes, ...
       const bool cta_roles = kind == kNvlAllReducePipeP2p || kind == kNvlReduceScatterPipeP2p;
-      const int roles = !cta_roles ? 1 : (pipe_ar ? 3 : 2);
+      const int roles = !cta_roles ? 1 : (pipe_ar ? 3 : 4);   // reduce-scatter: one pusher and three folders per lane
       uint64_t lanes = std::max(1, blocks / roles);
       uint64_t tps = (sp + lanes * 8 - 1) / (lanes * 8);
       tps = std::min<uint64_t>(8192, std::max<uint64_t>(256, (tps + 63) & ~(uint64_t)63));
