@@ -915,6 +915,93 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllGatherPush(const HlCommDev
   callDone(c, 0);
 }
 
+// The stores-only all-gather cut into tiles, with the link stage and the HBM stage on CTAs of their own (see
+// kPipeCta): per lane one pusher — its last warp is the signaller — and three copiers that each take a third of
+// every tile: they copy the own segment's part to its place, wait for the tile from all peers, and copy the landed
+// parts out. The link never waits for a copy.
+template <typename W>
+__global__ void __launch_bounds__(HL_NVL_THREADS, 1) kAllGatherLanes(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  constexpr int N = Packet<W>::N;
+  constexpr unsigned kMembers = 4, kParts = 3;
+  const int n = c.nranks, r = c.rank;
+  const uint64_t sp = (a.count + N - 1) / N;
+  const uint64_t tps = a.tile_packets;
+  const uint64_t tiles = (sp + tps - 1) / tps;
+  const unsigned member = blockIdx.x % kMembers, lane = blockIdx.x / kMembers, lanes = gridDim.x / kMembers;
+  const bool pusher = member == 0;
+  const int workers = pusher ? (int)blockDim.x - 32 : (int)blockDim.x;
+  const bool signaller = pusher && (int)threadIdx.x >= workers;
+  const int gtid = (int)threadIdx.x;
+  const uint64_t my_tiles = lane < lanes && lane < tiles ? (tiles - lane + lanes - 1) / lanes : 0;
+  Ctx x;
+  x.g0 = threadIdx.x;
+  x.gstride = (uint64_t)workers;
+  const W* in = reinterpret_cast<const W*>(a.in);
+  W* out = reinterpret_cast<W*>(a.out);
+  W* own = out + (uint64_t)r * a.out_seg_stride;
+  if (signaller) {
+    for (uint64_t k = 0; k < my_tiles; ++k) {
+      groupSync(1, (int)blockDim.x);                          // tile k's stores are issued
+      if (k + 1 < my_tiles) barArrive(2, (int)blockDim.x);    // picked up
+      tileSignal(c, 1, a.pipe_seq + k + 1, gtid - workers, lane);
+    }
+  } else {
+    for (uint64_t k = 0; k < my_tiles; ++k) {
+      const uint64_t p0 = (lane + k * lanes) * tps;
+      const uint64_t tp = sp - p0 < tps ? sp - p0 : tps;
+      if (pusher) {
+        const uint64_t cnt = tileElems<false, N>(a.count, 0, p0, tp);
+        for (int k2 = 1; k2 < n; ++k2) {
+          const int s = (r + k2) % n;
+          pushTile<W, W, kPipeCopyUnroll>(reinterpret_cast<uint4*>(c.stage[s]) + (uint64_t)r * sp + p0, in + p0 * N, cnt, x);
+        }
+        if (k > 0) groupSync(2, (int)blockDim.x);             // the signaller has picked up tile k - 1
+        barArrive(1, (int)blockDim.x);
+      } else {
+        const uint64_t chunk = (tp + kParts - 1) / kParts;
+        const uint64_t f0 = (uint64_t)(member - 1) * chunk;
+        const uint64_t len = f0 >= tp ? 0 : (tp - f0 < chunk ? tp - f0 : chunk);
+        const uint64_t q0 = p0 + f0;
+        const uint64_t cnt = len ? tileElems<false, N>(a.count, 0, q0, len) : 0;
+        if (cnt && own != in) {  // not in place: the own segment's part, while the peers' data is on its way
+          const bool vin = aligned16(in), vout = aligned16(own);
+          const uint64_t pk = (cnt + N - 1) / N;
+          for (uint64_t i = x.g0; i < pk; i += x.gstride * kPipeCopyUnroll) {
+            uint4 v[kPipeCopyUnroll];
+#pragma unroll
+            for (int u = 0; u < kPipeCopyUnroll; ++u) {
+              const uint64_t j = i + (uint64_t)u * x.gstride;
+              if (j < pk) v[u] = loadUserPacket<W, W>(in, (q0 + j) * N, a.count, vin);
+            }
+#pragma unroll
+            for (int u = 0; u < kPipeCopyUnroll; ++u) {
+              const uint64_t j = i + (uint64_t)u * x.gstride;
+              if (j < pk) storeUserPacket<W, W>(own, (q0 + j) * N, a.count, vout, v[u]);
+            }
+          }
+        }
+        tileWait(c, 1, a.pipe_seq + k + 1, gtid, &s_abort, 1, lane);
+        groupSync(3, workers);
+        if (s_abort) break;
+        const uint4* mine = reinterpret_cast<const uint4*>(c.stage[r]);
+        for (int k2 = 1; k2 < n && cnt; ++k2) {
+          const int s = (r + k2) % n;
+          segCopyOut<W, W, kPipeCopyUnroll>(out + (uint64_t)s * a.out_seg_stride + q0 * N, mine + (uint64_t)s * sp + q0, cnt, x);
+        }
+      }
+    }
+  }
+  // the peers' next pushes may land in these slots: nobody leaves before every peer's CTA of the same index is through
+  blockBarrier(c, a.seq + 1, 3);
+  callDone(c, lanes ? (tiles + lanes - 1) / lanes : 0);
+}
+
 // ------------------------------------------------------------------ broadcast
 template <typename W, bool kNvls>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* comms, HlEmuCalls calls) {
@@ -986,6 +1073,7 @@ static const void* pickKernelT(int kind, int nranks) {
     case kNvlAllReducePush: return (const void*)kPush<W, true>;
     case kNvlReduceScatterPush: return (const void*)kPush<W, false>;
     case kNvlAllGatherPush: return (const void*)kAllGatherPush<W>;
+    case kNvlAllGatherLanes: return (const void*)kAllGatherLanes<W>;
     case kNvlAllReducePipeP2p:   // one variant per rank-count class (the unrolled source loop of the fold)
       return nranks <= 2 ? (const void*)kPipeCta<W, true, 2> : (nranks <= 4 ? (const void*)kPipeCta<W, true, 4> : (const void*)kPipeCta<W, true, HL_MAX_RANKS>);
     case kNvlReduceScatterPipeP2p:
@@ -1037,6 +1125,7 @@ const char* kernelName(int kind) {
     case kNvlAllReducePush: return "allreduce_push";
     case kNvlReduceScatterPush: return "reducescatter_push";
     case kNvlAllGatherPush: return "allgather_push";
+    case kNvlAllGatherLanes: return "allgather_lanes";
     case kNvlAllReducePipeP2p: return "allreduce_pipelined_p2p";
     case kNvlAllReducePipeNvls: return "allreduce_pipelined_nvls";
     case kNvlReduceScatterPipeP2p: return "reducescatter_pipelined_p2p";
@@ -1076,7 +1165,7 @@ hlResult_t prepareKernels() {
                               kNvlReduceScatter, kNvlReduceScatterNvls, kNvlAllGather, kNvlBroadcast,
                               kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls, kNvlAllReducePipeP2p,
                               kNvlAllReducePipeNvls, kNvlReduceScatterPipeP2p, kNvlReduceScatterPipeNvls, kNvlAllReducePush,
-                              kNvlReduceScatterPush, kNvlAllGatherPush};
+                              kNvlReduceScatterPush, kNvlAllGatherPush, kNvlAllGatherLanes};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
       for (int nr : {2, 4, HL_MAX_RANKS}) {   // rank-count classes (only the pipelined push kernels differ by it)

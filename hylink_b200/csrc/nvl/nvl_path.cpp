@@ -261,7 +261,7 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
   const uint64_t cap_packets = stage_bytes_ / 16;
   uint64_t per_launch;                                  // elements handled per launch (per segment when segmented)
   const bool pipe = kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePipeNvls || kind == kNvlReduceScatterPipeP2p ||
-                    kind == kNvlReduceScatterPipeNvls;
+                    kind == kNvlReduceScatterPipeNvls || kind == kNvlAllGatherLanes;
   const bool pipe_ar = kind == kNvlAllReducePipeP2p || kind == kNvlAllReducePipeNvls;
   if (segmented || kind == kNvlAllReduceTwoShot || kind == kNvlAllReduceNvls || pipe_ar || kind == kNvlAllReducePush) {
     // the P2P pipelined all-reduce keeps inputs and results in separate halves of the staging region
@@ -292,7 +292,7 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       a.int_div = (c.op == hlAvg) ? nranks_ : 0;
       a.kind = kind;
     }
-    const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls && kind != kNvlAllGatherPush ? nranks_ : 1);
+    const size_t wire_bytes = (size_t)len * ws * (segmented && kind != kNvlAllGather && kind != kNvlAllGatherNvls && kind != kNvlAllGatherPush && kind != kNvlAllGatherLanes ? nranks_ : 1);
     int blocks = blocksFor(kind, wire_bytes, c.max_blocks);
     if (pipe) {
       // Tiles: as large as possible (every tile costs two flag round trips) while each CTA still gets
@@ -303,7 +303,7 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       const uint64_t sp = pipe_ar ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;
       // Peer-pointer variants give every stage of a tile CTAs of its own (three for all-reduce: push, fold,
       // copy-out; four for reduce-scatter: push and three folders); a "lane" is one such group and walks tiles lane, lane + lanes, ...
-      const bool cta_roles = kind == kNvlAllReducePipeP2p || kind == kNvlReduceScatterPipeP2p;
+      const bool cta_roles = kind == kNvlAllReducePipeP2p || kind == kNvlReduceScatterPipeP2p || kind == kNvlAllGatherLanes;
       const int roles = !cta_roles ? 1 : (pipe_ar ? 3 : 4);   // reduce-scatter: one pusher and three folders per lane
       uint64_t lanes = std::max(1, blocks / roles);
       uint64_t tps = (sp + lanes * 8 - 1) / (lanes * 8);
@@ -340,6 +340,10 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   return launchSliced(kind, b, c, false, s);
 }
 
+// Not selected by size until it has been measured against the phased kernel (HYLINK_AG_LANES_MIN_BYTES switches it on).
+size_t NvlPath::agLanesMinBytes() const { return (size_t)envInt({"HYLINK_AG_LANES_MIN_BYTES"}, (long long)1 << 60); }
+size_t NvlPath::lanesMinBytes() const { return (size_t)envInt({"HYLINK_RS_LANES_MIN_BYTES"}, 128LL << 20); }
+
 hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
@@ -351,7 +355,10 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
     if (c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= pipeMinBytes())) kind = kNvlReduceScatterPipeNvls;
     else if (same && (c.algo == hlAlgoPush || (c.algo == hlAlgoAuto && wire_bytes >= Config::get().push_min_bytes))) kind = kNvlReduceScatterPush;
   } else if (same && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot) {
-    kind = c.algo == hlAlgoPipelined ? kNvlReduceScatterPipeP2p : kNvlReduceScatterPush;
+    // Peer pointers: the phased stores-only kernel, and from 128 MiB the lane kernel that folds while it pushes
+    // (2 GPUs, bf16: 513 against 449 GB/s at 256 MiB, 580 against 485 GB/s at 1 GiB; 347 against 359 at 64 MiB).
+    const bool lanes = c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && wire_bytes >= lanesMinBytes());
+    kind = lanes ? kNvlReduceScatterPipeP2p : kNvlReduceScatterPush;
   }
   return launchSliced(kind, b, c, true, s);
 }
@@ -363,7 +370,9 @@ hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   // peer pointers: the stores-only kernel unless the call converts types or asks for the pull kernel by name
   const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
   const bool push = same && c.algo != hlAlgoTwoShotP2p && envBool({"HYLINK_AG_PUSH"}, true);
-  return launchSliced(push ? kNvlAllGatherPush : kNvlAllGather, b, c, true, s);
+  const size_t seg_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
+  const bool lanes = push && (c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && seg_bytes * (size_t)nranks_ >= agLanesMinBytes()));
+  return launchSliced(lanes ? kNvlAllGatherLanes : (push ? kNvlAllGatherPush : kNvlAllGather), b, c, true, s);
 }
 
 hlResult_t NvlPath::broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {

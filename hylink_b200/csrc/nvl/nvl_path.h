@@ -76,6 +76,8 @@ class NvlPath {
   int pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const;
   bool nvlsPays() const;
   size_t pipeMinBytes() const;
+  size_t agLanesMinBytes() const;
+  size_t lanesMinBytes() const;   // peer-pointer reduce-scatter: from this size on the lane kernel
   bool nvlsUsable(int wire_dt, int op, bool deterministic) const;
   int blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const;
 

@@ -89,4 +89,5 @@ enum HlNvlKernel {
   kNvlAllReducePush = 15,
   kNvlReduceScatterPush = 16,
   kNvlAllGatherPush = 17,
+  kNvlAllGatherLanes = 18,
 };

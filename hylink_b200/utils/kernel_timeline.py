@@ -21,7 +21,7 @@ TL_CALLS, TL_BLOCKS, TL_PHASES = 16, 148, 8
 KINDS = {0: "barrier", 1: "allreduce_oneshot", 2: "allreduce_twoshot", 3: "allreduce_nvls", 4: "reducescatter",
          5: "reducescatter_nvls", 6: "allgather", 7: "broadcast", 8: "alltoall", 9: "allgather_nvls", 10: "broadcast_nvls",
          11: "allreduce_pipelined_p2p", 12: "allreduce_pipelined_nvls", 13: "reducescatter_pipelined_p2p",
-         14: "reducescatter_pipelined_nvls", 15: "allreduce_push", 16: "reducescatter_push", 17: "allgather_push"}
+         14: "reducescatter_pipelined_nvls", 15: "allreduce_push", 16: "reducescatter_push", 17: "allgather_push", 18: "allgather_lanes"}
 PHASE_NAMES = ["entry", "arrive1", "leave1", "arrive2", "leave2", "arrive3", "leave3", "exit"]
 
 
