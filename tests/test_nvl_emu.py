@@ -363,3 +363,33 @@ def test_kernel_timeline_records_phases_in_order(monkeypatch):
             assert summary["total_us"] > 0 and "entry->arrive1" in summary["phases"]
     finally:
         g.close()
+
+
+@pytest.mark.parametrize("algo", ["auto", "twoshot", "pipelined"])
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_all_gather_kernels_agree(n, algo):
+    """Stores-only (auto), staged pull (twoshot) and lane (pipelined) all-gather: odd prefix inside a wider segment,
+    out of place and in place, several launches back to back, guard values behind every prefix."""
+    g = _group(n, stage_bytes=32 << 20)
+    seg, prefix = 300007, 262147
+    ins = [_rand(seg, torch.bfloat16, 31 + r) for r in range(n)]
+    outs = [torch.full((seg * n,), 7, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    for _ in range(3):
+        g.run("all_gather", ins, outs, prefix, out_seg_stride=seg, algo=algo)
+    torch.cuda.synchronize()
+    for r in range(n):
+        for q in range(n):
+            assert torch.equal(outs[r][q * seg:q * seg + prefix], ins[q][:prefix]), (r, q)
+            assert torch.all(outs[r][q * seg + prefix:(q + 1) * seg] == 7)
+    # in place: every rank's input already sits in its own segment of its output
+    bufs = [torch.full((seg * n,), 3, dtype=torch.bfloat16, device="cuda") for _ in range(n)]
+    for r in range(n):
+        bufs[r][r * seg:r * seg + prefix] = ins[r][:prefix]
+    g.run("all_gather", [bufs[r][r * seg:] for r in range(n)], bufs, prefix, out_seg_stride=seg, algo=algo)
+    torch.cuda.synchronize()
+    for r in range(n):
+        for q in range(n):
+            assert torch.equal(bufs[r][q * seg:q * seg + prefix], ins[q][:prefix]), (r, q)
+            assert torch.all(bufs[r][q * seg + prefix:(q + 1) * seg] == 3)
+    assert g.status(0)[0] == 0
+    g.close()
