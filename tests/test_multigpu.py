@@ -74,6 +74,11 @@ def test_deterministic_sum_order_against_host_oracles():
 def test_native_perf_tool_threads_and_fork():
     """hl_perf on two GPUs: ranks as threads over the NVLink kernels, ranks as processes over the PCIe path."""
     tool = os.path.join(ROOT, "hylink_b200", "bin", "hl_perf")
+    if not os.path.exists(tool):
+        from hylink_b200 import _build
+
+        _build.build_core()
+        _build.build_tools()
     for args, env in (
         (["--coll", "allreduce", "--ranks", "2", "--mode", "threads", "--path", "nvlink", "--dtype", "bf16",
           "--bytes-from", "4K", "--bytes-to", "64M", "--factor", "16", "--iters", "5"], {}),
