@@ -602,8 +602,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
   // CTAs per lane. All-reduce: push, fold (which pushes the result on), copy-out. Reduce-scatter: one pusher and
   // three folders that each take a third of the tile — 16 to 37 CTAs of posted stores fill the link, while the
   // fold is the stage that needs the SMs (measured with one folder per pusher: push 183 us, fold 247 us).
-  constexpr unsigned kRoles = kAllReduce ? 3 : 4;
-  constexpr unsigned kFoldParts = kAllReduce ? 1 : 3;
+  const unsigned kFoldParts = kAllReduce ? 1u : (unsigned)(a.lane_parts >= 1 && a.lane_parts <= 7 ? a.lane_parts : 3);
+  const unsigned kRoles = kAllReduce ? 3u : 1u + kFoldParts;
   const int n = c.nranks, r = c.rank;
   const uint64_t np = (a.count + N - 1) / N;
   const uint64_t sp = kAllReduce ? (np + n - 1) / n : np;   // packets per shard (all-reduce) or per segment (reduce-scatter)
@@ -928,7 +928,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kAllGatherLanes(const HlCom
   if (threadIdx.x == 0) s_abort = 0;
   __syncthreads();
   constexpr int N = Packet<W>::N;
-  constexpr unsigned kMembers = 4, kParts = 3;
+  const unsigned kParts = (unsigned)(a.lane_parts >= 1 && a.lane_parts <= 7 ? a.lane_parts : 3);
+  const unsigned kMembers = 1 + kParts;
   const int n = c.nranks, r = c.rank;
   const uint64_t sp = (a.count + N - 1) / N;
   const uint64_t tps = a.tile_packets;

@@ -304,7 +304,10 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       // Peer-pointer variants give every stage of a tile CTAs of its own (three for all-reduce: push, fold,
       // copy-out; four for reduce-scatter: push and three folders); a "lane" is one such group and walks tiles lane, lane + lanes, ...
       const bool cta_roles = kind == kNvlAllReducePipeP2p || kind == kNvlReduceScatterPipeP2p || kind == kNvlAllGatherLanes;
-      const int roles = !cta_roles ? 1 : (pipe_ar ? 3 : 4);   // reduce-scatter: one pusher and three folders per lane
+      // reduce-scatter, all-gather: one pusher and `parts` HBM-side CTAs per lane (three unless HYLINK_LANE_PARTS says otherwise)
+      static const int parts = std::min(7, std::max(1, (int)envInt({"HYLINK_LANE_PARTS"}, 3)));
+      const int roles = !cta_roles ? 1 : (pipe_ar ? 3 : 1 + parts);
+      for (int i = 0; i < nl; ++i) calls.c[i].lane_parts = parts;
       uint64_t lanes = std::max(1, blocks / roles);
       uint64_t tps = (sp + lanes * 8 - 1) / (lanes * 8);
       tps = std::min<uint64_t>(8192, std::max<uint64_t>(256, (tps + 63) & ~(uint64_t)63));
@@ -342,8 +345,14 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
 
 // Gathered bytes from which the peer-pointer all-gather uses the lane kernel (2 GPUs, bf16: 550 against 462 GB/s at
 // 256 MiB, 622 against 486 GB/s at 1 GiB, 375 against 390 GB/s at 64 MiB).
-size_t NvlPath::agLanesMinBytes() const { return (size_t)envInt({"HYLINK_AG_LANES_MIN_BYTES"}, 128LL << 20); }
-size_t NvlPath::lanesMinBytes() const { return (size_t)envInt({"HYLINK_RS_LANES_MIN_BYTES"}, 128LL << 20); }
+size_t NvlPath::agLanesMinBytes() const {
+  static const size_t v = (size_t)envInt({"HYLINK_AG_LANES_MIN_BYTES"}, 128LL << 20);  // read once: this sits on the launch path
+  return v;
+}
+size_t NvlPath::lanesMinBytes() const {
+  static const size_t v = (size_t)envInt({"HYLINK_RS_LANES_MIN_BYTES"}, 128LL << 20);
+  return v;
+}
 
 hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
@@ -370,7 +379,8 @@ hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   if (nvls) return launchSliced(kNvlAllGatherNvls, b, c, true, s);
   // peer pointers: the stores-only kernel unless the call converts types or asks for the pull kernel by name
   const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
-  const bool push = same && c.algo != hlAlgoTwoShotP2p && envBool({"HYLINK_AG_PUSH"}, true);
+  static const bool ag_push = envBool({"HYLINK_AG_PUSH"}, true);
+  const bool push = same && c.algo != hlAlgoTwoShotP2p && ag_push;
   const size_t seg_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
   const bool lanes = push && (c.algo == hlAlgoPipelined || (c.algo == hlAlgoAuto && seg_bytes * (size_t)nranks_ >= agLanesMinBytes()));
   return launchSliced(lanes ? kNvlAllGatherLanes : (push ? kNvlAllGatherPush : kNvlAllGather), b, c, true, s);

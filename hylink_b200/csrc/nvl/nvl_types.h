@@ -60,7 +60,7 @@ struct HlCallArgs {
   uint64_t pipe_seq;        // pipelined kernels (filled in on the device): tile k of a block is announced as pipe_seq + k + 1
   uint64_t tile_packets;    // pipelined kernels: 16-byte packets of one shard handled per tile
   int kind;                 // HlNvlKernel, recorded in the kernel timeline
-  int pad0;
+  int lane_parts;           // lane kernels (reduce-scatter, all-gather): HBM-side CTAs per pusher CTA (1..7)
 };
 
 // One argument block per emulated rank: on a single GPU the N ranks of a test
