@@ -1,22 +1,35 @@
 #!/usr/bin/env python
-"""Headline benchmark: GPT-2-medium data-parallel training step over this
-library's torch.distributed backend (25 MB gradient buckets, bf16, random
-weights, random tokens), plus a bus-bandwidth probe of the all-reduce kernel.
+"""Headline benchmark: bus bandwidth of all-reduce, reduce-scatter and all-gather against message size.
 
     python bench.py --gpus 1 --steps 10 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 10 --warmup 3
 
-Rank 0 prints ONE JSON line. ``value`` is whole-job tokens/s, device-timed
-(CUDA events, max over ranks) over exactly ``--steps`` steps; ``e2e`` repeats
-the measurement through ``DDPTrainer.step`` with a host-to-device copy of the
-batch from pinned memory and a device-to-host read of the loss every step.
-``--impl reference`` is the arm for the reference implementation.
+The collectives are issued through the product API — ``torch.distributed`` on
+this library's ``hylink`` backend — on bf16 buffers of 1 MiB to 1 GiB (powers
+of two; the size is the nccl-tests message size: the whole buffer for
+all-reduce, all n segments for reduce-scatter and all-gather). One *step* is
+one pass over the whole table (33 cells), every cell bracketed by its own pair
+of CUDA events; a cell's time is its mean over the timed steps, max over ranks.
+``value`` is the geometric mean of the bus bandwidth over all cells
+(busbw = bytes / time * 2(n-1)/n for all-reduce, * (n-1)/n for the other two;
+with one GPU the factor is 1). The same cells are timed on a NCCL process group
+in the same run (``nccl`` column), and the per-cell table, the split ratio and a
+GPT-2-medium DDP training step are reported as extra keys.
+
+``e2e`` repeats the table with, inside the timed region of every cell, the copy
+of the cell's input from pinned host memory to the device and a copy of the
+first 4 KiB of the result back to the host (wall clock around stream
+synchronisation).
+
+``--impl reference`` times the same cells on the unmodified reference library
+(``baseline/reference_arm.py``); ``--impl nccl`` on NCCL alone.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -27,12 +40,8 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-REF_UNAVAILABLE = ("the reference cannot run this configuration on this image: it is not a Python project (pip install of the tree: "
-                   "'Neither setup.py nor pyproject.toml found'), its multipath build libampccl_nccl.so does not compile against its "
-                   "CUDA PCCL ('pcclDataType_t has not been declared'), and its only PyTorch route, LD_PRELOAD=libpccl.so under "
-                   "backend=nccl, stops at communicator set-up on a B200 box ('sysfs reports invalid NUMA node -1', then with "
-                   "PCCL_GPU_NUMA_MAP 'NCCL error invalid argument, NCCL version 2.17.1' under PyTorch 2.11); record: "
-                   "profiles/reference_arm_probe.md")
+METRIC = "allreduce/RS/AG busbw GB/s vs size (geomean over 1 MiB-1 GiB cells, max over ranks)"
+COLLS = ("allreduce", "reducescatter", "allgather")
 
 
 class ClockSampler:
@@ -103,22 +112,280 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def run_arm(backend: str, args, tokens_shape):
-    """Builds the model on `backend`, returns (device ms/step, e2e ms/step, launches, loss, stats)."""
+def parse_size(s: str) -> int:
+    s = s.strip().upper()
+    mul = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30}.get(s[-1], 1)
+    return int(float(s[:-1]) * mul) if s[-1] in "KMG" else int(s)
+
+
+def size_list(lo: int, hi: int):
+    out, s = [], lo
+    while s <= hi:
+        out.append(s)
+        s *= 2
+    return out
+
+
+def bus_factor(coll: str, n: int) -> float:
+    if n <= 1:
+        return 1.0
+    return 2.0 * (n - 1) / n if coll == "allreduce" else (n - 1) / n
+
+
+def geomean(xs):
+    xs = [x for x in xs if x and x > 0]
+    return math.exp(sum(math.log(x) for x in xs) / len(xs)) if xs else 0.0
+
+
+def human(nbytes: int) -> str:
+    for unit, sh in (("GiB", 30), ("MiB", 20), ("KiB", 10)):
+        if nbytes >= 1 << sh:
+            return f"{nbytes >> sh} {unit}"
+    return f"{nbytes} B"
+
+
+# --------------------------------------------------------------------------- the sweep through torch.distributed
+class Table:
+    """Buffers and the per-cell calls of one process group."""
+
+    def __init__(self, dtype, sizes, world, group=None):
+        import torch
+
+        self.torch = torch
+        self.dtype, self.sizes, self.world, self.group = dtype, sizes, world, group
+        self.es = torch.empty((), dtype=dtype).element_size()
+        self.cells = [(c, s) for c in COLLS for s in sizes]
+        top = max(sizes)
+        self.slots = 2
+        # rotating buffers: between two timed calls of one cell a whole pass (> 4 GiB of traffic) goes through L2
+        self.inp = [(torch.rand(top // self.es, device="cuda") * 2 - 1).to(dtype) for _ in range(self.slots)]
+        self.out = [torch.empty(top // self.es, dtype=dtype, device="cuda") for _ in range(self.slots)]
+
+    def elems(self, nbytes):
+        n_el = max(self.world, (nbytes // self.es) // self.world * self.world)
+        return n_el, n_el // self.world
+
+    def input_bytes(self, coll, nbytes):
+        n_el, seg = self.elems(nbytes)
+        return (seg if coll == "allgather" else n_el) * self.es
+
+    def call(self, coll, nbytes, it):
+        import torch.distributed as dist
+
+        n_el, seg = self.elems(nbytes)
+        a, b = self.inp[it % self.slots], self.out[it % self.slots]
+        if coll == "allreduce":
+            dist.all_reduce(a[:n_el], group=self.group)     # in place, as torch.distributed defines it
+            return a
+        if coll == "reducescatter":
+            dist.reduce_scatter_tensor(b[:seg], a[:n_el], group=self.group)
+            return b
+        dist.all_gather_into_tensor(b[:n_el], a[:seg], group=self.group)
+        return b
+
+
+def timed_passes(tab: Table, steps: int, warmup: int, launches=None):
+    """W warm-up and K timed passes; returns (per-cell mean ms on this rank, device ms of the K passes, launches)."""
+    import torch
+    import torch.distributed as dist
+
+    for it in range(warmup):
+        for coll, nbytes in tab.cells:
+            tab.call(coll, nbytes, it)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    before = launches() if launches else 0
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in tab.cells] for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for it in range(steps):
+        for ci, (coll, nbytes) in enumerate(tab.cells):
+            ev[it][ci][0].record()
+            tab.call(coll, nbytes, warmup + it)
+            ev[it][ci][1].record()
+    t1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    after = launches() if launches else 0
+    per_cell = [sum(ev[it][ci][0].elapsed_time(ev[it][ci][1]) for it in range(steps)) / steps for ci in range(len(tab.cells))]
+    return per_cell, t0.elapsed_time(t1), after - before
+
+
+def e2e_passes(tab: Table, steps: int):
+    """Per-cell wall ms with the H2D copy of the input and a D2H read of the result inside the timed region."""
+    import torch
+    import torch.distributed as dist
+
+    top = max(tab.sizes)
+    host = torch.empty(top // tab.es, dtype=tab.dtype).pin_memory()
+    host.uniform_(-1, 1)
+    back = torch.empty(4096 // tab.es, dtype=tab.dtype).pin_memory()
+    sums = [0.0] * len(tab.cells)
+    for it in range(2 + steps):
+        for ci, (coll, nbytes) in enumerate(tab.cells):
+            n_el, seg = tab.elems(nbytes)
+            k = seg if coll == "allgather" else n_el
+            if it == 2 and ci == 0:
+                torch.cuda.synchronize()
+                dist.barrier()
+                torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            tab.inp[it % tab.slots][:k].copy_(host[:k], non_blocking=True)
+            res = tab.call(coll, nbytes, it)
+            back.copy_(res[:back.numel()], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            if it >= 2:
+                sums[ci] += (time.perf_counter() - t0) * 1e3
+    h2d = sum(tab.input_bytes(c, s) for c, s in tab.cells)
+    return [x / steps for x in sums], h2d, 4096 * len(tab.cells)
+
+
+def max_over_ranks(values, group=None):
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor(values, device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return [float(x) for x in t]
+
+
+# --------------------------------------------------------------------------- extra: the DDP training step
+def ddp_step(args, backend: str):
     import torch
     import torch.distributed as dist
 
     from hylink_b200.models.gpt2 import GPT2, GPT2Config
-    from hylink_b200.parallel.trainer import DDPTrainer, init_distributed
+    from hylink_b200.parallel.trainer import DDPTrainer
 
-    rank, world, dev = init_distributed(backend)
+    rank, world = dist.get_rank(), dist.get_world_size()
+    dev = torch.device("cuda", torch.cuda.current_device())
     torch.manual_seed(1234)
     cfg = GPT2Config.by_name(args.model)
     trainer = DDPTrainer(GPT2(cfg), dev, bucket_cap_mb=args.bucket_mb)
-    batch, seq = tokens_shape
     g = torch.Generator().manual_seed(100 + rank)
-    host_tokens = [torch.randint(0, cfg.vocab_size, (batch, seq + 1), generator=g).pin_memory() for _ in range(4)]
+    host_tokens = [torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq + 1), generator=g).pin_memory() for _ in range(4)]
     dev_tokens = [t.to(dev) for t in host_tokens]
+    steps = args.ddp_steps
+    for i in range(3):
+        t = dev_tokens[i % 4]
+        trainer.step_device(t[:, :-1], t[:, 1:])
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        t = dev_tokens[i % 4]
+        trainer.step_device(t[:, :-1], t[:, 1:])
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    dev_ms = e0.elapsed_time(e1) / steps
+    for i in range(2):
+        trainer.step(host_tokens[i % 4])
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    loss = 0.0
+    for i in range(steps):
+        loss = trainer.step(host_tokens[i % 4])
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    dev_ms, e2e_ms = max_over_ranks([dev_ms, e2e_ms])
+    tokens = args.micro_batch * args.seq * world
+    del trainer
+    torch.cuda.empty_cache()
+    return {"model": args.model, "backend": backend, "tokens_per_s": round(tokens / dev_ms * 1e3, 1), "ms_per_step": round(dev_ms, 3),
+            "e2e_tokens_per_s": round(tokens / e2e_ms * 1e3, 1), "steps": steps, "micro_batch": args.micro_batch, "seq_len": args.seq,
+            "bucket_mb": args.bucket_mb, "loss": round(float(loss), 4), "dtype": "bf16"}
+
+
+# --------------------------------------------------------------------------- arms
+def reference_arm(args, rank: int, world: int) -> int:
+    """The unmodified reference, thread-per-GPU in rank 0's process (its single-process mode); other ranks stand by."""
+    if rank != 0:
+        return 0
+    sizes = size_list(parse_size(args.lo), parse_size(args.hi))
+    n = args.gpus
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import reference_arm as ref
+
+        sampler = ClockSampler(0)
+        sampler.start()
+        sampler.mark_begin()
+        res = ref.run(n, args.steps, args.warmup, COLLS, sizes, e2e=True)
+        sampler.mark_end()
+        clocks = sampler.stop()
+    except Exception as ex:  # noqa: BLE001 - whatever stopped the reference is the answer
+        msg = " ".join(f"{type(ex).__name__}: {ex}".split())
+        print(json.dumps({"impl": "reference", "unavailable": msg[:600], "n_gpus": n}), flush=True)
+        return 0
+    cells = res["cells"]
+    table, bw, bw_e2e = [], [], []
+    for i, (coll, nbytes) in enumerate(cells):
+        f = bus_factor(coll, n)
+        b = nbytes / res["dev_ms"][i] / 1e6 * f
+        e = nbytes / res["e2e_ms"][i] / 1e6 * f
+        bw.append(b)
+        bw_e2e.append(e)
+        table.append({"coll": coll, "bytes": nbytes, "ms": round(res["dev_ms"][i], 4), "busbw_GBs": round(b, 2), "e2e_busbw_GBs": round(e, 2)})
+    h2d = sum((s // n if c == "allgather" else s) for c, s in cells)
+    rec = {"metric": METRIC, "value": round(geomean(bw), 3), "unit": "GB/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": round(sum(res["dev_ms"]), 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+           "dtype": "fp32 (the reference's public API reduces fp32 only; same byte sizes as the bf16 cells)", "data": "synthetic",
+           "impl": "reference",
+           "config": {"model": "collective sweep", "collectives": list(COLLS), "bytes": [sizes[0], sizes[-1]], "global_batch": None,
+                      "seq_len": None, "parallelism": f"{n} ranks as threads of one process (the reference's single-process mode)",
+                      "library": "baseline/_ref/libpccl.so through pcclAllReduce / pcclReduceScatter / pcclAllGather"
+                      if n > 1 else "baseline/_ref/libpccl.so through its ncclAllReduce / ncclReduceScatter / ncclAllGather (one rank)",
+                      "l2_policy": "two rotating buffer pairs of 1 GiB; a whole pass over the table lies between two timed calls of a cell"},
+           "clocks": clocks,
+           "e2e": {"value": round(geomean(bw_e2e), 3), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4096 * len(cells)},
+           "table": table, "wall_s": round(res["wall_s"], 1)}
+    print(json.dumps(rec), flush=True)
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="hylink", choices=["hylink", "reference", "nccl"])
+    ap.add_argument("--bytes-from", dest="lo", default="1M")
+    ap.add_argument("--bytes-to", dest="hi", default="1G")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32", "fp16"])
+    ap.add_argument("--no-nccl-arm", action="store_true", help="skip the NCCL column")
+    ap.add_argument("--no-ddp", action="store_true", help="skip the GPT-2-medium DDP step")
+    ap.add_argument("--model", default="gpt2-medium")
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=1024)
+    ap.add_argument("--bucket-mb", type=int, default=25)
+    ap.add_argument("--ddp-steps", type=int, default=10)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    args.steps = max(args.steps, 1)
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        return reference_arm(args, rank, world)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+
+    import torch
+    import torch.distributed as dist
+
+    from hylink_b200.parallel.trainer import init_distributed
+
+    backend = "hylink" if args.impl == "hylink" else "nccl"
+    rank, world, dev = init_distributed(backend)
+    dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[args.dtype]
+    sizes = size_list(parse_size(args.lo), parse_size(args.hi))
+    tab = Table(dtype, sizes, world)
 
     def stats():
         if backend != "hylink":
@@ -130,117 +397,70 @@ def run_arm(backend: str, args, tokens_shape):
     sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()  # nvidia-smi needs a moment to come up: start it before the warm-up
-    for i in range(args.warmup):
-        t = dev_tokens[i % len(dev_tokens)]
-        trainer.step_device(t[:, :-1], t[:, 1:])
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    sampler.mark_begin()
-    before = stats().get("kernel_launches", 0)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    loss = None
-    for i in range(args.steps):
-        t = dev_tokens[i % len(dev_tokens)]
-        loss = trainer.step_device(t[:, :-1], t[:, 1:])
-    e1.record()
-    torch.cuda.synchronize()
-    sampler.mark_end()
-    dist.barrier()
-    torch.cuda.synchronize()
-    dev_ms = e0.elapsed_time(e1) / args.steps
-    launches = stats().get("kernel_launches", 0) - before
+        sampler.mark_begin()
+    launches = (lambda: stats().get("kernel_launches", 0)) if backend == "hylink" else None
+    cell_ms, region_ms, n_launch = timed_passes(tab, args.steps, args.warmup, launches)
+    if rank == 0:
+        sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
+    alpha = stats().get("last_alpha", 0.0)
+    cell_ms = max_over_ranks(cell_ms)
+    region_ms = max_over_ranks([region_ms])[0]
 
-    # end to end through the public trainer API: pinned H2D of the batch and D2H of the loss every step
-    for i in range(2):
-        trainer.step(host_tokens[i % len(host_tokens)])
-    dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    last = 0.0
-    for i in range(args.steps):
-        last = trainer.step(host_tokens[i % len(host_tokens)])
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    both = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(both, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(both[0]), float(both[1])
-    final_stats = stats()
-    del trainer
+    nccl_ms = None
+    if backend == "hylink" and not args.no_nccl_arm:
+        nccl_group = dist.new_group(backend="nccl")
+        ntab = Table(dtype, sizes, world, group=nccl_group)
+        ntab.inp, ntab.out = tab.inp, tab.out
+        nccl_ms, _, _ = timed_passes(ntab, args.steps, args.warmup)
+        nccl_ms = max_over_ranks(nccl_ms)
+
+    e2e_ms, h2d, d2h = e2e_passes(tab, args.steps)
+    e2e_ms = max_over_ranks(e2e_ms)
+
+    table, bw, bw_nccl, bw_e2e = [], [], [], []
+    for i, (coll, nbytes) in enumerate(tab.cells):
+        n_el, _ = tab.elems(nbytes)
+        real = n_el * tab.es
+        f = bus_factor(coll, world)
+        b = real / cell_ms[i] / 1e6 * f
+        e = real / e2e_ms[i] / 1e6 * f
+        row = {"coll": coll, "bytes": real, "ms": round(cell_ms[i], 4), "busbw_GBs": round(b, 2), "e2e_busbw_GBs": round(e, 2)}
+        bw.append(b)
+        bw_e2e.append(e)
+        if nccl_ms:
+            nb = real / nccl_ms[i] / 1e6 * f
+            bw_nccl.append(nb)
+            row.update({"nccl_busbw_GBs": round(nb, 2), "vs_nccl": round(b / nb, 3)})
+        table.append(row)
+    del tab
     torch.cuda.empty_cache()
-    return dev_ms, e2e_ms, launches, float(last), clocks, final_stats, host_tokens[0].numel() * host_tokens[0].element_size()
 
+    ddp = None
+    if not args.no_ddp:
+        ddp = {backend: ddp_step(args, backend)}
+    final_stats = stats()
 
-def allreduce_probe(world: int):
-    """busbw of a 64 MiB bf16 all-reduce on the library's communicator vs the NCCL group (device-timed, max over ranks)."""
-    import torch
-    import torch.distributed as dist
-
-    from hylink_b200.utils.sweep import bus_factor, time_op
-
-    out = {}
-    if world < 2:
-        return out
-    n = (64 << 20) // 2
-    pool = torch.randn(4 * n, device="cuda").to(torch.bfloat16)
-    for name, group in (("hylink", None), ("nccl", dist.new_group(backend="nccl"))):
-        fn = lambda i, g=group: dist.all_reduce(pool[i * n:(i + 1) * n], group=g)
-        ms = time_op(fn, 4, 10, 3)
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        out[name + "_busbw_GBs"] = round(n * 2 / float(t[0]) / 1e6 * bus_factor("allreduce", world), 1)
-    return out
-
-
-def main() -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="hylink", choices=["hylink", "reference", "nccl"])
-    ap.add_argument("--model", default="gpt2-medium")
-    ap.add_argument("--micro-batch", type=int, default=8)
-    ap.add_argument("--seq", type=int, default=1024)
-    ap.add_argument("--bucket-mb", type=int, default=25)
-    ap.add_argument("--no-nccl-arm", action="store_true")
-    args = ap.parse_args()
-    args.warmup = max(args.warmup, 3)
-
-    rank = int(os.environ.get("RANK", 0))
-    world = int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": REF_UNAVAILABLE}))
-        return 0
-    if world != args.gpus and rank == 0:
-        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
-
-    import torch
-    import torch.distributed as dist
-
-    backend = "hylink" if args.impl == "hylink" else "nccl"
-    dev_ms, e2e_ms, launches, loss, clocks, stats, h2d = run_arm(backend, args, (args.micro_batch, args.seq))
-    tokens = args.micro_batch * args.seq * world
-    probe = allreduce_probe(world) if backend == "hylink" else {}
     if rank == 0:
         rec = {
-            "metric": "gpt2_medium_ddp_tokens_per_s", "value": round(tokens / dev_ms * 1e3, 1), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dev_ms, 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": args.impl,
-            "config": {"model": args.model, "global_batch": args.micro_batch * world, "seq_len": args.seq,
-                       "parallelism": f"dp{world}", "bucket_mb": args.bucket_mb, "backend": backend,
-                       "l2_policy": "working set larger than L2: 0.7 GB of bf16 weights plus activations are re-read every step",
-                       "optimizer": "fused AdamW inside the timed region"},
+            "metric": METRIC, "value": round(geomean(bw), 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(region_ms / args.steps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic", "impl": args.impl,
+            "config": {"model": "collective sweep", "collectives": list(COLLS), "bytes": [sizes[0], sizes[-1]],
+                       "global_batch": None, "seq_len": None, "parallelism": f"{world} ranks, one process per GPU",
+                       "api": f"torch.distributed all_reduce / reduce_scatter_tensor / all_gather_into_tensor, backend {backend}",
+                       "busbw": "bytes/time * 2(n-1)/n (all-reduce), * (n-1)/n (reduce-scatter, all-gather); factor 1 with one GPU",
+                       "l2_policy": "two rotating buffer pairs of 1 GiB; a whole pass over the table (> 4 GiB of traffic) lies "
+                                    "between two timed calls of a cell, so no cell is served from L2"},
             "clocks": clocks,
-            "e2e": {"value": round(tokens / e2e_ms * 1e3, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 3),
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
-            "gpu_launches": int(launches),
-            "loss": round(loss, 4),
-            "comm": {k: stats.get(k) for k in ("nvls", "symm_mode", "calls", "nvl_bytes", "pcie_bytes", "kernel_launches")},
-            "allreduce_64MiB_bf16": probe,
+            "e2e": {"value": round(geomean(bw_e2e), 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(n_launch),
+            "nccl": {"value": round(geomean(bw_nccl), 2), "cells_at_or_above_nccl": sum(1 for r in table if r.get("vs_nccl", 0) >= 1.0),
+                     "cells": len(table), "worst": min((r["vs_nccl"] for r in table), default=None)} if nccl_ms else None,
+            "split_ratio_pcie": round(float(alpha), 4),
+            "table": table,
+            "ddp": ddp,
+            "comm": {k: final_stats.get(k) for k in ("nvls", "symm_mode", "calls", "nvl_bytes", "pcie_bytes", "kernel_launches")},
         }
         print(json.dumps(rec), flush=True)
     dist.barrier()

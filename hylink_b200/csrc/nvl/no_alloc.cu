@@ -41,6 +41,7 @@ struct PerDevice {
 };
 PerDevice g_dev[64];
 std::mutex g_mu;
+int g_test_rows = 0;   // test aid: launch only the first k rows (the others never signal); 0 = all
 
 // Once per device, with that device current: find the array and write the
 // pointer tables (one per possible rank count) into it.
@@ -91,9 +92,9 @@ extern "C" hlResult_t hlAllReduceLocalNoAlloc(int nranks, const void* const* ins
     return hl::fail(hlInvalidArgument, "no-alloc all-reduce: %d buffers requested, supported range is 2..%d", nranks, (int)kMaxRanks);
   if ((int)op < 0 || op >= hlNumOps) return hl::fail(hlInvalidArgument, "no-alloc all-reduce: bad reduction operator %d", (int)op);
   if (!ins || !outs) return hl::fail(hlInvalidArgument, "no-alloc all-reduce: null pointer list");
-  if (count * es > kStagePerRank)
-    return hl::fail(hlInvalidArgument, "no-alloc all-reduce: %zu bytes per buffer exceed the fixed scratch of %zu bytes; use the regular group for larger messages",
-                    count * es, (size_t)kStagePerRank);
+  if (count > kStagePerRank / es)   // compared without multiplying: count * es may wrap
+    return hl::fail(hlInvalidArgument, "no-alloc all-reduce: %zu elements of %zu bytes per buffer exceed the fixed scratch of %zu bytes; use the regular group for larger messages",
+                    count, es, (size_t)kStagePerRank);
   if (count == 0) return hlSuccess;
   for (int i = 0; i < nranks; ++i)
     if (!ins[i] || !outs[i]) return hl::fail(hlInvalidArgument, "no-alloc all-reduce: buffer %d is null", i);
@@ -125,5 +126,34 @@ extern "C" hlResult_t hlAllReduceLocalNoAlloc(int nranks, const void* const* ins
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   const HlCommDev* table = reinterpret_cast<const HlCommDev*>(base + kTablesOff + (size_t)(nranks - 1) * kMaxRanks * kTableBytes);
-  return hl::nvl::launch(kNvlAllReduceTwoShot, (int)dtype, table, calls, nranks, blocks, s);
+  const int rows = (g_test_rows > 0 && g_test_rows < nranks) ? g_test_rows : nranks;
+  return hl::nvl::launch(kNvlAllReduceTwoShot, (int)dtype, table, calls, rows, blocks, s, nranks);
 }
+
+extern "C" hlResult_t hlAllReduceLocalNoAllocStatus(hlStream_t stream, int* code) {
+  if (code) *code = HL_DEV_OK;
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess || device < 0 || device >= 64) return hl::fail(hlDeviceError, "no-alloc all-reduce: no current CUDA device");
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_dev[device].ready) return hlSuccess;   // never called on this device: nothing can have gone wrong
+    base = g_dev[device].base;
+  }
+  e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return hl::fail(hlDeviceError, "no-alloc all-reduce: stream synchronisation failed: %s", cudaGetErrorString(e));
+  uint64_t words[kMaxRanks][16];   // 128 bytes per row: status words first
+  e = cudaMemcpy(words, base + kWordsOff, sizeof(words), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return hl::fail(hlDeviceError, "no-alloc all-reduce: reading the status words failed: %s", cudaGetErrorString(e));
+  for (size_t r = 0; r < kMaxRanks; ++r) {
+    if (words[r][0] != HL_DEV_OK) {
+      if (code) *code = (int)words[r][0];
+      return hl::fail(hlTimeout, "no-alloc all-reduce: row %zu gave up waiting (step %llu, peer row %llu, CTA %llu); its outputs are incomplete",
+                      r, (unsigned long long)(words[r][1] >> 32), (unsigned long long)(words[r][1] & 0xffffffffu), (unsigned long long)words[r][2]);
+    }
+  }
+  return hlSuccess;
+}
+
+extern "C" void hlNoAllocSetActiveRowsForTest(int rows) { g_test_rows = rows; }

@@ -31,6 +31,14 @@
  * first call outside any stream capture; later calls only enqueue work on
  * `stream` (one memset of the flag words, one kernel launch).
  *
+ * Errors on the device: every wait inside the kernel is bounded (2 s). A wait
+ * that runs out makes the kernel record a status code in the scratch and
+ * return with the outputs incomplete; the call that enqueued it has long
+ * returned hlSuccess by then. hlAllReduceLocalNoAllocStatus() waits for
+ * `stream` and reports that code; call it before trusting the outputs if a
+ * silent failure matters to you, and before the next call on the device (which
+ * clears the status words together with the flags).
+ *
  * Sharing: all calls on a device use the same array, which still holds the
  * previous call's contents; the flag words are cleared on `stream` at the start
  * of every call. Two calls that can overlap on the GPU (different streams
@@ -54,6 +62,17 @@ extern "C" {
  * enqueued on `stream`. */
 hlResult_t hlAllReduceLocalNoAlloc(int nranks, const void* const* ins, void* const* outs, size_t count,
                                    hlDataType_t dtype, hlRedOp_t op, hlStream_t stream);
+
+/* Waits for `stream`, then returns hlSuccess if the last call on the current
+ * device ran to completion and hlTimeout (with *code = the device status, see
+ * nvl_types.h, and a message in hlGetLastError()) if one of its bounded waits
+ * ran out. Copies 1 KiB from the device into a stack buffer; allocates nothing. */
+hlResult_t hlAllReduceLocalNoAllocStatus(hlStream_t stream, int* code);
+
+/* Test aid: launch only the first `rows` grid rows of later calls (0 = all), so
+ * that the rows which do run meet a peer that never signals and their bounded
+ * wait runs out. Nothing faults or hangs; the call ends after the 2 s limit. */
+void hlNoAllocSetActiveRowsForTest(int rows);
 
 #ifdef __cplusplus
 }

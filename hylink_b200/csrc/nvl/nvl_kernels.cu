@@ -11,13 +11,18 @@
 // needs no pack or merge copies.
 //
 // Protocol rules that make staging reuse safe without extra round trips:
-//   A. a kernel touches a PEER's staging only after the first barrier of its
-//      call (the local copy-in may run before it);
-//   B. a kernel whose last phase READS peers' staging ends with a barrier;
-//   C. launches of one communicator are stream-ordered on every rank.
-// With these, when rank r starts call k+1 every peer has finished reading r's
-// staging of call k, and no peer writes r's staging of call k+1 before r has
-// entered call k+1 (its first-barrier signal) and therefore finished call k.
+//   A. EVERY kernel ends with a cross-GPU barrier that follows its last access
+//      to any staging region, its own included (a kernel that finishes by
+//      copying landed data out of its own staging is not exempt: a faster peer
+//      would otherwise start the next call and push into slots that are still
+//      being read);
+//   B. launches of one communicator are stream-ordered on every rank, and all
+//      ranks launch the same grid for the same call.
+// With these, when any rank starts call k+1, all of its CTAs have left call k,
+// so CTA b of every peer has arrived at call k's last barrier, for every b:
+// no rank still reads or writes any staging of call k. A kernel of call k+1
+// may therefore write into a peer's staging right at entry (the stores-only
+// kernels do), and may stage locally before its first barrier.
 //
 // Block b of a rank only ever consumes data produced by block b of a peer
 // (same in-segment packet residue class), so the barrier is per block.
@@ -273,6 +278,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllReduceNvls(const HlCommDev
   if (!blockBarrier(c, a.seq + 2, 2)) return;
   for (int s = 0; s < n; ++s)
     copyOutAny<W>(a.out, a.out_dt, s * sp * N, mine + s * sp, segElems(a.count, s * sp * N, sp * N), x);
+  blockBarrier(c, a.seq + 3, 3);   // rule A: a peer's next call may store into this staging
   callDone(c, 0);
 }
 
@@ -535,11 +541,9 @@ __global__ void __launch_bounds__(kPipeThreads) kPipelined(const HlCommDev* comm
       }
     }
   }
-  if constexpr (!kAllReduce) {
-    // peers pull from this rank's staging in their exchange stage: nobody may start
-    // the next call's copy-in before everybody is through
-    blockBarrier(c, a.seq + 1, 3);
-  }
+  // rule A. Reduce-scatter: peers pull from this rank's staging in their exchange stage. All-reduce: the copy-out
+  // stage reads this rank's own staging, which a peer's next call may store into.
+  blockBarrier(c, a.seq + 1, 3);
   callDone(c, (tiles + gridDim.x - 1) / gridDim.x);
 }
 
@@ -691,11 +695,9 @@ __global__ void __launch_bounds__(HL_NVL_THREADS, 1) kPipeCta(const HlCommDev* c
       if (gave_up) break;
     }
   }
-  if constexpr (!kAllReduce) {
-    // a pusher of the next call may overwrite slots that a slower peer is still folding: nobody leaves before
-    // every peer's CTA of the same index is through
-    blockBarrier(c, a.seq + 1, 3);
-  }
+  // rule A: a pusher of the next call may overwrite slots that a slower peer is still folding (or, all-reduce,
+  // result areas that it is still copying out): nobody leaves before every peer's CTA of the same index is through
+  blockBarrier(c, a.seq + 1, 3);
   if (timed && blockIdx.x < HL_TL_BLOCKS) {
     lap(t_work);
     // slots 1..3 hold entry + duration, so that "time since entry" reads as the three sums; slot 4 carries the
@@ -766,6 +768,8 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kPush(const HlCommDev* comms, 
       const int s = (r + k) % n;
       segCopyOut<W, W, kPushUnroll>(out + (uint64_t)s * sp * N, mine + res_off + (uint64_t)s * sp, shardElems(s), x);
     }
+    // rule A: the result areas just read are where a peer's next (larger) call pushes its slots
+    blockBarrier(c, a.seq + 3, 3);
   }
   callDone(c, 0);
 }
@@ -856,6 +860,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllGather(const HlCommDev* co
     copyInAny<W, true>(mc, a.in, a.in_dt, 0, a.count, x);
     if (!blockBarrier(c, a.seq + 2, 2)) return;
     for (int q = 0; q < n; ++q) copyOutAny<W>(a.out, a.out_dt, q * a.out_seg_stride, mine + q * sp, a.count, x);
+    blockBarrier(c, a.seq + 3, 3);   // rule A
   } else {
     copyInAny<W>(mine, a.in, a.in_dt, 0, a.count, x);
     if (!blockBarrier(c, a.seq + 1, 1)) return;
@@ -1021,6 +1026,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kBroadcast(const HlCommDev* co
     }
     if (!blockBarrier(c, a.seq + 2, 2)) return;
     if (r != a.root || a.out != a.in) copyOutAny<W>(a.out, a.out_dt, 0, mine, a.count, x);
+    blockBarrier(c, a.seq + 3, 3);   // rule A
   } else {
     if (r == a.root) copyInAny<W>(mine, a.in, a.in_dt, 0, a.count, x);
     if (!blockBarrier(c, a.seq + 1, 1)) return;

@@ -137,7 +137,7 @@ hlResult_t NvlPath::resetAfterError() {
 }
 
 hlResult_t NvlPath::orderAfterPrevious(cudaStream_t s) {
-  // Rule C of the kernels' protocol: consecutive launches of one communicator
+  // Rule B of the kernels' protocol: consecutive launches of one communicator
   // must not overlap on this rank, whatever streams the caller uses.
   if (have_last_ && last_stream_ != s) {
     HL_CUDA(cudaEventRecord(order_ev_, last_stream_));

@@ -165,10 +165,10 @@ class HylinkBackend : public c10d::Backend {
  public:
   HylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size, std::chrono::milliseconds timeout)
       : c10d::Backend(rank, size), store_(store), timeout_(timeout) {
-    // CTAs a collective may occupy (0 = the library's table, one per SM for large messages). Collectives issued
-    // through this backend usually overlap with the backward pass: a grid on every SM finishes each bucket sooner
-    // but stalls the GEMMs beside it for longer than it saves (GPT-2-medium DDP on 2 GPUs: 55.4 ms per step with
-    // 148 CTAs, 54.5 ms with 48 to 96), so the default leaves more than half of the SMs to the compute stream.
+    // CTA budget of a collective (0 = the library's table, up to one CTA per SM for large messages). A caller
+    // whose collectives overlap with compute lowers it (setCtaBudget, as DDPTrainer does): a grid on every SM
+    // finishes each gradient bucket sooner but stalls the GEMMs beside it for longer than it saves (GPT-2-medium
+    // DDP on 2 GPUs: 55.4 ms per step with 148 CTAs, 54.5 ms with 48 to 96). Stand-alone collectives keep the table.
     if (const char* e = getenv("HYLINK_TORCH_MAX_BLOCKS")) max_blocks_ = atoi(e);
   }
   ~HylinkBackend() override { shutdown(); }
@@ -291,7 +291,10 @@ class HylinkBackend : public c10d::Backend {
     TORCH_CHECK(out.numel() == in.numel() * getSize(), "hylink: all_gather_into_tensor size mismatch");
     at::Tensor o = out, i = in;
     return run(OpType::_ALLGATHER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
-      hlCheck(hlAllGather(i.data_ptr(), o.data_ptr(), (size_t)i.numel(), toHl(i.scalar_type()), c, s), "allgather");
+      hlCallOpts co;
+      memset(&co, 0, sizeof(co));
+      co.max_blocks = max_blocks_;
+      hlCheck(hlAllGatherEx(i.data_ptr(), o.data_ptr(), (size_t)i.numel(), toHl(i.scalar_type()), &co, c, s), "allgather");
     });
   }
 
@@ -332,7 +335,10 @@ class HylinkBackend : public c10d::Backend {
     const OpInfo oi = toHlOp(opts.reduceOp);
     at::Tensor o = out, i = in;
     return run(OpType::_REDUCE_SCATTER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
-      hlCheck(hlReduceScatter(i.data_ptr(), o.data_ptr(), (size_t)o.numel(), toHl(i.scalar_type()), oi.op, c, s), "reduce_scatter");
+      hlCallOpts co;
+      memset(&co, 0, sizeof(co));
+      co.max_blocks = max_blocks_;
+      hlCheck(hlReduceScatterEx(i.data_ptr(), o.data_ptr(), (size_t)o.numel(), toHl(i.scalar_type()), oi.op, &co, c, s), "reduce_scatter");
     });
   }
 
@@ -416,6 +422,8 @@ class HylinkBackend : public c10d::Backend {
 
   // ---- extras exposed to Python -------------------------------------------
   void setFusedScale(float s) { fused_scale_ = s; }
+  void setCtaBudget(int b) { max_blocks_ = b < 0 ? 0 : b; }
+  int ctaBudget() const { return max_blocks_; }
   py::dict stats() {
     py::dict d;
     hlComm_t c = cuda_comm_ ? cuda_comm_ : cpu_comm_;
@@ -453,7 +461,7 @@ class HylinkBackend : public c10d::Backend {
   size_t ready_next_ = 0;
   std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
   float fused_scale_ = 0.0f;
-  int max_blocks_ = 64;
+  int max_blocks_ = 0;
 };
 
 c10::intrusive_ptr<c10d::Backend> createHylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
@@ -475,4 +483,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // Multiplies every all-reduce result by `scale` inside the kernel (0 = off):
   // lets a DDP wrapper fold its gradient pre-division into the collective.
   m.def("set_fused_scale", [](const c10::intrusive_ptr<c10d::Backend>& b, float s) { asHylink(b)->setFusedScale(s); });
+  // CTAs a collective of this group may occupy (0 = the library's size table). Returns the previous budget.
+  m.def("set_cta_budget", [](const c10::intrusive_ptr<c10d::Backend>& b, int n) {
+    const int old = asHylink(b)->ctaBudget();
+    asHylink(b)->setCtaBudget(n);
+    return old;
+  });
 }

@@ -68,3 +68,13 @@ def backend_stats(group=None) -> dict:
 def set_fused_scale(scale: float, group=None) -> None:
     """Multiply every all-reduce result by ``scale`` inside the kernel (0 switches it off)."""
     _load_ext().set_fused_scale(_backend_of(group), float(scale))
+
+
+def set_cta_budget(ctas: int, group=None) -> int:
+    """Limit the CTAs a collective of this group may occupy (0 = the library's size table); returns the old limit.
+
+    A collective that overlaps with compute kernels finishes sooner on every SM but holds those kernels back for
+    longer than it saves; callers that overlap (a DDP backward pass) therefore give the collectives a budget and
+    leave the other SMs to the compute stream. Stand-alone collectives run fastest with no budget.
+    """
+    return int(_load_ext().set_cta_budget(_backend_of(group), int(ctas)))

@@ -36,14 +36,30 @@ def init_distributed(backend: str = "hylink"):
 
 class DDPTrainer:
     def __init__(self, model: torch.nn.Module, device: torch.device, lr: float = 3e-4, bucket_cap_mb: int = 25,
-                 dtype: torch.dtype = torch.bfloat16):
+                 dtype: torch.dtype = torch.bfloat16, cta_budget: int | None = None):
         self.device = device
+        # gradient all-reduces overlap the backward pass: they get a CTA budget (the GEMMs keep the other SMs)
+        self._old_budget = None
+        if dist.get_backend() == "hylink":
+            from .backend import set_cta_budget
+
+            if cta_budget is None:
+                cta_budget = int(os.environ.get("HYLINK_DDP_CTA_BUDGET", "64"))
+            self._old_budget = set_cta_budget(cta_budget)
         self.model = model.to(device=device, dtype=dtype)
         self.ddp = DDP(self.model, device_ids=[device.index], bucket_cap_mb=bucket_cap_mb, gradient_as_bucket_view=True,
                        static_graph=False)
         self.opt = torch.optim.AdamW(self.ddp.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
         self._loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
         self._dev_batch = None
+
+    def close(self) -> None:
+        """Gives the process group its previous CTA budget back."""
+        if self._old_budget is not None:
+            from .backend import set_cta_budget
+
+            set_cta_budget(self._old_budget)
+            self._old_budget = None
 
     def step_device(self, idx: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One optimisation step on device-resident tokens; returns the loss tensor (no host sync)."""
