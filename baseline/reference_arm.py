@@ -189,73 +189,23 @@ def run_multi(n: int, steps: int, warmup: int, colls, sizes, e2e: bool = True) -
 
 
 def run_single(steps: int, warmup: int, colls, sizes, e2e: bool = True) -> dict:
-    """One GPU: the reference's NCCL personality with a one-rank communicator (device-to-device copy)."""
-    import torch
+    """One GPU: the reference's NCCL personality with a one-rank communicator (device-to-device copy), in a child
+    process that loads neither PyTorch nor the real NCCL (see reference_single.py for why)."""
+    import json
+    import subprocess
+    import sys
 
-    lib = load_library()
-    torch.cuda.set_device(0)
-    dev = torch.device("cuda", 0)
-    torch.zeros(1, device=dev)
-    comm = C.c_void_p()
-    devs = (C.c_int * 1)(0)
-    lib.ncclCommInitAll.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_int)]
-    rc = lib.ncclCommInitAll(C.byref(comm), 1, devs)
-    if rc != 0:
-        raise RuntimeError(f"ncclCommInitAll(1) -> result {rc}")
-    ncclFloat32, ncclSum = 7, 0
-    lib.ncclAllReduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
-    lib.ncclReduceScatter.argtypes = lib.ncclAllReduce.argtypes
-    lib.ncclAllGather.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]
-    cells = _cells(colls, sizes)
-    max_bytes = max(sizes)
-    stream = torch.cuda.Stream(device=dev)
-    sptr = C.c_void_p(stream.cuda_stream)
-    send = [torch.rand(max_bytes // 4, device=dev) for _ in range(2)]
-    recv = [torch.empty(max_bytes // 4, device=dev) for _ in range(2)]
-    host = torch.empty(max_bytes // 4).pin_memory()
-    back = torch.empty(1024).pin_memory()
-
-    def submit(coll, s, d, nbytes):
-        cnt = nbytes // 4
-        if coll == "allreduce":
-            return lib.ncclAllReduce(s, d, cnt, ncclFloat32, ncclSum, comm, sptr)
-        if coll == "reducescatter":
-            return lib.ncclReduceScatter(s, d, cnt, ncclFloat32, ncclSum, comm, sptr)
-        return lib.ncclAllGather(s, d, cnt, ncclFloat32, comm, sptr)
-
-    t_begin = time.perf_counter()
-    dev_sum, e2e_sum = [0.0] * len(cells), [0.0] * len(cells)
-    with torch.cuda.stream(stream):
-        for it in range(warmup + steps):
-            for ci, (coll, nbytes) in enumerate(cells):
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s, d = send[it % 2], recv[it % 2]
-                e0.record(stream)
-                rc = submit(coll, C.c_void_p(s.data_ptr()), C.c_void_p(d.data_ptr()), nbytes)
-                e1.record(stream)
-                if rc != 0:
-                    raise RuntimeError(f"{coll} {nbytes} B -> nccl result {rc}")
-                stream.synchronize()
-                if it >= warmup:
-                    dev_sum[ci] += e0.elapsed_time(e1)
-        if e2e:
-            for it in range(2 + steps):
-                for ci, (coll, nbytes) in enumerate(cells):
-                    t0 = time.perf_counter()
-                    s, d = send[it % 2], recv[it % 2]
-                    s[:nbytes // 4].copy_(host[:nbytes // 4], non_blocking=True)
-                    rc = submit(coll, C.c_void_p(s.data_ptr()), C.c_void_p(d.data_ptr()), nbytes)
-                    if rc != 0:
-                        raise RuntimeError(f"{coll} {nbytes} B -> nccl result {rc}")
-                    back.copy_(d[:1024], non_blocking=True)
-                    stream.synchronize()
-                    if it >= 2:
-                        e2e_sum[ci] += (time.perf_counter() - t0) * 1e3
-    wall = time.perf_counter() - t_begin
-    lib.ncclCommDestroy.argtypes = [C.c_void_p]
-    lib.ncclCommDestroy(comm)
-    return {"cells": cells, "dev_ms": [x / steps for x in dev_sum], "e2e_ms": [x / steps for x in e2e_sum] if e2e else None,
-            "wall_s": wall}
+    cmd = [sys.executable, str(Path(__file__).resolve().parent / "reference_single.py"), str(steps), str(warmup), ",".join(colls),
+           ",".join(str(s) for s in sizes)]
+    p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+    if not lines:
+        raise RuntimeError(f"the one-GPU run of the reference ended with exit code {p.returncode}: {p.stderr[-300:]}")
+    res = json.loads(lines[-1])
+    if "error" in res:
+        raise RuntimeError(res["error"])
+    res["cells"] = [tuple(c) for c in res["cells"]]
+    return res
 
 
 def run(n: int, steps: int, warmup: int, colls, sizes, e2e: bool = True) -> dict:

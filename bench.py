@@ -148,18 +148,28 @@ def human(nbytes: int) -> str:
 class Table:
     """Buffers and the per-cell calls of one process group."""
 
-    def __init__(self, dtype, sizes, world, group=None):
+    def __init__(self, dtype, sizes, world, group=None, registered=False):
         import torch
 
         self.torch = torch
+        self.registered = registered
         self.dtype, self.sizes, self.world, self.group = dtype, sizes, world, group
         self.es = torch.empty((), dtype=dtype).element_size()
         self.cells = [(c, s) for c in COLLS for s in sizes]
         top = max(sizes)
         self.slots = 2
         # rotating buffers: between two timed calls of one cell a whole pass (> 4 GiB of traffic) goes through L2
-        self.inp = [(torch.rand(top // self.es, device="cuda") * 2 - 1).to(dtype) for _ in range(self.slots)]
-        self.out = [torch.empty(top // self.es, dtype=dtype, device="cuda") for _ in range(self.slots)]
+        if registered:
+            # the library's allocator (hylink_b200.parallel.symmetric_empty): registered memory, collectives run zero-copy
+            from hylink_b200.parallel import symmetric_empty
+
+            self.inp = [symmetric_empty(top // self.es, dtype) for _ in range(self.slots)]
+            self.out = [symmetric_empty(top // self.es, dtype) for _ in range(self.slots)]
+            for t in self.inp:
+                t.copy_((torch.rand(top // self.es, device="cuda") * 2 - 1).to(dtype))
+        else:
+            self.inp = [(torch.rand(top // self.es, device="cuda") * 2 - 1).to(dtype) for _ in range(self.slots)]
+            self.out = [torch.empty(top // self.es, dtype=dtype, device="cuda") for _ in range(self.slots)]
 
     def elems(self, nbytes):
         n_el = max(self.world, (nbytes // self.es) // self.world * self.world)
@@ -295,6 +305,7 @@ def ddp_step(args, backend: str):
     e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
     dev_ms, e2e_ms = max_over_ranks([dev_ms, e2e_ms])
     tokens = args.micro_batch * args.seq * world
+    trainer.close()
     del trainer
     torch.cuda.empty_cache()
     return {"model": args.model, "backend": backend, "tokens_per_s": round(tokens / dev_ms * 1e3, 1), "ms_per_step": round(dev_ms, 3),
@@ -360,6 +371,8 @@ def main() -> int:
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32", "fp16"])
     ap.add_argument("--no-nccl-arm", action="store_true", help="skip the NCCL column")
     ap.add_argument("--no-ddp", action="store_true", help="skip the GPT-2-medium DDP step")
+    ap.add_argument("--unregistered", action="store_true", help="headline on ordinary torch tensors (staged) instead of registered memory")
+    ap.add_argument("--ddp-only", action="store_true", help="only the GPT-2-medium DDP step (prints its record alone)")
     ap.add_argument("--model", default="gpt2-medium")
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=1024)
@@ -383,9 +396,17 @@ def main() -> int:
 
     backend = "hylink" if args.impl == "hylink" else "nccl"
     rank, world, dev = init_distributed(backend)
+    if args.ddp_only:
+        rec = ddp_step(args, backend)
+        if rank == 0:
+            print(json.dumps({"metric": "gpt2_medium_ddp_tokens_per_s", "impl": args.impl, "n_gpus": world, **rec}), flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return 0
     dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[args.dtype]
     sizes = size_list(parse_size(args.lo), parse_size(args.hi))
-    tab = Table(dtype, sizes, world)
+    registered = backend == "hylink" and not args.unregistered and world > 1
+    tab = Table(dtype, sizes, world, registered=registered)
 
     def stats():
         if backend != "hylink":
@@ -400,9 +421,6 @@ def main() -> int:
         sampler.mark_begin()
     launches = (lambda: stats().get("kernel_launches", 0)) if backend == "hylink" else None
     cell_ms, region_ms, n_launch = timed_passes(tab, args.steps, args.warmup, launches)
-    if rank == 0:
-        sampler.mark_end()
-    clocks = sampler.stop() if rank == 0 else None
     alpha = stats().get("last_alpha", 0.0)
     cell_ms = max_over_ranks(cell_ms)
     region_ms = max_over_ranks([region_ms])[0]
@@ -414,9 +432,20 @@ def main() -> int:
         ntab.inp, ntab.out = tab.inp, tab.out
         nccl_ms, _, _ = timed_passes(ntab, args.steps, args.warmup)
         nccl_ms = max_over_ranks(nccl_ms)
+        del ntab
 
     e2e_ms, h2d, d2h = e2e_passes(tab, args.steps)
     e2e_ms = max_over_ranks(e2e_ms)
+    staged_ms = None
+    if registered:
+        # the same cells on ordinary torch tensors: every byte goes through the library's staging region
+        ptab = Table(dtype, sizes, world)
+        staged_ms, _, _ = timed_passes(ptab, args.steps, args.warmup)
+        staged_ms = max_over_ranks(staged_ms)
+        del ptab
+    if rank == 0:
+        sampler.mark_end()   # the clocks cover all timed passes: this library's, NCCL's and the end-to-end ones
+    clocks = sampler.stop() if rank == 0 else None
 
     table, bw, bw_nccl, bw_e2e = [], [], [], []
     for i, (coll, nbytes) in enumerate(tab.cells):
@@ -432,6 +461,8 @@ def main() -> int:
             nb = real / nccl_ms[i] / 1e6 * f
             bw_nccl.append(nb)
             row.update({"nccl_busbw_GBs": round(nb, 2), "vs_nccl": round(b / nb, 3)})
+        if staged_ms:
+            row["unregistered_busbw_GBs"] = round(real / staged_ms[i] / 1e6 * f, 2)
         table.append(row)
     del tab
     torch.cuda.empty_cache()
@@ -449,6 +480,9 @@ def main() -> int:
             "config": {"model": "collective sweep", "collectives": list(COLLS), "bytes": [sizes[0], sizes[-1]],
                        "global_batch": None, "seq_len": None, "parallelism": f"{world} ranks, one process per GPU",
                        "api": f"torch.distributed all_reduce / reduce_scatter_tensor / all_gather_into_tensor, backend {backend}",
+                       "buffers": ("registered memory from hylink_b200.parallel.symmetric_empty (zero-copy kernels); the "
+                                   "unregistered_busbw_GBs column repeats every cell on ordinary torch tensors (staged kernels)")
+                       if registered else "ordinary torch tensors",
                        "busbw": "bytes/time * 2(n-1)/n (all-reduce), * (n-1)/n (reduce-scatter, all-gather); factor 1 with one GPU",
                        "l2_policy": "two rotating buffer pairs of 1 GiB; a whole pass over the table (> 4 GiB of traffic) lies "
                                     "between two timed calls of a cell, so no cell is served from L2"},
@@ -457,6 +491,7 @@ def main() -> int:
             "gpu_launches": int(n_launch),
             "nccl": {"value": round(geomean(bw_nccl), 2), "cells_at_or_above_nccl": sum(1 for r in table if r.get("vs_nccl", 0) >= 1.0),
                      "cells": len(table), "worst": min((r["vs_nccl"] for r in table), default=None)} if nccl_ms else None,
+            "unregistered": {"value": round(geomean([r["unregistered_busbw_GBs"] for r in table]), 2)} if staged_ms else None,
             "split_ratio_pcie": round(float(alpha), 4),
             "table": table,
             "ddp": ddp,

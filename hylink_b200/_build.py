@@ -112,7 +112,9 @@ def build_nccl_shim(verbose: bool = False) -> Path | None:
         target = LIB / lib_name
         if changed or not target.exists():
             core = [] if "nccltrace" in lib_name else ["-L", str(LIB), "-lhylink_b200", "-Wl,-rpath,$ORIGIN"]
-            _run(["g++", "-shared", "-o", str(target), str(obj), *core, *extra, "-lpthread", "-ldl", "-lrt"])
+            # -Bsymbolic-functions: calls between this library's own nccl* entry points stay inside it even when the
+            # process has another library with the same names loaded (the real NCCL)
+            _run(["g++", "-shared", "-Wl,-Bsymbolic-functions", "-o", str(target), str(obj), *core, *extra, "-lpthread", "-ldl", "-lrt"])
             if verbose:
                 print("linked", target)
         out = out or target

@@ -96,6 +96,11 @@ _sig("hlEmuCreate", _i, _i, _i, _sz, _i, C.POINTER(_vp))
 _sig("hlEmuDestroy", _i, _vp)
 _sig("hlEmuCollective", _i, _vp, _i, C.POINTER(_vp), C.POINTER(_vp), _sz, _sz, _sz, _i, _i, _i, _i, _f, _i, _i, _i, _vp)
 _sig("hlEmuSetActiveRanks", _i, _vp, _i)
+_sig("hlEmuHeapAlloc", _i, _vp, _sz, C.POINTER(_vp))
+_sig("hlEmuHeapFree", _i, _vp, _vp)
+_sig("hlMemAlloc", _i, _vp, _sz, C.POINTER(_vp))
+_sig("hlMemFree", _i, _vp, _vp)
+_sig("hlMemIsRegistered", _i, _vp, _vp, _sz)
 _sig("hlEmuStatus", _i, _vp, _i, _u64p, _u64p, _u64p)
 _sig("hlEmuReset", _i, _vp)
 _sig("hlEmuLaunches", _i, _vp, _u64p)

@@ -19,10 +19,16 @@ hlResult_t pollDeviceStatus(hlComm* c) {
     uint64_t detail = 0, block = 0;
     const uint64_t code = c->nvl->deviceStatus(0, &detail, &block);
     if (code != HL_DEV_OK && c->async_error.load() == hlSuccess) {
-      c->async_error.store(hlTimeout);
-      HL_ERR("rank %d: a device-side wait ran out (code %llu, barrier %llu, peer %llu, block %llu)", c->rank,
-             (unsigned long long)code, (unsigned long long)(detail >> 32), (unsigned long long)(detail & 0xffffffffu),
-             (unsigned long long)block);
+      if (code == HL_DEV_ASYMMETRIC) {
+        c->async_error.store(hlInvalidArgument);
+        HL_ERR("rank %d: rank %llu passed a registered buffer at another heap offset than this rank (registered buffers must be "
+               "allocated in the same order on every rank)", c->rank, (unsigned long long)(detail & 0xffffffffu));
+      } else {
+        c->async_error.store(hlTimeout);
+        HL_ERR("rank %d: a device-side wait ran out (code %llu, barrier %llu, peer %llu, block %llu)", c->rank,
+               (unsigned long long)code, (unsigned long long)(detail >> 32), (unsigned long long)(detail & 0xffffffffu),
+               (unsigned long long)block);
+      }
       if (c->bs) c->bs->latchFailure();
     }
   }
@@ -67,6 +73,32 @@ static void account(hlComm* c, size_t bytes, size_t nvl_bytes, size_t pcie_bytes
   c->stats.bytes += bytes;
   c->stats.nvl_bytes += nvl_bytes;
   c->stats.pcie_bytes += pcie_bytes;
+}
+
+// One rank: every collective is the identity on `bytes` bytes. Served here as nothing at all (in place) or one
+// launch of the vectorised copy kernel (the landing-reduce kernel with one source) on the caller's stream, unless
+// the call converts types, scales, or asks for a kernel by name (then the ordinary kernels run on the one-rank group). The reference does the same in its NCCL
+// personality (pcie-ccl-cuda/src/api/nccl_compat/compat_common.cpp:453-472).
+static bool singleRankIdentity(hlComm* c, const Resolved& r, const void* send, void* recv, size_t bytes, hlStream_t stream,
+                               hlResult_t* result) {
+  if (c->nranks != 1 || c->host_device) return false;
+  if (r.in_dt != r.out_dt || r.in_dt != r.wire_dt || r.scale != 1.0f || r.algo != hlAlgoAuto) return false;
+  *result = hlSuccess;
+  c->stats.calls++;
+  c->stats.bytes += bytes;
+  if (send == recv) return true;
+  nvl::ReduceLandingArgs a;
+  memset(&a, 0, sizeof(a));
+  a.dst = recv;
+  a.src[0] = send;
+  a.nsrc = 1;
+  a.scale = 1.0f;
+  const bool words = bytes % 4 == 0 && (((uintptr_t)send | (uintptr_t)recv) & 3) == 0;   // plain 32-bit lanes: no conversion at all
+  a.dtype = words ? hlUint32 : hlUint8;
+  a.count = words ? bytes / 4 : bytes;
+  *result = nvl::launchReduceLanding(a, 0, (cudaStream_t)stream);
+  c->stats.kernel_launches++;
+  return true;
 }
 
 // Decides which transport(s) serve a call.
@@ -127,6 +159,8 @@ hlResult_t commInit(hlComm_t* out, int nranks, hlUniqueId id, int rank, int devi
 
 }  // namespace hl
 
+static std::atomic<hlComm_t> g_alloc_comm[64];   // per device: the communicator whose heap serves the allocator hooks
+
 extern "C" {
 
 hlResult_t hlCommInitRank(hlComm_t* comm, int nranks, hlUniqueId id, int rank) {
@@ -148,6 +182,10 @@ hlResult_t hlSetRendezvousTimeoutMs(int ms) {
 
 hlResult_t hlCommDestroy(hlComm_t comm) {
   if (!comm) return hlSuccess;
+  if (comm->device >= 0 && comm->device < 64) {
+    hlComm_t expect = comm;
+    g_alloc_comm[comm->device].compare_exchange_strong(expect, nullptr);
+  }
   if (!comm->host_device) {
     cudaSetDevice(comm->device);
     cudaDeviceSynchronize();
@@ -209,6 +247,10 @@ hlResult_t hlAllReduceEx(const void* send, void* recv, size_t count, hlDataType_
   if (count == 0) return hlSuccess;
   const size_t bytes = count * hlTypeSize(t);
   std::lock_guard<std::mutex> lk(comm->mu);
+  {
+    hlResult_t one;
+    if (singleRankIdentity(comm, r, send, recv, bytes, stream, &one)) return one;
+  }
   const hlPath_t path = choosePath(comm, r.path, bytes);
   if (path == hlPathPcie) {
     if (!comm->pcie) return fail(hlUnsupported, "PCIe path not initialised (single rank or disabled)");
@@ -249,6 +291,10 @@ hlResult_t hlReduceScatterEx(const void* send, void* recv, size_t recvcount, hlD
   if (recvcount == 0) return hlSuccess;
   const size_t bytes = recvcount * hlTypeSize(t);
   std::lock_guard<std::mutex> lk(comm->mu);
+  {
+    hlResult_t one;
+    if (singleRankIdentity(comm, r, send, recv, bytes, stream, &one)) return one;
+  }
   const hlPath_t path = choosePath(comm, r.path, bytes);
   if (path == hlPathPcie) {
     if (!comm->pcie) return fail(hlUnsupported, "PCIe path not initialised");
@@ -288,6 +334,10 @@ hlResult_t hlAllGatherEx(const void* send, void* recv, size_t sendcount, hlDataT
   if (sendcount == 0) return hlSuccess;
   const size_t bytes = sendcount * hlTypeSize(t);
   std::lock_guard<std::mutex> lk(comm->mu);
+  {
+    hlResult_t one;
+    if (singleRankIdentity(comm, r, send, recv, bytes, stream, &one)) return one;
+  }
   const hlPath_t path = choosePath(comm, r.path, bytes);
   if (path == hlPathPcie) {
     if (!comm->pcie) return fail(hlUnsupported, "PCIe path not initialised");
@@ -327,6 +377,10 @@ hlResult_t hlBroadcastEx(const void* send, void* recv, size_t count, hlDataType_
   if (count == 0) return hlSuccess;
   const size_t bytes = count * hlTypeSize(t);
   std::lock_guard<std::mutex> lk(comm->mu);
+  {
+    hlResult_t one;
+    if (singleRankIdentity(comm, r, send ? send : recv, recv, bytes, stream, &one)) return one;
+  }
   const hlPath_t path = choosePath(comm, r.path == hlPathAuto ? hlPathNvlink : r.path, bytes);
   if (path == hlPathPcie) {
     if (!comm->pcie) return fail(hlUnsupported, "PCIe path not initialised");
@@ -362,6 +416,10 @@ hlResult_t hlAllToAllEx(const void* send, void* recv, size_t count, hlDataType_t
   if (count == 0) return hlSuccess;
   const size_t bytes = count * hlTypeSize(t);
   std::lock_guard<std::mutex> lk(comm->mu);
+  {
+    hlResult_t one;
+    if (singleRankIdentity(comm, r, send, recv, bytes, stream, &one)) return one;
+  }
   const hlPath_t path = choosePath(comm, r.path, bytes);
   if (path == hlPathPcie) {
     if (!comm->pcie) return fail(hlUnsupported, "PCIe path not initialised");
@@ -383,6 +441,46 @@ hlResult_t hlAllToAllEx(const void* send, void* recv, size_t count, hlDataType_t
   c.max_blocks = r.max_blocks;
   account(comm, bytes, bytes, 0);
   return comm->nvl->allToAll(b, c, (cudaStream_t)stream);
+}
+
+// ---- collectives with explicit segment strides (dedicated-link path) -----------------------------------------------
+// The segments of the gathered / scattered buffer need not be adjacent: `stride` elements lie between their starts
+// (>= count). This is what the V-variants of the NCCL surface map to when every rank contributes the same count.
+static hlResult_t segCall(int which, const void* send, void* recv, size_t count, size_t in_stride, size_t out_stride, hlDataType_t t,
+                          hlRedOp_t op, hlComm_t comm, hlStream_t stream) {
+  HL_CHECK(precheck(comm));
+  if (!send || !recv) return fail(hlInvalidArgument, "null buffer");
+  if (!hlTypeSize(t)) return fail(hlInvalidArgument, "unknown data type %d", (int)t);
+  if ((in_stride && in_stride < count) || (out_stride && out_stride < count)) return fail(hlInvalidArgument, "segment stride smaller than the segment");
+  if (count == 0) return hlSuccess;
+  if (comm->host_device || !comm->nvl) return fail(hlUnsupported, "strided segments need the dedicated-link path");
+  std::lock_guard<std::mutex> lk(comm->mu);
+  NvlBufs b;
+  memset(&b, 0, sizeof(b));
+  b.in[0] = send;
+  b.out[0] = recv;
+  NvlCall c;
+  c.count = count;
+  c.in_seg_stride = in_stride;
+  c.out_seg_stride = out_stride;
+  c.in_dt = c.out_dt = c.wire_dt = t;
+  c.op = op;
+  const size_t bytes = count * hlTypeSize(t);
+  account(comm, bytes, bytes, 0);
+  if (which == 0) return comm->nvl->allGather(b, c, (cudaStream_t)stream);
+  if (which == 1) return comm->nvl->reduceScatter(b, c, (cudaStream_t)stream);
+  return comm->nvl->allToAll(b, c, (cudaStream_t)stream);
+}
+hlResult_t hlAllGatherSeg(const void* send, void* recv, size_t count, size_t recv_stride, hlDataType_t t, hlComm_t comm, hlStream_t stream) {
+  return segCall(0, send, recv, count, 0, recv_stride, t, hlSum, comm, stream);
+}
+hlResult_t hlReduceScatterSeg(const void* send, void* recv, size_t count, size_t send_stride, hlDataType_t t, hlRedOp_t op, hlComm_t comm,
+                              hlStream_t stream) {
+  return segCall(1, send, recv, count, send_stride, 0, t, op, comm, stream);
+}
+hlResult_t hlAllToAllSeg(const void* send, void* recv, size_t count, size_t send_stride, size_t recv_stride, hlDataType_t t, hlComm_t comm,
+                         hlStream_t stream) {
+  return segCall(2, send, recv, count, send_stride, recv_stride, t, hlSum, comm, stream);
 }
 
 hlResult_t hlBarrier(hlComm_t comm, hlStream_t stream) {
@@ -415,6 +513,10 @@ hlResult_t hlNvlLinkProbe(hlComm_t comm, int mode, int blocks, int threads, int 
   return comm->nvl->linkProbe(mode, blocks, threads, unroll, layout, bytes, (cudaStream_t)stream);
 }
 
+// Registered memory. With an NVLink path of two or more ranks the buffer comes from the communicator's symmetric heap
+// (same offset on every rank, mapped by every peer, multicast-bound with NVLS), which lets collectives on it run
+// zero-copy; every rank must then allocate and free in the same order. Otherwise (one rank, host device, heap
+// exhausted or unavailable) it is ordinary memory.
 hlResult_t hlMemAlloc(hlComm_t comm, size_t bytes, void** ptr) {
   if (!comm || !ptr) return hlInvalidArgument;
   if (comm->host_device) {
@@ -422,6 +524,14 @@ hlResult_t hlMemAlloc(hlComm_t comm, size_t bytes, void** ptr) {
     return *ptr ? hlSuccess : hlSystemError;
   }
   HL_CUDA(cudaSetDevice(comm->device));
+  if (comm->nvl && comm->nranks > 1 && bytes) {
+    std::lock_guard<std::mutex> lk(comm->mu);
+    void* p[HL_MAX_RANKS] = {nullptr};
+    if (comm->nvl->heapAlloc(bytes, p) == hlSuccess) {
+      *ptr = p[0];
+      return hlSuccess;
+    }
+  }
   HL_CUDA(cudaMalloc(ptr, bytes));
   return hlSuccess;
 }
@@ -431,15 +541,56 @@ hlResult_t hlMemFree(hlComm_t comm, void* ptr) {
     free(ptr);
     return hlSuccess;
   }
+  if (!ptr) return hlSuccess;
+  if (comm->nvl) {
+    std::lock_guard<std::mutex> lk(comm->mu);
+    uint64_t off;
+    if (comm->nvl->heapOffset(0, ptr, 1, &off)) return comm->nvl->heapFree(ptr);
+  }
   HL_CUDA(cudaFree(ptr));
   return hlSuccess;
+}
+int hlMemIsRegistered(hlComm_t comm, const void* ptr, size_t bytes) {
+  if (!comm || !comm->nvl || !ptr) return 0;
+  uint64_t off;
+  return comm->nvl->heapOffset(0, ptr, bytes ? bytes : 1, &off) ? 1 : 0;
+}
+
+// The communicator whose heap serves hlTorchAlloc / hlTorchFree (allocator hooks with the signature PyTorch's
+// pluggable CUDA allocator expects). Set by the torch.distributed backend when it creates its communicator.
+void hlSetAllocatorComm(hlComm_t comm) {
+  if (comm && comm->device >= 0 && comm->device < 64) g_alloc_comm[comm->device].store(comm);
+}
+hlComm_t hlGetAllocatorComm(int device) { return device >= 0 && device < 64 ? g_alloc_comm[device].load() : nullptr; }
+void* hlTorchAlloc(ssize_t size, int device, void* stream) {
+  (void)stream;
+  hlComm_t c = hlGetAllocatorComm(device);
+  void* p = nullptr;
+  if (c) {
+    if (hlMemAlloc(c, (size_t)size, &p) == hlSuccess) return p;
+    return nullptr;
+  }
+  cudaSetDevice(device);
+  if (cudaMalloc(&p, (size_t)size) != cudaSuccess) return nullptr;
+  return p;
+}
+void hlTorchFree(void* ptr, ssize_t size, int device, void* stream) {
+  (void)size;
+  (void)stream;
+  hlComm_t c = hlGetAllocatorComm(device);
+  if (c) {
+    hlMemFree(c, ptr);
+    return;
+  }
+  cudaSetDevice(device);
+  cudaFree(ptr);
 }
 
 hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out) {
   if (!comm || !out) return hlInvalidArgument;
   std::lock_guard<std::mutex> lk(comm->mu);
   *out = comm->stats;
-  out->kernel_launches = (comm->nvl ? comm->nvl->launches() : 0) + (comm->pcie ? comm->pcie->kernelLaunches() : 0);
+  out->kernel_launches = comm->stats.kernel_launches + (comm->nvl ? comm->nvl->launches() : 0) + (comm->pcie ? comm->pcie->kernelLaunches() : 0);
   out->copy_engine_ops = comm->pcie ? comm->pcie->copyOps() : 0;
   if (comm->orch) comm->orch->fillStats(out);
   return hlSuccess;
@@ -511,6 +662,11 @@ hlResult_t hlEmuCollective(hlEmu_t e, int kind, const void* const* ins, void* co
     default: return fail(hlInvalidArgument, "unknown emulated collective %d", kind);
   }
 }
+hlResult_t hlEmuHeapAlloc(hlEmu_t e, size_t bytes, void** ptrs) {
+  if (!e || !ptrs) return hlInvalidArgument;
+  return e->path->heapAlloc(bytes, ptrs);
+}
+hlResult_t hlEmuHeapFree(hlEmu_t e, void* ptr_rank0) { return e ? e->path->heapFree(ptr_rank0) : hlInvalidArgument; }
 hlResult_t hlEmuSetActiveRanks(hlEmu_t e, int k) {
   if (!e || k < 1 || k > e->path->nranks()) return hlInvalidArgument;
   e->path->setEmuActiveRanks(k);

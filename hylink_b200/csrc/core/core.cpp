@@ -180,6 +180,8 @@ static Config* loadConfig() {
   c->nvl_timeout_ms = (int)envInt({"HYLINK_NVL_TIMEOUT_MS"}, 20000);
   c->nvls = (int)envInt({"HYLINK_NVLS"}, -1);
   c->symm_mode = envStr({"HYLINK_SYMM_MODE"}, "auto");
+  c->symm_heap_bytes = (size_t)envInt({"HYLINK_SYMM_HEAP_BYTES"}, 8LL << 30);
+  c->zero_copy = envBool({"HYLINK_ZERO_COPY"}, true);
   c->oneshot_max_bytes = (size_t)envInt({"HYLINK_ONESHOT_MAX_BYTES"}, 128LL << 10);
   c->pipe_min_bytes = (size_t)envInt({"HYLINK_PIPE_MIN_BYTES"}, 0);
   c->push_min_bytes = (size_t)envInt({"HYLINK_PUSH_MIN_BYTES"}, 32LL << 20);

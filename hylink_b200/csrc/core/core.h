@@ -102,6 +102,8 @@ struct Config {
   int nvl_timeout_ms;            // bound of every device-side wait
   int nvls;                      // -1 auto, 0 off, 1 require
   std::string symm_mode;         // auto | vmm | ipc
+  size_t symm_heap_bytes;        // registered-memory heap per rank (created at the first hlMemAlloc)
+  bool zero_copy;                // use the zero-copy kernels when a call's buffers are registered
   size_t oneshot_max_bytes;
   size_t pipe_min_bytes;         // from this size on the pipelined NVLS kernels are used (0 = by rank count)
   size_t push_min_bytes;         // with NVLS available: from this size on the stores-only kernels are used

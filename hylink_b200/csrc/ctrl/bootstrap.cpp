@@ -1,5 +1,6 @@
 #include "ctrl/bootstrap.h"
 
+#include <atomic>
 #include <errno.h>
 #include <fcntl.h>
 #include <poll.h>
@@ -28,10 +29,15 @@ uint64_t hashId(const hlUniqueId& id) {
   }
   return h;
 }
-bool idIsZero(const hlUniqueId& id) {
-  for (int i = 0; i < HL_UNIQUE_ID_BYTES; ++i)
-    if (id.internal[i]) return false;
-  return true;
+// Ranks that are threads of one process rendezvous in process memory. Their id starts with a zero byte (ids made by
+// hlGetUniqueId never do); the bytes behind it tell groups apart, so that two groups of the same size can be set up
+// at the same time. The all-zero id (the reference's convention for single-process mode) is the group with tag 0.
+bool idIsZero(const hlUniqueId& id) { return id.internal[0] == 0; }
+static uint64_t inProcessTag(const hlUniqueId& id) {
+  uint64_t h = 0;
+  for (int i = 1; i < HL_UNIQUE_ID_BYTES; ++i)
+    if (id.internal[i]) return hashId(id);
+  return h;
 }
 
 // Rendezvous limit of the NEXT Bootstrap::create on this thread (0 = the
@@ -60,7 +66,7 @@ struct SpGroup {
   ~SpGroup() { free(mem); }
 };
 static std::mutex g_sp_mu;
-static std::map<int, std::shared_ptr<SpGroup>> g_sp_open;  // nranks -> group still missing ranks
+static std::map<std::pair<int, uint64_t>, std::shared_ptr<SpGroup>> g_sp_open;  // (nranks, group tag) -> group still missing ranks
 static std::map<CtrlBlock*, std::shared_ptr<SpGroup>> g_sp_live;
 static uint64_t g_sp_serial = 0;
 
@@ -105,7 +111,8 @@ hlResult_t Bootstrap::create(const hlUniqueId& id, int nranks, int rank, size_t 
   if (b->single_process_) {
     std::lock_guard<std::mutex> lk(g_sp_mu);
     std::shared_ptr<SpGroup> g;
-    auto it = g_sp_open.find(nranks);
+    const std::pair<int, uint64_t> key(nranks, inProcessTag(id));
+    auto it = g_sp_open.find(key);
     if (it != g_sp_open.end() && !(it->second->taken & (1u << rank)) && it->second->bytes == b->map_bytes_) g = it->second;
     if (!g) {
       g = std::make_shared<SpGroup>();
@@ -114,11 +121,11 @@ hlResult_t Bootstrap::create(const hlUniqueId& id, int nranks, int rank, size_t 
       memset(g->mem, 0, g->bytes);
       g->serial = ++g_sp_serial;
       initBlock(new (g->mem) CtrlBlock, nranks, extra_bytes);
-      g_sp_open[nranks] = g;
+      g_sp_open[key] = g;
       g_sp_live[(CtrlBlock*)g->mem] = g;
     }
     g->taken |= (1u << rank);
-    if (g->taken == (nranks >= 32 ? 0xffffffffu : ((1u << nranks) - 1))) g_sp_open.erase(nranks);
+    if (g->taken == (nranks >= 32 ? 0xffffffffu : ((1u << nranks) - 1))) g_sp_open.erase(key);
     b->block_ = (CtrlBlock*)g->mem;
     snprintf(tag, sizeof(tag), "sp%d_%llx", (int)getpid(), (unsigned long long)g->serial);
   } else {
@@ -385,6 +392,15 @@ hlResult_t Bootstrap::broadcastFd(int root, int my_fd, int* out_fd) {
 }
 
 }  // namespace hl
+
+// An id for ranks that are threads of ONE process: a zero byte, then a tag that tells this group from others.
+extern "C" hlResult_t hlGetInProcessId(hlUniqueId* id) {
+  if (!id) return hlInvalidArgument;
+  static std::atomic<uint64_t> serial{0};
+  memset(id, 0, sizeof(*id));
+  snprintf(id->internal + 1, sizeof(id->internal) - 1, "inproc-%d-%llu", (int)getpid(), (unsigned long long)serial.fetch_add(1) + 1);
+  return hlSuccess;
+}
 
 extern "C" hlResult_t hlGetUniqueId(hlUniqueId* id) {
   if (!id) return hlInvalidArgument;

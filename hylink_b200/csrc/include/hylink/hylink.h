@@ -18,6 +18,7 @@
 #define HYLINK_HYLINK_H_
 
 #include <stddef.h>
+#include <sys/types.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -69,7 +70,10 @@ typedef enum {
   hlAlgoTwoShotP2p = 2,  /* pull-reduce of the owned shard, pull all-gather; fixed sum order */
   hlAlgoNvls = 3,        /* multimem.ld_reduce + multimem.st through NVSwitch */
   hlAlgoPipelined = 4,   /* warp-specialised tiles: copy-in, link exchange and copy-out overlap */
-  hlAlgoPush = 5         /* peer stores only: push shards to their owner, fold locally, push results */
+  hlAlgoPush = 5,        /* peer stores only: push shards to their owner, fold locally, push results */
+  hlAlgoZeroCopy = 6,    /* registered (hlMemAlloc) buffers read and written in place on every rank; refused for others */
+  hlAlgoZeroCopyNvls = 7,/* ... through NVSwitch (multimem) */
+  hlAlgoZeroCopyP2p = 8  /* ... with plain peer loads and stores, fixed sum order */
 } hlAlgo_t;
 
 #define HL_UNIQUE_ID_BYTES 128
@@ -144,13 +148,33 @@ hlResult_t hlAllToAllEx(const void* send, void* recv, size_t count_per_peer, hlD
 /* Device-side barrier over the NVLink flags (an 8-byte exchange). */
 hlResult_t hlBarrier(hlComm_t comm, hlStream_t stream);
 
-/* ---- device memory ------------------------------------------------------ */
-/* Device memory tied to the communicator's device (host memory with the
- * host-memory device). Collectives stage user buffers through the
- * communicator's own symmetric region, so any device pointer works as an
- * argument; this pair exists for NCCL-style callers that expect an allocator. */
+/* ---- registered device memory --------------------------------------------
+ * hlMemAlloc returns memory of the communicator's device. When the communicator
+ * has a dedicated-link path with two or more ranks the memory is REGISTERED: it
+ * comes from a symmetric heap (HYLINK_SYMM_HEAP_BYTES per rank, created at the
+ * first call) that every peer maps and, with NVLS, that is bound to one
+ * multicast object. Collectives whose buffers are registered run zero-copy:
+ * peers' inputs are read and peers' outputs written in place (multimem
+ * load-reduce / store through NVSwitch, or plain peer loads and stores), with
+ * no staging copy at all. Rules, as for any symmetric allocator: every rank
+ * calls hlMemAlloc / hlMemFree in the same order with the same sizes (a buffer
+ * then has the same heap offset everywhere; a collective whose ranks disagree
+ * is stopped with an error before it touches memory), no collective of the
+ * communicator may be in flight during the very first allocation, and zero-copy
+ * needs 16-byte aligned buffers of whole 16-byte packets (anything else is
+ * staged as usual). Unregistered pointers keep working everywhere. When the
+ * heap is exhausted or unavailable the call falls back to cudaMalloc. With the
+ * host-memory device the memory is host memory. */
 hlResult_t hlMemAlloc(hlComm_t comm, size_t bytes, void** ptr);
 hlResult_t hlMemFree(hlComm_t comm, void* ptr);
+/* 1 when [ptr, ptr + bytes) lies in the communicator's registered heap. */
+int hlMemIsRegistered(hlComm_t comm, const void* ptr, size_t bytes);
+/* Allocator hooks with the signature of PyTorch's pluggable CUDA allocator; they serve from the heap of the
+ * communicator that hlSetAllocatorComm named for the device (plain cudaMalloc / cudaFree when there is none). */
+void hlSetAllocatorComm(hlComm_t comm);
+hlComm_t hlGetAllocatorComm(int device);
+void* hlTorchAlloc(ssize_t size, int device, void* stream);
+void hlTorchFree(void* ptr, ssize_t size, int device, void* stream);
 
 /* ---- observability ----------------------------------------------------- */
 typedef struct {

@@ -23,6 +23,9 @@ hlResult_t hlEmuDestroy(hlEmu_t e);
 hlResult_t hlEmuCollective(hlEmu_t e, int kind, const void* const* ins, void* const* outs, size_t count,
                            size_t in_seg_stride, size_t out_seg_stride, int in_dt, int out_dt, int wire_dt,
                            int op, float scale, int root, int algo, int max_blocks, hlStream_t stream);
+/* Registered memory of the emulated group: one buffer per emulated rank at the same heap offset. */
+hlResult_t hlEmuHeapAlloc(hlEmu_t e, size_t bytes, void** ptrs);
+hlResult_t hlEmuHeapFree(hlEmu_t e, void* ptr_rank0);
 hlResult_t hlEmuSetActiveRanks(hlEmu_t e, int k);
 /* status of emulated rank i: 0 ok, 1 a bounded wait ran out. detail = step<<32 | peer. */
 hlResult_t hlEmuStatus(hlEmu_t e, int i, uint64_t* code, uint64_t* detail, uint64_t* block);
@@ -51,6 +54,17 @@ hlResult_t hlIrGenerate(const char* collective, const char* numa_pattern, const 
 hlResult_t hlIrInspect(const char* xml, const char* numa_pattern, int send_segs, int recv_segs, int in_place,
                        hlIrInfo* info);
 hlResult_t hlIrRoundTrip(const char* xml, char* buf, size_t* len);
+/* An id for a group whose ranks are threads of the calling process (they rendezvous in process memory, not through
+ * shared-memory files). Every call names a new group; the all-zero id names one more. */
+hlResult_t hlGetInProcessId(hlUniqueId* id);
+
+/* Collectives whose segments are `stride` elements apart (>= count; 0 = adjacent) in the gathered / scattered buffer.
+ * Dedicated-link path only. */
+hlResult_t hlAllGatherSeg(const void* send, void* recv, size_t count, size_t recv_stride, hlDataType_t t, hlComm_t comm, hlStream_t stream);
+hlResult_t hlReduceScatterSeg(const void* send, void* recv, size_t count, size_t send_stride, hlDataType_t t, hlRedOp_t op, hlComm_t comm,
+                              hlStream_t stream);
+hlResult_t hlAllToAllSeg(const void* send, void* recv, size_t count, size_t send_stride, size_t recv_stride, hlDataType_t t, hlComm_t comm,
+                         hlStream_t stream);
 /* Runs a caller-supplied schedule on the PCIe path of `comm`. */
 hlResult_t hlSubmitIr(hlComm_t comm, const char* xml, const void* send, void* recv, size_t seg_count, size_t stride,
                       int send_segs, int recv_segs, hlDataType_t t, hlRedOp_t op, hlStream_t stream);

@@ -18,7 +18,7 @@ namespace {
 
 constexpr size_t kMaxRanks = HL_NOALLOC_MAX_RANKS;
 constexpr int kMaxBlocks = 16;                                  // CTAs per buffer this entry point ever uses
-constexpr size_t kTableBytes = 256;                             // one HlCommDev, padded
+constexpr size_t kTableBytes = 512;                             // one HlCommDev, padded
 constexpr size_t kTablesOff = 0;                                // [nranks 1..8][rank 0..7] pointer tables
 constexpr size_t kTablesBytes = kMaxRanks * kMaxRanks * kTableBytes;
 constexpr size_t kWordsOff = kTablesOff + kTablesBytes;         // per rank: status (64 B), poison word, sequence words

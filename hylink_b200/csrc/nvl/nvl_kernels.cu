@@ -1060,6 +1060,177 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kAllToAll(const HlCommDev* com
   callDone(c, 0);
 }
 
+// ------------------------------------------------------------------ zero-copy kernels on registered memory
+// Buffers that the library's allocator handed out lie in a symmetric heap: same offset on every rank, every
+// peer's heap mapped here, and (with NVLS) one multicast alias of all of them. These kernels read the peers'
+// inputs and write the peers' outputs IN PLACE — nothing is staged, no byte is copied twice:
+//   all-reduce      NVLS: multimem.ld_reduce of the owned shard straight from all ranks' inputs, scale,
+//                         multimem.st straight into all ranks' outputs.
+//                   P2P:  16-byte loads of the owned shard from every peer's input (ascending rank order, fp32
+//                         accumulate), the result stored into every peer's output.
+//   reduce-scatter  the same loads for segment `rank`, result stored locally.
+//   all-gather      the local input stored into segment `rank` of every rank's output (one multimem.st, or n stores).
+//   broadcast       the root stores into every rank's output.
+// Protocol: announce the heap offsets of this call to every peer | barrier (every peer has entered the call: its
+// input is complete and its output may be overwritten) | check that all ranks use the same offsets | the transfer |
+// barrier (every store has landed; nobody still reads this rank's input). The reference reads registered user
+// buffers of its peers in place as well, but only with copy-engine transfers on its PCIe path
+// (pcie-ccl-cuda/src/core/process_state.cpp:329-510).
+enum ZcColl { kZcAllReduce = 0, kZcReduceScatter = 1, kZcAllGather = 2, kZcBroadcast = 3 };
+constexpr int kZcNvlsUnroll = 8;
+
+__device__ __forceinline__ bool zcHandshake(const HlCommDev& c, const HlCallArgs& a) {
+  const int t = threadIdx.x;
+  if (t < c.nranks) {
+    // plain stores: the release store of the barrier below (same thread) orders them before the flag
+    volatile uint64_t* slot = c.flags[t] + HL_ZC_ARGS_WORD_OFF + 2 * c.rank;
+    slot[0] = a.zc_in_off;
+    slot[1] = a.zc_out_off;
+  }
+  if (!blockBarrier(c, a.seq + 1, 1)) return false;
+  __shared__ int s_sym;
+  if (t == 0) s_sym = 1;
+  __syncthreads();
+  if (t < c.nranks) {
+    const volatile uint64_t* got = c.flags[c.rank] + HL_ZC_ARGS_WORD_OFF + 2 * t;
+    if (got[0] != a.zc_in_off || got[1] != a.zc_out_off) {
+      // a peer passed a buffer at another heap offset: touching anything would read or overwrite the wrong memory
+      volatile uint64_t* st = c.status;
+      st[1] = ((uint64_t)9 << 32) | (uint64_t)t;
+      st[2] = blockIdx.x;
+      st[0] = HL_DEV_ASYMMETRIC;
+      *reinterpret_cast<volatile uint32_t*>(c.abort_word) = 1;
+      __threadfence_system();
+      s_sym = 0;
+    }
+  }
+  __syncthreads();
+  return s_sym != 0;
+}
+
+template <typename W>
+__device__ __forceinline__ uint4 zcScale(uint4 v, float scale) {
+  if (scale != 1.0f) {
+    constexpr int N = Packet<W>::N;
+    typename Wire<W>::Acc acc[N];
+    Packet<W>::unpack(v, acc);
+    finish<W>(acc, scale, 0);
+    v = Packet<W>::pack(acc);
+  }
+  return v;
+}
+
+// `count` is a whole number of 16-byte packets and every buffer is 16-byte aligned (the host side sends anything
+// else through the staged kernels).
+template <typename W, int kColl, bool kNvls, int MR>
+__global__ void __launch_bounds__(HL_NVL_THREADS) kZeroCopy(const HlCommDev* comms, HlEmuCalls calls) {
+  const HlCommDev& c = comms[blockIdx.y];
+  HlCallArgs a = calls.c[blockIdx.y];
+  if (!entryOk(c, a)) return;
+  constexpr int N = Packet<W>::N;
+  const int n = c.nranks, r = c.rank;
+  const Ctx x = makeCtx();
+  if (!zcHandshake(c, a)) return;
+  const uint64_t np = a.count / N;
+  if constexpr (kColl == kZcAllReduce || kColl == kZcReduceScatter) {
+    // all-reduce: the owned shard of the buffer; reduce-scatter: segment r of the input
+    uint64_t first, cnt;
+    if constexpr (kColl == kZcAllReduce) {
+      const uint64_t sp = (np + n - 1) / n;
+      first = (uint64_t)r * sp;
+      cnt = first >= np ? 0 : (np - first < sp ? np - first : sp);
+    } else {
+      first = (uint64_t)r * (a.in_seg_stride / N);
+      cnt = np;
+    }
+    uint4* out_local = reinterpret_cast<uint4*>(a.out);
+    if constexpr (kNvls) {
+      const uint4* mi = reinterpret_cast<const uint4*>(c.mc_heap + a.zc_in_off) + first;
+      uint4* mo = reinterpret_cast<uint4*>(c.mc_heap + a.zc_out_off) + first;
+      for (uint64_t i = x.g0; i < cnt; i += x.gstride * kZcNvlsUnroll) {
+        uint4 v[kZcNvlsUnroll];
+#pragma unroll
+        for (int u = 0; u < kZcNvlsUnroll; ++u) {
+          const uint64_t j = i + (uint64_t)u * x.gstride;
+          if (j < cnt) v[u] = multimemLdReduceAdd<W>(mi + j);
+        }
+#pragma unroll
+        for (int u = 0; u < kZcNvlsUnroll; ++u) {
+          const uint64_t j = i + (uint64_t)u * x.gstride;
+          if (j < cnt) {
+            const uint4 red = zcScale<W>(v[u], a.scale);
+            if constexpr (kColl == kZcAllReduce) multimemSt(mo + j, red);
+            else out_local[j] = red;
+          }
+        }
+      }
+    } else {
+      constexpr int U = MR <= 2 ? 6 : (MR <= 4 ? 3 : 2);
+      for (uint64_t i = x.g0; i < cnt; i += x.gstride * U) {
+        uint4 v[U][MR];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint64_t j = i + (uint64_t)u * x.gstride;
+          if (j < cnt) {
+#pragma unroll
+            for (int q = 0; q < MR; ++q)
+              if (q < n) v[u][q] = (reinterpret_cast<const uint4*>(c.heap[q] + a.zc_in_off) + first)[j];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint64_t j = i + (uint64_t)u * x.gstride;
+          if (j < cnt) {
+            const uint4 red = reducePackets<W, MR>(v[u], n, a.op, a.scale, a.int_div);
+            if constexpr (kColl == kZcAllReduce) {
+#pragma unroll
+              for (int q = 0; q < MR; ++q)
+                if (q < n) (reinterpret_cast<uint4*>(c.heap[(r + q) % n] + a.zc_out_off) + first)[j] = red;
+            } else {
+              out_local[j] = red;
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // all-gather: this rank's input goes to segment r of every output; broadcast: the root's input to every output
+    const bool sender = kColl == kZcAllGather || r == a.root;
+    const uint64_t seg_first = kColl == kZcAllGather ? (uint64_t)r * (a.out_seg_stride / N) : 0;
+    if (sender) {
+      const uint4* in = reinterpret_cast<const uint4*>(a.in);
+      constexpr int U = kPushUnroll;
+      for (uint64_t i = x.g0; i < np; i += x.gstride * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint64_t j = i + (uint64_t)u * x.gstride;
+          if (j < np) v[u] = in[j];
+        }
+        if constexpr (kNvls) {
+          uint4* mo = reinterpret_cast<uint4*>(c.mc_heap + a.zc_out_off) + seg_first;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint64_t j = i + (uint64_t)u * x.gstride;
+            if (j < np) multimemSt(mo + j, v[u]);
+          }
+        } else {
+          for (int k = 0; k < n; ++k) {
+            uint4* po = reinterpret_cast<uint4*>(c.heap[(r + k) % n] + a.zc_out_off) + seg_first;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint64_t j = i + (uint64_t)u * x.gstride;
+              if (j < np) po[j] = v[u];
+            }
+          }
+        }
+      }
+    }
+  }
+  blockBarrier(c, a.seq + 2, 2);
+  callDone(c, 0);
+}
+
 }  // namespace dev
 
 // ====================================================================== host
@@ -1085,6 +1256,14 @@ static const void* pickKernelT(int kind, int nranks) {
       return nranks <= 2 ? (const void*)kPipeCta<W, true, 2> : (nranks <= 4 ? (const void*)kPipeCta<W, true, 4> : (const void*)kPipeCta<W, true, HL_MAX_RANKS>);
     case kNvlReduceScatterPipeP2p:
       return nranks <= 2 ? (const void*)kPipeCta<W, false, 2> : (nranks <= 4 ? (const void*)kPipeCta<W, false, 4> : (const void*)kPipeCta<W, false, HL_MAX_RANKS>);
+    case kNvlZcAllReduceP2p:
+      return nranks <= 2 ? (const void*)kZeroCopy<W, kZcAllReduce, false, 2> : (nranks <= 4 ? (const void*)kZeroCopy<W, kZcAllReduce, false, 4> : (const void*)kZeroCopy<W, kZcAllReduce, false, HL_MAX_RANKS>);
+    case kNvlZcReduceScatterP2p:
+      return nranks <= 2 ? (const void*)kZeroCopy<W, kZcReduceScatter, false, 2> : (nranks <= 4 ? (const void*)kZeroCopy<W, kZcReduceScatter, false, 4> : (const void*)kZeroCopy<W, kZcReduceScatter, false, HL_MAX_RANKS>);
+    case kNvlZcAllGatherP2p: return (const void*)kZeroCopy<W, kZcAllGather, false, 2>;
+    case kNvlZcBroadcastP2p: return (const void*)kZeroCopy<W, kZcBroadcast, false, 2>;
+    case kNvlZcAllGatherNvls: return (const void*)kZeroCopy<W, kZcAllGather, true, 2>;     // multimem.st moves bits: any type
+    case kNvlZcBroadcastNvls: return (const void*)kZeroCopy<W, kZcBroadcast, true, 2>;
     default: break;
   }
   if constexpr (dev::IsFloatTrio<W>::value) {
@@ -1093,6 +1272,8 @@ static const void* pickKernelT(int kind, int nranks) {
       case kNvlReduceScatterNvls: return (const void*)kReduceScatter<W, true>;
       case kNvlAllReducePipeNvls: return (const void*)kPipelined<W, true, true>;
       case kNvlReduceScatterPipeNvls: return (const void*)kPipelined<W, true, false>;
+      case kNvlZcAllReduceNvls: return (const void*)kZeroCopy<W, kZcAllReduce, true, 2>;
+      case kNvlZcReduceScatterNvls: return (const void*)kZeroCopy<W, kZcReduceScatter, true, 2>;
       default: break;
     }
   }
@@ -1137,6 +1318,14 @@ const char* kernelName(int kind) {
     case kNvlAllReducePipeNvls: return "allreduce_pipelined_nvls";
     case kNvlReduceScatterPipeP2p: return "reducescatter_pipelined_p2p";
     case kNvlReduceScatterPipeNvls: return "reducescatter_pipelined_nvls";
+    case kNvlZcAllReduceNvls: return "allreduce_zerocopy_nvls";
+    case kNvlZcAllReduceP2p: return "allreduce_zerocopy_p2p";
+    case kNvlZcReduceScatterNvls: return "reducescatter_zerocopy_nvls";
+    case kNvlZcReduceScatterP2p: return "reducescatter_zerocopy_p2p";
+    case kNvlZcAllGatherNvls: return "allgather_zerocopy_nvls";
+    case kNvlZcAllGatherP2p: return "allgather_zerocopy_p2p";
+    case kNvlZcBroadcastNvls: return "broadcast_zerocopy_nvls";
+    case kNvlZcBroadcastP2p: return "broadcast_zerocopy_p2p";
     default: return "?";
   }
 }
@@ -1172,7 +1361,9 @@ hlResult_t prepareKernels() {
                               kNvlReduceScatter, kNvlReduceScatterNvls, kNvlAllGather, kNvlBroadcast,
                               kNvlAllToAll, kNvlAllGatherNvls, kNvlBroadcastNvls, kNvlAllReducePipeP2p,
                               kNvlAllReducePipeNvls, kNvlReduceScatterPipeP2p, kNvlReduceScatterPipeNvls, kNvlAllReducePush,
-                              kNvlReduceScatterPush, kNvlAllGatherPush, kNvlAllGatherLanes};
+                              kNvlReduceScatterPush, kNvlAllGatherPush, kNvlAllGatherLanes, kNvlZcAllReduceNvls,
+                              kNvlZcAllReduceP2p, kNvlZcReduceScatterNvls, kNvlZcReduceScatterP2p, kNvlZcAllGatherNvls,
+                              kNvlZcAllGatherP2p, kNvlZcBroadcastNvls, kNvlZcBroadcastP2p};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
       for (int nr : {2, 4, HL_MAX_RANKS}) {   // rank-count classes (only the pipelined push kernels differ by it)

@@ -8,7 +8,9 @@ namespace hl {
 
 static constexpr size_t kFlagBytes = (size_t)HL_FLAG_KINDS * HL_MAX_BLOCKS * HL_MAX_RANKS * sizeof(uint64_t);
 
-static size_t flagAreaBytes() { return (kFlagBytes + 4095) & ~(size_t)4095; }
+static constexpr size_t kZcArgBytes = (size_t)HL_MAX_RANKS * 2 * sizeof(uint64_t);   // behind the flag words (HL_ZC_ARGS_WORD_OFF)
+
+static size_t flagAreaBytes() { return (kFlagBytes + kZcArgBytes + 4095) & ~(size_t)4095; }
 
 NvlPath::~NvlPath() {
   if (device_ >= 0) cudaSetDevice(device_);
@@ -20,10 +22,13 @@ NvlPath::~NvlPath() {
   if (timeline_dev_) cudaFree(timeline_dev_);
   if (status_host_) cudaFreeHost(status_host_);
   if (emu_) {
-    for (int q = 0; q < nranks_; ++q)
+    for (int q = 0; q < nranks_; ++q) {
       if (emu_mem_[q]) cudaFree(emu_mem_[q]);
+      if (emu_heap_[q]) cudaFree(emu_heap_[q]);
+    }
   } else {
     const bool gone = bs_ ? bs_->anyFailed() : true;
+    if (heap_region_.mode != kSymmNone) symmFree(bs_, &heap_region_, gone);
     symmFree(bs_, &region_, gone);
   }
   cudaGetLastError();
@@ -63,6 +68,7 @@ hlResult_t NvlPath::finishInit(int timeout_ms) {
     c.stage_bytes = stage_bytes_;
     c.timeout_ns = (uint64_t)timeout_ms * 1000000ull;
   }
+  memcpy(host_comm_, h, sizeof(h));
   HL_CUDA(cudaMalloc((void**)&dcomm_, sizeof(HlCommDev) * nl));
   HL_CUDA(cudaMemcpy(dcomm_, h, sizeof(HlCommDev) * nl, cudaMemcpyHostToDevice));
   HL_CUDA(cudaEventCreateWithFlags(&order_ev_, cudaEventDisableTiming));
@@ -227,6 +233,185 @@ hlResult_t NvlPath::linkProbe(int mode, int blocks, int threads, int unroll, int
   return hlSuccess;
 }
 
+
+// ---------------------------------------------------------------------- registered memory
+static constexpr uint64_t kHeapAlign = 512;
+
+hlResult_t NvlPath::ensureHeap() {
+  if (heap_bytes_ || heap_failed_) return heap_bytes_ ? hlSuccess : hlUnsupported;
+  const Config& cfg = Config::get();
+  size_t want = cfg.symm_heap_bytes;
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CUDA(cudaDeviceSynchronize());   // the per-communicator constants are rewritten below: no launch may be in flight
+  const int nl = localRanks();
+  if (emu_) {
+    want = std::min<size_t>(want, (size_t)256 << 20);   // n heaps on one device
+    for (int q = 0; q < nranks_; ++q) {
+      if (cudaMalloc(&emu_heap_[q], want) != cudaSuccess) {
+        cudaGetLastError();
+        heap_failed_ = true;
+        return hlUnsupported;
+      }
+    }
+  } else {
+    hlResult_t r = symmAlloc(bs_, device_, want, cfg.nvls, cfg.symm_mode, &heap_region_);
+    if (r != hlSuccess) {
+      HL_WARN("registered-memory heap of %zu MiB could not be created; buffers will be staged", want >> 20);
+      heap_failed_ = true;
+      heap_region_ = SymmRegion();
+      return hlUnsupported;
+    }
+    heap_mc_ = heap_region_.mc != nullptr;
+  }
+  for (int i = 0; i < nl; ++i) {
+    HlCommDev& c = host_comm_[i];
+    for (int q = 0; q < nranks_; ++q) c.heap[q] = (uint8_t*)(emu_ ? emu_heap_[q] : heap_region_.ptr[q]);
+    c.mc_heap = emu_ ? nullptr : (uint8_t*)heap_region_.mc;
+    c.heap_bytes = want;
+  }
+  HL_CUDA(cudaMemcpy(dcomm_, host_comm_, sizeof(HlCommDev) * nl, cudaMemcpyHostToDevice));
+  HL_CUDA(cudaDeviceSynchronize());
+  heap_bytes_ = want;
+  heap_free_.clear();
+  heap_used_.clear();
+  heap_free_[0] = want;
+  if (!emu_ && bs_) HL_CHECK(bs_->barrier(kBarSymm));
+  HL_INFO("registered-memory heap ready: %zu MiB per rank, multicast=%d", want >> 20, (int)heap_mc_);
+  return hlSuccess;
+}
+
+hlResult_t NvlPath::heapAlloc(size_t bytes, void** ptrs) {
+  if (!ptrs || bytes == 0) return fail(hlInvalidArgument, "heap allocation of %zu bytes", bytes);
+  if (ensureHeap() != hlSuccess) return hlUnsupported;
+  const uint64_t need = ((uint64_t)bytes + kHeapAlign - 1) & ~(kHeapAlign - 1);
+  for (auto it = heap_free_.begin(); it != heap_free_.end(); ++it) {   // first fit: the same choice on every rank
+    if (it->second < need) continue;
+    const uint64_t off = it->first, len = it->second;
+    heap_free_.erase(it);
+    if (len > need) heap_free_[off + need] = len - need;
+    heap_used_[off] = need;
+    for (int i = 0; i < localRanks(); ++i) ptrs[i] = host_comm_[i].heap[host_comm_[i].rank] + off;
+    return hlSuccess;
+  }
+  return hlUnsupported;   // exhausted (identically on every rank)
+}
+
+hlResult_t NvlPath::heapFree(void* p) {
+  if (!heap_bytes_ || !p) return hlInvalidArgument;
+  const uint8_t* base = host_comm_[0].heap[host_comm_[0].rank];
+  if ((const uint8_t*)p < base || (const uint8_t*)p >= base + heap_bytes_) return hlInvalidArgument;
+  uint64_t off = (uint64_t)((const uint8_t*)p - base);
+  auto it = heap_used_.find(off);
+  if (it == heap_used_.end()) return fail(hlInvalidArgument, "not the start of a registered allocation");
+  uint64_t len = it->second;
+  heap_used_.erase(it);
+  auto next = heap_free_.lower_bound(off);
+  if (next != heap_free_.end() && next->first == off + len) {   // merge with the following hole
+    len += next->second;
+    next = heap_free_.erase(next);
+  }
+  if (next != heap_free_.begin()) {
+    auto prev = std::prev(next);
+    if (prev->first + prev->second == off) {   // and with the one before
+      prev->second += len;
+      return hlSuccess;
+    }
+  }
+  heap_free_[off] = len;
+  return hlSuccess;
+}
+
+size_t NvlPath::heapInUse() const {
+  size_t t = 0;
+  for (auto& kv : heap_used_) t += kv.second;
+  return t;
+}
+
+bool NvlPath::heapOffset(int i, const void* p, size_t bytes, uint64_t* off) const {
+  if (!heap_bytes_ || !p) return false;
+  const uint8_t* base = host_comm_[i].heap[host_comm_[i].rank];
+  const uint8_t* q = (const uint8_t*)p;
+  if (q < base || q + bytes > base + heap_bytes_) return false;
+  *off = (uint64_t)(q - base);
+  return true;
+}
+
+// Which flavour of zero-copy kernel a call gets. Reductions go through the switch when NVLS pays (it halves the
+// inbound traffic) and the call allows it; pure data movement uses posted peer stores unless NVLS is asked for
+// by name (measured on 4 GPUs: multimem.st into staging moved 430 GB/s where peer stores moved 627).
+int NvlPath::zeroCopyFlavour(const NvlCall& c, bool reduce) const {
+  if (!Config::get().zero_copy && c.algo == hlAlgoAuto) return 0;
+  if (c.algo != hlAlgoAuto && c.algo != hlAlgoZeroCopy && c.algo != hlAlgoZeroCopyNvls && c.algo != hlAlgoZeroCopyP2p) return 0;
+  if (c.algo == hlAlgoZeroCopyP2p) return 2;
+  const bool mc_ok = heap_mc_ && (!reduce || ((c.wire_dt == hlFloat32 || c.wire_dt == hlFloat16 || c.wire_dt == hlBfloat16) &&
+                                               (c.op == hlSum || c.op == hlAvg) && !c.deterministic));
+  if (c.algo == hlAlgoZeroCopyNvls) return mc_ok ? 1 : 0;
+  static const int reduce_pref = (int)envInt({"HYLINK_ZC_REDUCE_NVLS"}, -1), gather_pref = (int)envInt({"HYLINK_ZC_GATHER_NVLS"}, 0);
+  const int pref = reduce ? reduce_pref : gather_pref;
+  if (!mc_ok || pref == 0) return 2;
+  if (pref == 1) return 1;
+  return nranks_ >= Config::get().nvls_min_ranks ? 1 : 2;
+}
+
+bool NvlPath::zeroCopyEligible(const NvlBufs& b, const NvlCall& c, bool in_remote, bool out_remote, uint64_t in_extent, uint64_t out_extent,
+                               uint64_t* in_off, uint64_t* out_off) const {
+  if (!heap_bytes_ || c.in_dt != c.wire_dt || c.out_dt != c.wire_dt) return false;
+  const uint64_t ws = hlTypeSize((hlDataType_t)c.wire_dt);
+  const uint64_t epp = 16 / ws;
+  if (c.count % epp) return false;                            // whole 16-byte packets only
+  if ((c.in_seg_stride % epp) || (c.out_seg_stride % epp)) return false;
+  *in_off = *out_off = 0;
+  for (int i = 0; i < localRanks(); ++i) {
+    if (((uintptr_t)b.in[i] | (uintptr_t)b.out[i]) & 15) return false;
+    uint64_t io = 0, oo = 0;
+    if (in_remote && !heapOffset(i, b.in[i], in_extent * ws, &io)) return false;
+    if (out_remote && !heapOffset(i, b.out[i], out_extent * ws, &oo)) return false;
+    if (i == 0) {
+      *in_off = io;
+      *out_off = oo;
+    } else if (io != *in_off || oo != *out_off) {
+      return false;
+    }
+  }
+  return true;
+}
+
+hlResult_t NvlPath::launchZeroCopy(int kind, const NvlBufs& b, const NvlCall& c, uint64_t in_off, uint64_t out_off, size_t bytes_per_rank,
+                                   cudaStream_t s) {
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CHECK(orderAfterPrevious(s));
+  const int nl = localRanks();
+  HlEmuCalls calls;
+  memset(&calls, 0, sizeof(calls));
+  for (int i = 0; i < nl; ++i) {
+    HlCallArgs& a = calls.c[i];
+    a.in = b.in[i];
+    a.out = b.out[i];
+    a.count = c.count;
+    a.in_seg_stride = c.in_seg_stride ? c.in_seg_stride : c.count;
+    a.out_seg_stride = c.out_seg_stride ? c.out_seg_stride : c.count;
+    a.scale = (c.scale == 0.0f ? 1.0f : c.scale) * (c.op == hlAvg ? 1.0f / (float)nranks_ : 1.0f);
+    a.op = c.op;
+    a.in_dt = c.in_dt;
+    a.out_dt = c.out_dt;
+    a.root = c.root;
+    a.int_div = (c.op == hlAvg) ? nranks_ : 0;
+    a.kind = kind;
+    a.zc_in_off = in_off;
+    a.zc_out_off = out_off;
+  }
+  // one CTA per 16 KiB of this rank's share (every thread owns a packet or two, so that all remote accesses of a
+  // small call are in flight at once), up to one per SM
+  int cap = c.max_blocks > 0 ? c.max_blocks : (Config::get().nvl_max_blocks > 0 ? Config::get().nvl_max_blocks : 148);
+  if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));
+  static const size_t per_cta = (size_t)envInt({"HYLINK_ZC_BYTES_PER_CTA"}, 16LL << 10);
+  const size_t want = std::max<size_t>(1, (bytes_per_rank + per_cta - 1) / per_cta);
+  const int blocks = (int)std::min<size_t>(want, (size_t)std::min(cap, HL_MAX_BLOCKS));
+  HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, emu_ ? emu_active_ : 1, blocks, s, nranks_));
+  ++launches_;
+  return hlSuccess;
+}
+
 int NvlPath::blocksFor(int kind, size_t wire_bytes_per_rank, int max_blocks) const {
   int cap = max_blocks > 0 ? max_blocks : (Config::get().nvl_max_blocks > 0 ? Config::get().nvl_max_blocks : 148);
   if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));
@@ -326,9 +511,18 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
   return hlSuccess;
 }
 
+static bool wantsZeroCopy(int algo) { return algo == hlAlgoZeroCopy || algo == hlAlgoZeroCopyNvls || algo == hlAlgoZeroCopyP2p; }
+
 hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
+  {
+    uint64_t io, oo;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, true) : 0;
+    if (zc && zeroCopyEligible(b, c, true, true, c.count, c.count, &io, &oo))
+      return launchZeroCopy(zc == 1 ? kNvlZcAllReduceNvls : kNvlZcAllReduceP2p, b, c, io, oo, wire_bytes / (size_t)nranks_, s);
+    if (wantsZeroCopy(c.algo)) return fail(hlUnsupported, "all-reduce: zero-copy needs registered, 16-byte aligned buffers of whole 16-byte packets");
+  }
   int algo = pickAllReduceAlgo(wire_bytes, c.wire_dt, c.op, c.deterministic, c.algo);
   if (algo == hlAlgoOneShot && wire_bytes > stage_bytes_) algo = hlAlgoTwoShotP2p;
   const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;  // the push kernels do not convert
@@ -357,6 +551,14 @@ size_t NvlPath::lanesMinBytes() const {
 hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
+  {
+    uint64_t io, oo;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, true) : 0;
+    const uint64_t stride = c.in_seg_stride ? c.in_seg_stride : c.count;
+    if (zc && zeroCopyEligible(b, c, true, false, stride * (uint64_t)(nranks_ - 1) + c.count, c.count, &io, &oo))
+      return launchZeroCopy(zc == 1 ? kNvlZcReduceScatterNvls : kNvlZcReduceScatterP2p, b, c, io, 0, wire_bytes / (size_t)nranks_, s);
+    if (wantsZeroCopy(c.algo)) return fail(hlUnsupported, "reduce-scatter: zero-copy needs a registered, 16-byte aligned input of whole 16-byte packets");
+  }
   const bool nvls = nvlsUsable(c.wire_dt, c.op, c.deterministic) && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot &&
                     (c.algo == hlAlgoNvls || c.algo == hlAlgoPipelined || nvlsPays());
   const bool same = c.in_dt == c.wire_dt && c.out_dt == c.wire_dt;
@@ -375,6 +577,14 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
 
 hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
+  {
+    uint64_t io, oo;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, false) : 0;
+    const uint64_t stride = c.out_seg_stride ? c.out_seg_stride : c.count;
+    if (zc && zeroCopyEligible(b, c, false, true, c.count, stride * (uint64_t)(nranks_ - 1) + c.count, &io, &oo))
+      return launchZeroCopy(zc == 1 ? kNvlZcAllGatherNvls : kNvlZcAllGatherP2p, b, c, 0, oo, c.count * hlTypeSize((hlDataType_t)c.wire_dt), s);
+    if (wantsZeroCopy(c.algo)) return fail(hlUnsupported, "all-gather: zero-copy needs a registered, 16-byte aligned output of whole 16-byte packets");
+  }
   const bool nvls = has_mc_ && c.algo == hlAlgoNvls;
   if (nvls) return launchSliced(kNvlAllGatherNvls, b, c, true, s);
   // peer pointers: the stores-only kernel unless the call converts types or asks for the pull kernel by name
@@ -389,6 +599,13 @@ hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s
 hlResult_t NvlPath::broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   if (c.root < 0 || c.root >= nranks_) return fail(hlInvalidArgument, "broadcast root %d out of range", c.root);
+  {
+    uint64_t io, oo;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, false) : 0;
+    if (zc && zeroCopyEligible(b, c, false, true, c.count, c.count, &io, &oo))
+      return launchZeroCopy(zc == 1 ? kNvlZcBroadcastNvls : kNvlZcBroadcastP2p, b, c, 0, oo, c.count * hlTypeSize((hlDataType_t)c.wire_dt), s);
+    if (wantsZeroCopy(c.algo)) return fail(hlUnsupported, "broadcast: zero-copy needs a registered, 16-byte aligned buffer of whole 16-byte packets");
+  }
   const bool nvls = has_mc_ && c.algo != hlAlgoTwoShotP2p && c.algo != hlAlgoOneShot;
   return launchSliced(nvls ? kNvlBroadcastNvls : kNvlBroadcast, b, c, false, s);
 }

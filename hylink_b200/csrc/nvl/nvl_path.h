@@ -13,6 +13,8 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <map>
+
 #include "ctrl/bootstrap.h"
 #include "nvl/nvl_launch.h"
 #include "nvl/symm_mem.h"
@@ -73,6 +75,16 @@ class NvlPath {
   // Clears the poison after a recorded timeout (all ranks, collectively, with
   // no launch in flight); flags and sequence restart from a common value.
   hlResult_t resetAfterError();
+  // Registered memory: a symmetric heap (same size on every rank, every peer's heap mapped here, one multicast alias
+  // with NVLS), created at the first allocation. Allocation and release are collective in effect: every rank must
+  // issue the same sequence of sizes, so that a buffer sits at the same offset everywhere. `ptrs` receives one
+  // pointer per local rank (one, except in the emulated group). Returns hlUnsupported when the heap is exhausted
+  // or cannot be created; the caller then falls back to ordinary device memory.
+  hlResult_t heapAlloc(size_t bytes, void** ptrs);
+  hlResult_t heapFree(void* ptr_of_local_rank0);
+  bool heapOffset(int local_rank, const void* p, size_t bytes, uint64_t* off) const;
+  size_t heapBytes() const { return heap_bytes_; }
+  size_t heapInUse() const;
   int pickAllReduceAlgo(size_t wire_bytes, int wire_dt, int op, bool deterministic, int requested) const;
   bool nvlsPays() const;
   size_t pipeMinBytes() const;
@@ -86,6 +98,13 @@ class NvlPath {
   hlResult_t finishInit(int timeout_ms);
   hlResult_t launchSliced(int kind, const NvlBufs& b, const NvlCall& c, bool segmented, cudaStream_t s);
   hlResult_t orderAfterPrevious(cudaStream_t s);
+  hlResult_t ensureHeap();
+  // Zero-copy kernels: which buffers peers reach in place (and therefore have to be registered, aligned and whole packets).
+  bool zeroCopyEligible(const NvlBufs& b, const NvlCall& c, bool in_remote, bool out_remote, uint64_t in_extent, uint64_t out_extent,
+                        uint64_t* in_off, uint64_t* out_off) const;
+  hlResult_t launchZeroCopy(int kind, const NvlBufs& b, const NvlCall& c, uint64_t in_off, uint64_t out_off, size_t bytes_per_rank,
+                            cudaStream_t s);
+  int zeroCopyFlavour(const NvlCall& c, bool reduce) const;   // 0 none, 1 NVLS, 2 peer pointers
   Bootstrap* bs_ = nullptr;
   bool emu_ = false;
   int emu_active_ = 0;
@@ -100,6 +119,14 @@ class NvlPath {
   uint64_t* timeline_dev_ = nullptr;  // kernel timeline ring per local rank, null when off
   uint64_t* seq_dev_ = nullptr;    // per local rank: flag base, tile base, finished-CTA counter (advanced by the kernels)
   uint64_t launches_ = 0;
+  SymmRegion heap_region_;
+  void* emu_heap_[HL_MAX_RANKS] = {nullptr};
+  size_t heap_bytes_ = 0;
+  bool heap_failed_ = false;
+  bool heap_mc_ = false;
+  std::map<uint64_t, uint64_t> heap_free_;   // offset -> length
+  std::map<uint64_t, uint64_t> heap_used_;
+  HlCommDev host_comm_[HL_MAX_RANKS];
   cudaEvent_t order_ev_ = nullptr;
   cudaStream_t last_stream_ = nullptr;
   bool have_last_ = false;

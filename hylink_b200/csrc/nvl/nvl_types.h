@@ -41,7 +41,16 @@ struct HlCommDev {
   uint64_t stage_bytes;
   uint64_t timeout_ns;
   uint64_t* timeline;              // device ring of HL_TL_WORDS words, null when the timeline is off
+  // Registered (symmetric) user memory: every rank owns a heap of heap_bytes; buffers handed out by the library's
+  // allocator lie at the same offset on every rank, so a kernel reaches a peer's buffer as heap[q] + offset and all
+  // ranks' copies at once as mc_heap + offset. Null / 0 until the heap exists.
+  uint8_t* heap[HL_MAX_RANKS];
+  uint8_t* mc_heap;                // NVSwitch multicast alias of the heap (null without NVLS)
+  uint64_t heap_bytes;
 };
+// Behind the flag words of every rank sit [HL_MAX_RANKS][2] words in which peer q announces the heap offsets
+// (in, out) of its buffers for the running zero-copy call; they must equal the local ones.
+#define HL_ZC_ARGS_WORD_OFF ((size_t)HL_FLAG_KINDS * HL_MAX_BLOCKS * HL_MAX_RANKS)
 
 // Per-call arguments (by value in the launch).
 struct HlCallArgs {
@@ -61,6 +70,8 @@ struct HlCallArgs {
   uint64_t tile_packets;    // pipelined kernels: 16-byte packets of one shard handled per tile
   int kind;                 // HlNvlKernel, recorded in the kernel timeline
   int lane_parts;           // lane kernels (reduce-scatter, all-gather): HBM-side CTAs per pusher CTA (1..7)
+  uint64_t zc_in_off;       // zero-copy kernels: heap offset of `in` (valid when the kernel reads `in` from peers)
+  uint64_t zc_out_off;      // zero-copy kernels: heap offset of `out` (valid when the kernel writes peers' `out`)
 };
 
 // One argument block per emulated rank: on a single GPU the N ranks of a test
@@ -90,4 +101,14 @@ enum HlNvlKernel {
   kNvlReduceScatterPush = 16,
   kNvlAllGatherPush = 17,
   kNvlAllGatherLanes = 18,
+  // zero-copy kernels on registered memory: peers' buffers are read / written in place, nothing is staged
+  kNvlZcAllReduceNvls = 19,
+  kNvlZcAllReduceP2p = 20,
+  kNvlZcReduceScatterNvls = 21,
+  kNvlZcReduceScatterP2p = 22,
+  kNvlZcAllGatherNvls = 23,
+  kNvlZcAllGatherP2p = 24,
+  kNvlZcBroadcastNvls = 25,
+  kNvlZcBroadcastP2p = 26,
 };
+#define HL_DEV_ASYMMETRIC 4   // zero-copy call whose buffers do not sit at the same heap offset on every rank

@@ -26,6 +26,7 @@
 #include <torch/csrc/distributed/c10d/Work.hpp>
 #include <torch/python.h>
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -125,13 +126,22 @@ class HylinkWork : public c10d::Work {
     c10::cuda::CUDAStreamGuard g(comm_stream);
     future_->markCompleted(at::IValue(outputs_));
   }
+  // One-rank groups: the work ran on the caller's own stream, so there is nothing to wait for on that stream and
+  // no event is recorded (an event pair per call is most of the cost of a collective that moves nothing).
+  void armInline(c10::cuda::CUDAStream stream, const std::shared_ptr<EventPool>& pool) {
+    cuda_ = true;
+    inline_ = true;
+    device_ = stream.device();
+    pool_ = pool;
+    inline_stream_ = stream.stream();
+  }
   void armCpu() {
     future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
     future_->markCompleted(at::IValue(outputs_));
   }
 
   bool isCompleted() override {
-    if (!cuda_) return true;
+    if (!cuda_ || (inline_ && !event_)) return true;
     const cudaError_t e = cudaEventQuery(event_);
     if (e == cudaErrorNotReady) {
       (void)cudaGetLastError();
@@ -141,20 +151,38 @@ class HylinkWork : public c10d::Work {
   }
   bool isSuccess() const override { return true; }
   void synchronize() override {
-    if (cuda_) C10_CUDA_CHECK(cudaStreamWaitEvent(c10::cuda::getCurrentCUDAStream(device_.index()).stream(), event_, 0));
+    if (!cuda_) return;
+    cudaStream_t cur = c10::cuda::getCurrentCUDAStream(device_.index()).stream();
+    if (inline_) {
+      if (cur == inline_stream_) return;   // stream order already covers it
+      if (!event_) {                       // recorded late: covers the work and whatever followed it on that stream
+        event_ = pool_->acquire();
+        C10_CUDA_CHECK(cudaEventRecord(event_, inline_stream_));
+      }
+    }
+    C10_CUDA_CHECK(cudaStreamWaitEvent(cur, event_, 0));
   }
   bool wait(std::chrono::milliseconds /*timeout*/) override {
     synchronize();
     keep_.clear();
     return true;
   }
-  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override { return future_; }
+  c10::intrusive_ptr<c10::ivalue::Future> getFuture() override {
+    if (!future_ && inline_) {
+      future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()), std::vector<c10::Device>{device_});
+      c10::cuda::CUDAStreamGuard g(c10::cuda::getStreamFromExternal(inline_stream_, device_.index()));
+      future_->markCompleted(at::IValue(outputs_));
+    }
+    return future_;
+  }
   std::vector<at::Tensor> result() override { return outputs_; }
 
  private:
   std::vector<at::Tensor> outputs_;
   std::vector<at::Tensor> keep_;  // inputs kept alive until the caller has waited
   bool cuda_ = false;
+  bool inline_ = false;
+  cudaStream_t inline_stream_ = nullptr;
   c10::Device device_{c10::kCPU};
   cudaEvent_t event_ = nullptr;
   std::shared_ptr<EventPool> pool_;
@@ -177,6 +205,7 @@ class HylinkBackend : public c10d::Backend {
 
   void shutdown() override {
     std::lock_guard<std::mutex> lk(mu_);
+    alive_->store(false);   // registered tensors that outlive the group must not reach into a destroyed communicator
     if (cuda_comm_) {
       hlCommDestroy(cuda_comm_);
       cuda_comm_ = nullptr;
@@ -215,6 +244,7 @@ class HylinkBackend : public c10d::Backend {
       comm_stream_ = std::make_unique<c10::cuda::CUDAStream>(c10::cuda::getStreamFromPool(/*isHighPriority=*/hp && atoi(hp) != 0, device));
     }
     hlCheck(hlCommInitRankDevice(&slot, getSize(), id, getRank(), device), "hlCommInitRankDevice");
+    if (cuda) hlSetAllocatorComm(slot);   // the registered-memory allocator hooks serve from this communicator's heap
     if (cuda && ready_ring_.empty()) {
       c10::cuda::CUDAGuard dg(t.device());
       ready_ring_.resize(64);
@@ -228,7 +258,14 @@ class HylinkBackend : public c10d::Backend {
                                      std::vector<at::Tensor> keep, F&& body) {
     hlComm_t comm = commFor(probe);
     auto work = c10::make_intrusive<HylinkWork>(getRank(), type, std::move(outputs), std::move(keep));
-    if (probe.is_cuda()) {
+    if (probe.is_cuda() && getSize() == 1) {
+      // one rank: every collective is local work; it runs on the caller's stream, with no hop to another stream
+      c10::cuda::CUDAGuard dg(probe.device());
+      auto cur = c10::cuda::getCurrentCUDAStream(probe.device().index());
+      body(comm, (hlStream_t)cur.stream());
+      work->armInline(cur, events_);
+      ++collectives_;
+    } else if (probe.is_cuda()) {
       c10::cuda::CUDAGuard dg(probe.device());
       auto cur = c10::cuda::getCurrentCUDAStream(probe.device().index());
       cudaEvent_t ready = ready_ring_[ready_next_++ % ready_ring_.size()];
@@ -308,7 +345,7 @@ class HylinkBackend : public c10d::Backend {
     return run(OpType::ALLGATHER, in, dst, {in, flat}, [&](hlComm_t c, hlStream_t s) {
       hlCheck(hlAllGather(in.data_ptr(), flat.data_ptr(), (size_t)in.numel(), toHl(in.scalar_type()), c, s), "allgather");
       c10::OptionalStreamGuard sg;
-      if (in.is_cuda()) sg.reset_stream(*comm_stream_);
+      if (in.is_cuda()) sg.reset_stream(c10::cuda::getStreamFromExternal((cudaStream_t)s, in.device().index()));
       else hlCheck(hlCommDrain(c), "hlCommDrain");  // host path: the gather must have landed before it is split up
       for (int q = 0; q < getSize(); ++q) dst[q].copy_(flat.narrow(0, (int64_t)q * in.numel(), in.numel()).view_as(dst[q]), true);
     });
@@ -352,12 +389,13 @@ class HylinkBackend : public c10d::Backend {
     at::Tensor probe = out;
     return run(OpType::REDUCE_SCATTER, probe, {out}, parts, [&](hlComm_t c, hlStream_t s) {
       c10::OptionalStreamGuard sg;
-      if (out.is_cuda()) sg.reset_stream(*comm_stream_);
+      if (out.is_cuda()) sg.reset_stream(c10::cuda::getStreamFromExternal((cudaStream_t)s, out.device().index()));
       std::vector<at::Tensor> flat_parts;
       for (auto& p : parts) flat_parts.push_back(p.reshape({-1}));
       at::Tensor flat = at::cat(flat_parts);
       hlCheck(hlReduceScatter(flat.data_ptr(), out.data_ptr(), (size_t)out.numel(), toHl(out.scalar_type()), oi.op, c, s), "reduce_scatter");
-      if (out.is_cuda()) c10::cuda::CUDACachingAllocator::recordStream(flat.storage().data_ptr(), *comm_stream_);
+      if (out.is_cuda())
+        c10::cuda::CUDACachingAllocator::recordStream(flat.storage().data_ptr(), c10::cuda::getStreamFromExternal((cudaStream_t)s, out.device().index()));
     });
   }
 
@@ -421,6 +459,25 @@ class HylinkBackend : public c10d::Backend {
   }
 
   // ---- extras exposed to Python -------------------------------------------
+  // A tensor in registered memory (same heap offset on every rank): collectives on it run zero-copy. Every rank
+  // must call this in the same order with the same sizes. Falls back to ordinary device memory when the heap is full.
+  at::Tensor symmetricEmpty(std::vector<int64_t> sizes, at::ScalarType dtype, int device) {
+    at::Tensor probe = at::empty({1}, at::TensorOptions().device(at::kCUDA, device).dtype(at::kFloat));
+    hlComm_t comm = commFor(probe);
+    int64_t numel = 1;
+    for (auto d : sizes) numel *= d;
+    const size_t bytes = (size_t)std::max<int64_t>(numel, 1) * c10::elementSize(dtype);
+    void* ptr = nullptr;
+    hlCheck(hlMemAlloc(comm, bytes, &ptr), "hlMemAlloc");
+    std::shared_ptr<std::atomic<bool>> alive = alive_;
+    // (after the group is gone its heap is gone with it: nothing left to release)
+    return at::from_blob(ptr, sizes, [comm, alive](void* p) { if (alive->load()) hlMemFree(comm, p); },
+                         at::TensorOptions().device(at::kCUDA, device).dtype(dtype));
+  }
+  bool isRegistered(const at::Tensor& t) {
+    std::lock_guard<std::mutex> lk(mu_);
+    return cuda_comm_ && t.is_cuda() && hlMemIsRegistered(cuda_comm_, t.data_ptr(), t.nbytes()) != 0;
+  }
   void setFusedScale(float s) { fused_scale_ = s; }
   void setCtaBudget(int b) { max_blocks_ = b < 0 ? 0 : b; }
   int ctaBudget() const { return max_blocks_; }
@@ -462,6 +519,7 @@ class HylinkBackend : public c10d::Backend {
   std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
   float fused_scale_ = 0.0f;
   int max_blocks_ = 0;
+  std::shared_ptr<std::atomic<bool>> alive_ = std::make_shared<std::atomic<bool>>(true);
 };
 
 c10::intrusive_ptr<c10d::Backend> createHylinkBackend(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size,
@@ -483,6 +541,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // Multiplies every all-reduce result by `scale` inside the kernel (0 = off):
   // lets a DDP wrapper fold its gradient pre-division into the collective.
   m.def("set_fused_scale", [](const c10::intrusive_ptr<c10d::Backend>& b, float s) { asHylink(b)->setFusedScale(s); });
+  m.def("symmetric_empty", [](const c10::intrusive_ptr<c10d::Backend>& b, std::vector<int64_t> sizes, py::object dtype, int device) {
+    return asHylink(b)->symmetricEmpty(std::move(sizes), torch::python::detail::py_object_to_dtype(dtype), device);
+  });
+  m.def("is_registered", [](const c10::intrusive_ptr<c10d::Backend>& b, const at::Tensor& t) { return asHylink(b)->isRegistered(t); });
   // CTAs a collective of this group may occupy (0 = the library's size table). Returns the previous budget.
   m.def("set_cta_budget", [](const c10::intrusive_ptr<c10d::Backend>& b, int n) {
     const int old = asHylink(b)->ctaBudget();

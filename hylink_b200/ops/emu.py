@@ -17,7 +17,8 @@ import torch
 from .._native import OPS, check, lib, torch_dtype_code
 
 KINDS = {"all_reduce": 0, "reduce_scatter": 1, "all_gather": 2, "broadcast": 3, "all_to_all": 4, "barrier": 5}
-ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5}
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5, "zerocopy": 6, "zerocopy_nvls": 7,
+         "zerocopy_p2p": 8}
 
 
 class EmuGroup:
@@ -55,6 +56,14 @@ class EmuGroup:
                                   out_seg_stride, in_dt, out_dt, wire_dt, OPS[op], scale, root, ALGOS[algo],
                                   max_blocks, C.c_void_p(stream)), f"emu {kind}")
 
+    def alloc_registered(self, numel: int, dtype=torch.float32):
+        """One tensor per emulated rank in registered memory (the same heap offset on every rank)."""
+        es = torch.empty((), dtype=dtype).element_size()
+        ptrs = (C.c_void_p * self.nranks)()
+        check(lib.hlEmuHeapAlloc(self._h, numel * es, ptrs), "hlEmuHeapAlloc")
+        holder = _HeapBlock(self, ptrs[0])
+        return [_tensor_at(ptrs[i], numel, dtype, holder) for i in range(self.nranks)]
+
     def kernel_timeline(self, i: int = 0):
         """Decoded kernel timeline of emulated rank ``i`` (needs ``HYLINK_KERNEL_TIMELINE=1`` when the group is made)."""
         from ..utils.kernel_timeline import decode
@@ -81,3 +90,34 @@ class EmuGroup:
         n = C.c_uint64()
         check(lib.hlEmuLaunches(self._h, C.byref(n)), "hlEmuLaunches")
         return n.value
+
+
+class _HeapBlock:
+    """Releases a registered allocation of the emulated group when its last tensor goes away."""
+
+    def __init__(self, group: EmuGroup, ptr0):
+        self.group, self.ptr0 = group, ptr0
+
+    def __del__(self):
+        try:
+            if self.group._h:
+                lib.hlEmuHeapFree(self.group._h, C.c_void_p(self.ptr0))
+        except Exception:
+            pass
+
+
+class _Raw:
+    """Just enough of the CUDA array interface for torch.as_tensor to wrap device memory it does not own."""
+
+    def __init__(self, ptr, nbytes, holder):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 3}
+        self._holder = holder
+
+
+def _tensor_at(ptr, numel, dtype, holder):
+    es = torch.empty((), dtype=dtype).element_size()
+    raw = torch.as_tensor(_Raw(ptr, numel * es, holder), device="cuda")
+    t = raw.view(dtype)
+    if holder is not None:
+        t._hl_holder = holder   # the view keeps the allocation alive
+    return t

@@ -78,3 +78,46 @@ def set_cta_budget(ctas: int, group=None) -> int:
     leave the other SMs to the compute stream. Stand-alone collectives run fastest with no budget.
     """
     return int(_load_ext().set_cta_budget(_backend_of(group), int(ctas)))
+
+
+def symmetric_empty(shape, dtype=None, group=None, device=None):
+    """An uninitialised CUDA tensor in the group's registered memory.
+
+    Registered buffers sit at the same offset of a symmetric heap on every rank; collectives whose buffers are
+    registered run zero-copy (peers' inputs read and peers' outputs written in place through NVLink / NVSwitch).
+    Every rank must call this in the same order with the same sizes, and release the tensors in the same order.
+    """
+    import torch
+
+    if isinstance(shape, int):
+        shape = (shape,)
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    return _load_ext().symmetric_empty(_backend_of(group), list(shape), dtype or torch.float32, dev)
+
+
+def is_registered(tensor, group=None) -> bool:
+    """Whether the tensor lies in the group's registered memory."""
+    return bool(_load_ext().is_registered(_backend_of(group), tensor))
+
+
+_pool = None
+
+
+def registered_mem_pool():
+    """A ``torch.cuda.MemPool`` whose memory is registered with the group of the ``hylink`` backend.
+
+    Tensors created under ``torch.cuda.use_mem_pool(pool)`` (for instance the gradient buckets of a
+    ``DistributedDataParallel`` wrapper built there) come from the symmetric heap, so collectives on them run
+    zero-copy. All ranks must allocate in the same order, which any SPMD program does. The process group's
+    communicator must exist (one collective has run) before the first allocation.
+    """
+    global _pool
+    if _pool is None:
+        import torch
+        from torch.cuda.memory import CUDAPluggableAllocator
+
+        from .. import _native
+
+        alloc = CUDAPluggableAllocator(str(_native._LIB_PATH), "hlTorchAlloc", "hlTorchFree")
+        _pool = (torch.cuda.MemPool(alloc.allocator()), alloc)
+    return _pool[0]

@@ -11,7 +11,8 @@ import ctypes as C
 from .._native import CallOpts, CommStats, OPS, UniqueId, check, lib, torch_dtype_code
 
 PATHS = {"auto": 0, "nvlink": 1, "pcie": 2, "split": 3}
-ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5}
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5, "zerocopy": 6, "zerocopy_nvls": 7,
+         "zerocopy_p2p": 8}
 
 
 def unique_id() -> bytes:
@@ -99,6 +100,23 @@ class Communicator:
                                torch_dtype_code(send.dtype), C.byref(o), self._h, self._stream(send)), "hlAllToAllEx")
         return recv
 
+    def alloc_registered(self, numel: int, dtype=None):
+        """A tensor in the communicator's registered memory (see ``hlMemAlloc``): collectives on it run zero-copy.
+        Collective in effect: every rank calls it in the same order with the same sizes."""
+        import torch
+
+        from ..ops.emu import _tensor_at
+
+        dtype = dtype or torch.float32
+        es = torch.empty((), dtype=dtype).element_size()
+        p = C.c_void_p()
+        check(lib.hlMemAlloc(self._h, numel * es, C.byref(p)), "hlMemAlloc")
+        return _tensor_at(p.value, numel, dtype, _CommBlock(self, p.value))
+
+    def is_registered(self, t) -> bool:
+        lib.hlMemIsRegistered.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        return bool(lib.hlMemIsRegistered(self._h, C.c_void_p(t.data_ptr()), t.numel() * t.element_size()))
+
     def barrier(self, stream=None):
         import torch
 
@@ -137,3 +155,15 @@ class Communicator:
 
     def load_tuning(self, text: str):
         check(lib.hlCommLoadTuning(self._h, text.encode()), "hlCommLoadTuning")
+
+
+class _CommBlock:
+    def __init__(self, comm: Communicator, ptr):
+        self.comm, self.ptr = comm, ptr
+
+    def __del__(self):
+        try:
+            if self.comm._h:
+                lib.hlMemFree(self.comm._h, C.c_void_p(self.ptr))
+        except Exception:
+            pass

@@ -47,8 +47,29 @@ class DDPTrainer:
                 cta_budget = int(os.environ.get("HYLINK_DDP_CTA_BUDGET", "64"))
             self._old_budget = set_cta_budget(cta_budget)
         self.model = model.to(device=device, dtype=dtype)
-        self.ddp = DDP(self.model, device_ids=[device.index], bucket_cap_mb=bucket_cap_mb, gradient_as_bucket_view=True,
-                       static_graph=False)
+        self.registered_buckets = False
+        self._pool = None
+        self._steps = 0
+        pool = None
+        if dist.get_backend() == "hylink" and dist.get_world_size() > 1 and os.environ.get("HYLINK_DDP_REGISTERED", "1") != "0":
+            # Gradient buckets in registered memory: the bucket all-reduces then run zero-copy, in place in every
+            # rank's bucket (multimem load-reduce / store through NVSwitch), on a few SMs beside the backward GEMMs.
+            try:
+                from .backend import registered_mem_pool
+
+                dist.barrier()                       # the group's communicator (and its allocator) exists after this
+                pool = registered_mem_pool()
+            except Exception as ex:  # noqa: BLE001 - an older PyTorch without pluggable pools: buckets are staged
+                print(f"hylink: gradient buckets stay unregistered ({type(ex).__name__}: {ex})", flush=True)
+        if pool is not None:
+            with torch.cuda.use_mem_pool(pool):
+                self.ddp = DDP(self.model, device_ids=[device.index], bucket_cap_mb=bucket_cap_mb, gradient_as_bucket_view=True,
+                               static_graph=False)
+            self.registered_buckets = True
+            self._pool = pool
+        else:
+            self.ddp = DDP(self.model, device_ids=[device.index], bucket_cap_mb=bucket_cap_mb, gradient_as_bucket_view=True,
+                           static_graph=False)
         self.opt = torch.optim.AdamW(self.ddp.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
         self._loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
         self._dev_batch = None
@@ -63,6 +84,13 @@ class DDPTrainer:
 
     def step_device(self, idx: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One optimisation step on device-resident tokens; returns the loss tensor (no host sync)."""
+        if self._pool is not None and self._steps == 1:
+            # DDP re-buckets its gradients once, before the second forward pass, in the order they became ready:
+            # do that here, under the registered pool, so that the new buckets are registered too.
+            with torch.cuda.use_mem_pool(self._pool):
+                if self.ddp.reducer._rebuild_buckets():
+                    self.ddp._has_rebuilt_buckets = True
+        self._steps += 1
         loss = self.ddp(idx, targets)
         self.opt.zero_grad(set_to_none=True)
         loss.backward()

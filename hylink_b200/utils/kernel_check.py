@@ -123,6 +123,46 @@ def main(argv=None) -> int:
                     comm.broadcast(buf, root=root, algo=algo)
                     torch.cuda.synchronize()
                     verdict("broadcast", algo, dname, n_el, buf, ins[root], True)
+            # zero-copy kernels on registered memory (both flavours), buffers allocated in the same order on every rank
+            if n_el * es % 16 == 0 and seg * es % 16 == 0:
+                rin = comm.alloc_registered(n_el, dt)
+                rout = comm.alloc_registered(n_el + 32, dt)
+                assert comm.is_registered(rin) and comm.is_registered(rout)
+                pad = 16 // es
+                for algo in (["zerocopy_nvls", "zerocopy_p2p", "auto"] if nvls else ["zerocopy_p2p", "auto"]):
+                    rin.copy_(ins[rank])
+                    rout.fill_(3.0)
+                    comm.all_reduce(rin, rout[pad:pad + n_el], algo=algo)
+                    torch.cuda.synchronize()
+                    verdict("zc-allreduce", algo, dname, n_el, rout[pad:pad + n_el], want_sum, algo == "zerocopy_p2p")
+                    if not (bool((rout[:pad] == 3.0).all()) and bool((rout[pad + n_el:] == 3.0).all())):
+                        failures.append({"coll": "zc-allreduce", "algo": algo, "dtype": dname, "elems": n_el, "rank": rank, "guard": True})
+                    # in place
+                    comm.all_reduce(rin, rin, algo=algo)
+                    torch.cuda.synchronize()
+                    verdict("zc-allreduce-inplace", algo, dname, n_el, rin, want_sum, algo == "zerocopy_p2p")
+                    rin.copy_(ins[rank])
+                    part = torch.full((seg,), 3.0, device="cuda", dtype=dt)
+                    comm.reduce_scatter(rin, part, algo=algo)
+                    torch.cuda.synchronize()
+                    verdict("zc-reducescatter", algo, dname, seg, part, want_sum[rank * seg:(rank + 1) * seg], algo == "zerocopy_p2p")
+                    rout.fill_(3.0)
+                    comm.all_gather(ins[rank][:seg], rout[pad:pad + n_el], algo=algo)
+                    torch.cuda.synchronize()
+                    verdict("zc-allgather", algo, dname, n_el, rout[pad:pad + n_el], want_gather, True)
+                    rin.copy_(ins[rank])
+                    comm.broadcast(rin, root=world - 1, algo=algo)
+                    torch.cuda.synchronize()
+                    verdict("zc-broadcast", algo, dname, n_el, rin, ins[world - 1], True)
+                # staged and zero-copy calls interleaved without host synchronisation
+                for _ in range(3):
+                    rin.copy_(ins[rank])
+                    comm.all_reduce(rin, rin)
+                    comm.all_reduce(ins[rank], rout[pad:pad + n_el], algo="push")
+                    comm.all_gather(rin[:seg], rout[pad:pad + n_el])
+                torch.cuda.synchronize()
+                verdict("zc-mixed", "auto", dname, n_el, rout[pad:pad + n_el], torch.cat([want_sum[:seg]] * world), not nvls or world < 4)
+                del rin, rout
             # calls of different sizes and kinds back to back, no host synchronisation in between: the staging
             # hand-over from one kernel to the next
             big, small = ins[rank], ins[rank][:max(1, n_el // 3)]

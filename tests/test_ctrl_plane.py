@@ -76,3 +76,43 @@ def test_missing_rank_times_out_not_hangs():
     finally:
         del os.environ["HYLINK_BARRIER_TIMEOUT_MS"]
         lib.hlConfigReload()
+
+
+def test_two_in_process_groups_of_the_same_size_at_once():
+    """Ranks as threads of one process, two groups of two created concurrently: every rank must meet its own group
+    (ids from hlGetInProcessId carry a group tag behind their leading zero byte)."""
+    import ctypes as C
+    import threading
+
+    import torch
+
+    from hylink_b200._native import UniqueId, check, lib
+
+    lib.hlGetInProcessId.argtypes = [C.POINTER(UniqueId)]
+    ids = [UniqueId(), UniqueId()]
+    for u in ids:
+        check(lib.hlGetInProcessId(C.byref(u)), "hlGetInProcessId")
+    assert C.string_at(C.addressof(ids[0]), 128) != C.string_at(C.addressof(ids[1]), 128)
+    results, errors = {}, []
+
+    def rank(group, r):
+        try:
+            h = C.c_void_p()
+            check(lib.hlCommInitRankDevice(C.byref(h), 2, ids[group], r, -2), "init")
+            x = torch.full((1000,), float(10 * group + r + 1))
+            check(lib.hlAllReduce(x.data_ptr(), x.data_ptr(), 1000, 7, 0, h, None), "allreduce")
+            check(lib.hlCommDrain(h), "drain")
+            results[(group, r)] = float(x[0])
+            lib.hlCommDestroy(h)
+        except Exception as ex:  # noqa: BLE001
+            errors.append(repr(ex))
+
+    # rank 0 of both groups first, then rank 1 of both: with one open group per size the second rank 0 would
+    # displace the first group and the pairs would cross
+    th = [threading.Thread(target=rank, args=(g, r)) for r in (0, 1) for g in (0, 1)]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join(60)
+    assert not errors, errors
+    assert results == {(0, 0): 3.0, (0, 1): 3.0, (1, 0): 23.0, (1, 1): 23.0}

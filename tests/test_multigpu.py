@@ -95,3 +95,11 @@ def test_parallel_schemes_match_dense_math():
     """Tensor/sequence parallel, sharded optimizer, MoE all-to-all, Ulysses / context-parallel attention, GPipe."""
     out = _torchrun(2, ["-m", "hylink_b200.utils.parallel_selftest"])
     assert "PARALLEL SELFTEST PASSED" in out, out[-3000:]
+
+
+def test_nccl_program_served_without_a_real_nccl():
+    """Thread-per-GPU ncclCommInitAll program, group calls, V-variants, split and ncclMemAlloc on the stand-alone personality."""
+    e = dict(os.environ, HYLINK_NCCL_STANDALONE="1", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    p = subprocess.run([sys.executable, "-m", "hylink_b200.utils.nccl_standalone_check"], cwd=ROOT, env=e, stdout=subprocess.PIPE,
+                       stderr=subprocess.STDOUT, text=True, timeout=600)
+    assert p.returncode == 0 and "NCCL_STANDALONE_CHECK ok" in p.stdout, p.stdout[-4000:]
