@@ -2,7 +2,8 @@
 // libhylink_nccl.so, active with HYLINK_CUDA_BLOCK_SHIM=1).
 //
 // A thread that enters cudaStreamSynchronize / cudaDeviceSynchronize /
-// cudaEventSynchronize / a synchronous cudaMemcpy / cudaMalloc / cudaFree may
+// cudaEventSynchronize / a synchronous cudaMemcpy / cudaMemset / a cudaMemcpyAsync that touches
+// pageable host memory / cudaMalloc / cudaFree / cudaMallocHost / cudaHostAlloc / cudaFreeHost may
 // hold driver locks while it waits for a stream that is itself parked behind
 // one of this library's doorbells; the CPU executor that would ring the
 // doorbell needs the driver to issue its copies. Draining the executors before
@@ -77,6 +78,37 @@ __attribute__((visibility("default"))) cudaError_t cudaMallocHost(void** p, size
   static auto fn = next<cudaError_t (*)(void**, size_t)>("cudaMallocHost");
   Guard g;
   return fn ? fn(p, n) : cudaErrorUnknown;
+}
+__attribute__((visibility("default"))) cudaError_t cudaHostAlloc(void** p, size_t n, unsigned int flags) {
+  static auto fn = next<cudaError_t (*)(void**, size_t, unsigned int)>("cudaHostAlloc");
+  Guard g;
+  return fn ? fn(p, n, flags) : cudaErrorUnknown;
+}
+__attribute__((visibility("default"))) cudaError_t cudaMemset(void* p, int value, size_t n) {
+  static auto fn = next<cudaError_t (*)(void*, int, size_t)>("cudaMemset");
+  Guard g;
+  return fn ? fn(p, value, n) : cudaErrorUnknown;
+}
+// An "asynchronous" copy between the device and PAGEABLE host memory blocks the calling thread inside the driver
+// (`tensor.item()` and friends end here): it is drained for like the synchronous calls. Copies that involve only
+// device or pinned memory return at once and pass straight through.
+__attribute__((visibility("default"))) cudaError_t cudaMemcpyAsync(void* dst, const void* src, size_t n, cudaMemcpyKind k, cudaStream_t s) {
+  static auto fn = next<cudaError_t (*)(void*, const void*, size_t, cudaMemcpyKind, cudaStream_t)>("cudaMemcpyAsync");
+  if (!fn) return cudaErrorUnknown;
+  if (!active() || k == cudaMemcpyDeviceToDevice) return fn(dst, src, n, k, s);
+  const void* host = k == cudaMemcpyDeviceToHost ? dst : (k == cudaMemcpyHostToDevice ? src : nullptr);
+  bool pageable = false;
+  if (host) {
+    cudaPointerAttributes at;
+    static auto attr = next<cudaError_t (*)(cudaPointerAttributes*, const void*)>("cudaPointerGetAttributes");
+    if (attr && attr(&at, host) == cudaSuccess) pageable = at.type == cudaMemoryTypeUnregistered;
+    else pageable = true;
+    static auto last = next<cudaError_t (*)(void)>("cudaGetLastError");
+    if (last) last();   // an unregistered pointer may leave an error behind on older runtimes
+  }
+  if (!pageable) return fn(dst, src, n, k, s);
+  Guard g;
+  return fn(dst, src, n, k, s);
 }
 __attribute__((visibility("default"))) cudaError_t cudaFreeHost(void* p) {
   static auto fn = next<cudaError_t (*)(void*)>("cudaFreeHost");

@@ -10,6 +10,8 @@
 
 #include <cstring>
 
+#include "core/trace.h"
+
 using namespace hl;
 
 namespace hl {
@@ -240,6 +242,7 @@ hlResult_t hlAllReduce(const void* send, void* recv, size_t count, hlDataType_t 
 hlResult_t hlAllReduceEx(const void* send, void* recv, size_t count, hlDataType_t t, hlRedOp_t op,
                          const hlCallOpts* opts, hlComm_t comm, hlStream_t stream) {
   HL_CHECK(precheck(comm));
+  TraceScope range("collective", "hylink all_reduce", comm->rank);   // also an NVTX range
   if (!send || !recv) return fail(hlInvalidArgument, "null buffer");
   if ((int)op < 0 || op >= hlNumOps) return fail(hlInvalidArgument, "bad reduction op %d", (int)op);
   Resolved r;
@@ -285,6 +288,7 @@ hlResult_t hlReduceScatter(const void* send, void* recv, size_t recvcount, hlDat
 hlResult_t hlReduceScatterEx(const void* send, void* recv, size_t recvcount, hlDataType_t t, hlRedOp_t op,
                              const hlCallOpts* opts, hlComm_t comm, hlStream_t stream) {
   HL_CHECK(precheck(comm));
+  TraceScope range("collective", "hylink reduce_scatter", comm->rank);   // also an NVTX range
   if (!send || !recv) return fail(hlInvalidArgument, "null buffer");
   Resolved r;
   HL_CHECK(resolve(t, opts, &r));
@@ -328,6 +332,7 @@ hlResult_t hlAllGather(const void* send, void* recv, size_t sendcount, hlDataTyp
 hlResult_t hlAllGatherEx(const void* send, void* recv, size_t sendcount, hlDataType_t t, const hlCallOpts* opts,
                          hlComm_t comm, hlStream_t stream) {
   HL_CHECK(precheck(comm));
+  TraceScope range("collective", "hylink all_gather", comm->rank);   // also an NVTX range
   if (!send || !recv) return fail(hlInvalidArgument, "null buffer");
   Resolved r;
   HL_CHECK(resolve(t, opts, &r));
@@ -369,6 +374,7 @@ hlResult_t hlBroadcast(const void* send, void* recv, size_t count, hlDataType_t 
 hlResult_t hlBroadcastEx(const void* send, void* recv, size_t count, hlDataType_t t, int root, const hlCallOpts* opts,
                          hlComm_t comm, hlStream_t stream) {
   HL_CHECK(precheck(comm));
+  TraceScope range("collective", "hylink broadcast", comm->rank);   // also an NVTX range
   if (!recv) return fail(hlInvalidArgument, "null buffer");
   if (root < 0 || root >= comm->nranks) return fail(hlInvalidArgument, "root %d out of range", root);
   if (comm->rank == root && !send) return fail(hlInvalidArgument, "null send buffer on the root");
@@ -410,6 +416,7 @@ hlResult_t hlAllToAll(const void* send, void* recv, size_t count, hlDataType_t t
 hlResult_t hlAllToAllEx(const void* send, void* recv, size_t count, hlDataType_t t, const hlCallOpts* opts,
                         hlComm_t comm, hlStream_t stream) {
   HL_CHECK(precheck(comm));
+  TraceScope range("collective", "hylink all_to_all", comm->rank);   // also an NVTX range
   if (!send || !recv) return fail(hlInvalidArgument, "null buffer");
   Resolved r;
   HL_CHECK(resolve(t, opts, &r));
@@ -592,6 +599,9 @@ hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out) {
   *out = comm->stats;
   out->kernel_launches = comm->stats.kernel_launches + (comm->nvl ? comm->nvl->launches() : 0) + (comm->pcie ? comm->pcie->kernelLaunches() : 0);
   out->copy_engine_ops = comm->pcie ? comm->pcie->copyOps() : 0;
+  out->fused_landing_slices = comm->pcie ? comm->pcie->fusedSlices() : 0;
+  out->folded_sources = comm->pcie ? comm->pcie->foldedSources() : 0;
+  out->registered_bytes = comm->nvl ? comm->nvl->heapInUse() : 0;
   if (comm->orch) comm->orch->fillStats(out);
   return hlSuccess;
 }

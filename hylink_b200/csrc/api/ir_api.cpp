@@ -5,6 +5,7 @@
 #include "api/comm.h"
 #include "hylink/hylink_ext.h"
 #include "ir/compiler.h"
+#include "host/topology.h"
 #include "pcie/pcie_path.h"
 
 using namespace hl;
@@ -24,6 +25,27 @@ hlResult_t hlIrGenerate(const char* collective, const char* numa_pattern, const 
   ir::Program p;
   HL_CHECK(ir::generate(collective, ir::parsePattern(numa_pattern), variant ? variant : "", root, &p));
   return copyOut(ir::toXml(p), buf, len);
+}
+
+int hlTopoPairQuery(const char* bus_a, const char* bus_b, int* same_switch, int* nvlink) {
+  bool pix = false, nvl = false;
+  const bool ok = hl::nvmlPairQuery(bus_a ? bus_a : "", bus_b ? bus_b : "", &pix, &nvl);
+  if (same_switch) *same_switch = pix ? 1 : 0;
+  if (nvlink) *nvlink = nvl ? 1 : 0;
+  return ok ? 1 : 0;
+}
+int hlTopoDirectAllowed(const char* collective, const char* pattern, const unsigned char* pix, const unsigned char* nvlink,
+                        const unsigned char* peer, int n) {
+  hl::PairTopology t;
+  t.n = n;
+  t.pix.assign(pix, pix + (size_t)n * n);
+  t.nvlink.assign(nvlink, nvlink + (size_t)n * n);
+  t.peer.assign(peer, peer + (size_t)n * n);
+  return hl::directVariantAllowed(collective ? collective : "", pattern ? pattern : "", t) ? 1 : 0;
+}
+
+int hlDmaLaneCount(const char* collective, size_t message_bytes, int world, int max_lanes, int forced) {
+  return hl::dmaLanePolicy(collective, message_bytes, world, max_lanes, forced);
 }
 
 hlResult_t hlIrInspect(const char* xml, const char* numa_pattern, int send_segs, int recv_segs, int in_place, hlIrInfo* info) {

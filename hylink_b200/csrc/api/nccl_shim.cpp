@@ -160,6 +160,7 @@ struct Side {
   uint64_t id_hash = 0;
   int splits = 0;
   bool pending = false;   // the real communicator was still initialising when it was handed out (non-blocking init)
+  bool scoped = false;    // has an entry in this machine's node-scope table
 };
 std::mutex g_mu;
 std::map<ncclComm_t, Side> g_side;
@@ -204,6 +205,7 @@ OwnComm* asOwn(ncclComm_t c) {
 void attachSide(ncclComm_t real, uint64_t id_hash, const hlUniqueId* in_process = nullptr) {
   if (!enabled() || !real) return;
   int n = 0, r = 0, dev = -1;
+  bool scoped = false;
   if (g_real.ncclCommCount(real, &n) != ncclSuccess || g_real.ncclCommUserRank(real, &r) != ncclSuccess ||
       g_real.ncclCommCuDevice(real, &dev) != ncclSuccess)
     return;
@@ -216,6 +218,17 @@ void attachSide(ncclComm_t real, uint64_t id_hash, const hlUniqueId* in_process 
     HL_INFO("libhylink_nccl: communicator of %d ranks is not confined to this node (%d GPUs): pass-through", n, local);
     return;
   }
+  if (!in_process && n > 1 && !hl::envBool({"HYLINK_NCCL_ASSUME_SINGLE_NODE"}, false)) {
+    // every rank registers in this machine's table and looks for the others: ranks on another machine never appear
+    int flags = 0;
+    const int seen = hlNodeScopeDetect(id_hash, n, r, dev, (int)std::max<long long>(200, hl::Config::get().node_scope_wait_ms), &flags);
+    scoped = true;   // the entry stays while the communicator lives (peers may still be looking for it)
+    if (!(flags & 1) || !(flags & 2)) {
+      hlNodeScopeLeave(id_hash, n, r);
+      HL_INFO("libhylink_nccl: %d of %d ranks are on this machine%s: pass-through", seen, n, (flags & 1) ? " (two ranks share a device)" : "");
+      return;
+    }
+  }
   // Ranks leave the real init within moments of each other, so a short wait
   // distinguishes "all here" from "some ranks are elsewhere".
   hlSetRendezvousTimeoutMs((int)std::max<long long>(2000, hl::Config::get().node_scope_wait_ms));
@@ -226,10 +239,12 @@ void attachSide(ncclComm_t real, uint64_t id_hash, const hlUniqueId* in_process 
   if (prev >= 0) cudaSetDevice(prev);
   if (rc != hlSuccess) {
     HL_WARN("libhylink_nccl: side communicator not created (%s): pass-through", hlGetLastError());
+    if (scoped) hlNodeScopeLeave(id_hash, n, r);
     return;
   }
   std::lock_guard<std::mutex> lk(g_mu);
   Side& s = g_side[real];
+  s.scoped = scoped;
   s.comm = side;
   s.rank = r;
   s.nranks = n;
@@ -251,6 +266,7 @@ void dropSide(ncclComm_t real, bool abort) {
     auto it = g_side.find(real);
     if (it == g_side.end()) return;
     c = it->second.comm;
+    if (it->second.scoped) hlNodeScopeLeave(it->second.id_hash, it->second.nranks, it->second.rank);
     g_side.erase(it);
   }
   if (!c) return;

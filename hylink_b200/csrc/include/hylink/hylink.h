@@ -189,6 +189,9 @@ typedef struct {
   double last_pcie_ms;
   int nvls;                   /* 1 if a multicast mapping is active */
   int symm_mode;              /* 0 none, 1 cuMem+fd, 2 cudaIpc, 3 in-process */
+  uint64_t fused_landing_slices; /* PCIe path: reduce launches that read landed host chunks themselves (no H2D copy) */
+  uint64_t folded_sources;    /* ... and further sources folded into such launches */
+  uint64_t registered_bytes;  /* bytes handed out from the registered-memory heap */
 } hlCommStats;
 hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out);
 /* Serialises the tuned (op-key -> alpha, bandwidth) table as JSON into buf;

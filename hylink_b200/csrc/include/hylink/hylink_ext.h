@@ -65,6 +65,19 @@ hlResult_t hlReduceScatterSeg(const void* send, void* recv, size_t count, size_t
                               hlStream_t stream);
 hlResult_t hlAllToAllSeg(const void* send, void* recv, size_t count, size_t send_stride, size_t recv_stride, hlDataType_t t, hlComm_t comm,
                          hlStream_t stream);
+/* Pair topology (NVML through dlopen; HYLINK_NVML_LIB names another library). hlTopoPairQuery: 1 when NVML answered;
+ * *same_switch = the two PCI functions sit under one PCIe switch, *nvlink = NVLink joins them.
+ * hlTopoDirectAllowed: the selection rule of the `_direct` schedule files for n x n matrices (row-major). */
+int hlTopoPairQuery(const char* bus_a, const char* bus_b, int* same_switch, int* nvlink);
+int hlTopoDirectAllowed(const char* collective, const char* pattern, const unsigned char* same_switch, const unsigned char* nvlink,
+                        const unsigned char* peer, int n);
+/* Node scope: registers (rank, pid, device) of a communicator (named by its hash) in this machine's shared table and
+ * waits up to wait_ms for the other ranks. Returns the ranks seen here; *flags = all on this machine | no two on one
+ * device << 1 | devices in rank order << 2. hlNodeScopeLeave drops the entry (the last rank removes the table). */
+int hlNodeScopeDetect(uint64_t comm_hash, int nranks, int rank, int device, int wait_ms, int* flags);
+void hlNodeScopeLeave(uint64_t comm_hash, int nranks, int rank);
+/* Copy-engine lanes per direction the PCIe executor uses for a collective of this size (the lane policy table). */
+int hlDmaLaneCount(const char* collective, size_t message_bytes, int world, int max_lanes, int forced);
 /* Runs a caller-supplied schedule on the PCIe path of `comm`. */
 hlResult_t hlSubmitIr(hlComm_t comm, const char* xml, const void* send, void* recv, size_t seg_count, size_t stride,
                       int send_segs, int recv_segs, hlDataType_t t, hlRedOp_t op, hlStream_t stream);

@@ -207,6 +207,30 @@ hlResult_t compile(const Program& p, const CompileOptions& opt, CompiledGraph* o
     }
     if (seen != N) return fail(hlInvalidArgument, "schedule has a dependency cycle (%zu of %zu nodes orderable)", seen, N);
   }
+  // Landing fusion: pair every D2DReduce with the H2D that produced its source chunk when nobody else reads it.
+  {
+    std::vector<int> readers(g.nodes.size(), 0);          // how many nodes wait for node i because they READ what it wrote
+    for (const Node& n : g.nodes)
+      for (int d : n.wait_for) {
+        const Node& wtr = g.nodes[(size_t)d];
+        const bool reads_it = (n.src == wtr.dst && n.op != Op::NOP) || (n.op == Op::H2HReduce && n.src2 == wtr.dst) ||
+                              (n.op == Op::D2DReduce && n.dst == wtr.dst);
+        if (reads_it) readers[(size_t)d]++;
+      }
+    for (Node& r : g.nodes) {
+      if (r.op != Op::D2DReduce || r.skip) continue;
+      if (r.src.space != Buf::Internal && r.src.space != Buf::Scratch) continue;
+      if (r.src.owner != r.rank) continue;
+      for (int d : r.wait_for) {
+        Node& wtr = g.nodes[(size_t)d];
+        if (wtr.op == Op::H2D && wtr.rank == r.rank && wtr.dst == r.src && readers[(size_t)d] == 1 && wtr.fused_into < 0) {
+          r.fused_h2d = wtr.id;
+          wtr.fused_into = r.id;
+          break;
+        }
+      }
+    }
+  }
   *out = std::move(g);
   return hlSuccess;
 }

@@ -49,6 +49,11 @@ struct Node {
   bool skip = false;        // aliased self-copy: completes without work
   int line = 0;
   std::vector<int> wait_for;
+  // Landing fusion (a property of the graph; an executor may ignore it). A D2DReduce whose source chunk was put
+  // into device scratch by an H2D of the same rank, for that reduce alone, can read the pinned host chunk itself:
+  // `fused_h2d` names that H2D node on the reduce, `fused_into` names the reduce on the H2D node.
+  int fused_h2d = -1;
+  int fused_into = -1;
 };
 
 enum class InPlace { None, Same, GatherSlot, ScatterSlot };

@@ -336,13 +336,19 @@ bool NvlPath::heapOffset(int i, const void* p, size_t bytes, uint64_t* off) cons
   return true;
 }
 
-// Which flavour of zero-copy kernel a call gets. Reductions go through the switch when NVLS pays (it halves the
-// inbound traffic) and the call allows it; pure data movement uses posted peer stores unless NVLS is asked for
-// by name (measured on 4 GPUs: multimem.st into staging moved 430 GB/s where peer stores moved 627).
-int NvlPath::zeroCopyFlavour(const NvlCall& c, bool reduce) const {
+// Which flavour of zero-copy kernel a call gets (0 none, 1 NVLS, 2 peer pointers). Measured on 4 B200 (bf16, busbw):
+//  * all-gather / broadcast: posted peer stores (688 GB/s at 1 GiB) beat multimem.st (529) at every size;
+//  * reduce-scatter: peer loads (638 GB/s at 1 GiB) beat multimem.ld_reduce (522): through the switch every GPU
+//    sends its WHOLE input out (its own contribution travels to the switch too), so the call is bound by outbound
+//    traffic at busbw = (n-1)/n of the link, while peer pulls send (n-1)/n of the input and reach the link rate;
+//  * all-reduce: the switch wins where latency counts (48 vs 17 GB/s at 1 MiB) and on long messages (683 vs 663 at
+//    1 GiB), peer loads + stores win in between (573 vs 520 at 64 MiB), where they run the link at a higher rate.
+//    From eight ranks on the switch moves 1.125x the message per GPU where peer pointers move 1.75x.
+int NvlPath::zeroCopyFlavour(const NvlCall& c, int coll, size_t wire_bytes) const {
   if (!Config::get().zero_copy && c.algo == hlAlgoAuto) return 0;
   if (c.algo != hlAlgoAuto && c.algo != hlAlgoZeroCopy && c.algo != hlAlgoZeroCopyNvls && c.algo != hlAlgoZeroCopyP2p) return 0;
   if (c.algo == hlAlgoZeroCopyP2p) return 2;
+  const bool reduce = coll <= 1;
   const bool mc_ok = heap_mc_ && (!reduce || ((c.wire_dt == hlFloat32 || c.wire_dt == hlFloat16 || c.wire_dt == hlBfloat16) &&
                                                (c.op == hlSum || c.op == hlAvg) && !c.deterministic));
   if (c.algo == hlAlgoZeroCopyNvls) return mc_ok ? 1 : 0;
@@ -350,7 +356,11 @@ int NvlPath::zeroCopyFlavour(const NvlCall& c, bool reduce) const {
   const int pref = reduce ? reduce_pref : gather_pref;
   if (!mc_ok || pref == 0) return 2;
   if (pref == 1) return 1;
-  return nranks_ >= Config::get().nvls_min_ranks ? 1 : 2;
+  if (coll != 0 || nranks_ < Config::get().nvls_min_ranks) return 2;
+  static const long long p2p_lo = envInt({"HYLINK_ZC_AR_P2P_MIN"}, -1), p2p_hi = envInt({"HYLINK_ZC_AR_P2P_MAX"}, -1);
+  const size_t lo = p2p_lo >= 0 ? (size_t)p2p_lo : (nranks_ <= 4 ? (size_t)16 << 20 : 0);
+  const size_t hi = p2p_hi >= 0 ? (size_t)p2p_hi : (nranks_ <= 4 ? (size_t)256 << 20 : 0);
+  return (wire_bytes >= lo && wire_bytes < hi) ? 2 : 1;
 }
 
 bool NvlPath::zeroCopyEligible(const NvlBufs& b, const NvlCall& c, bool in_remote, bool out_remote, uint64_t in_extent, uint64_t out_extent,
@@ -496,8 +506,8 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
       uint64_t lanes = std::max(1, blocks / roles);
       uint64_t tps = (sp + lanes * 8 - 1) / (lanes * 8);
       tps = std::min<uint64_t>(8192, std::max<uint64_t>(256, (tps + 63) & ~(uint64_t)63));
-      const char* forced = getenv("HYLINK_PIPE_TILE_PACKETS");
-      if (forced) tps = std::max<uint64_t>(64, (uint64_t)atoll(forced) & ~(uint64_t)63);
+      static const long long forced = envInt({"HYLINK_PIPE_TILE_PACKETS"}, 0);   // read once: this sits on the launch path
+      if (forced > 0) tps = std::max<uint64_t>(64, (uint64_t)forced & ~(uint64_t)63);
       const uint64_t tiles = (sp + tps - 1) / tps;
       lanes = std::min<uint64_t>(lanes, tiles);
       blocks = (int)lanes * roles;
@@ -518,7 +528,7 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
   {
     uint64_t io, oo;
-    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, true) : 0;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 0, wire_bytes) : 0;
     if (zc && zeroCopyEligible(b, c, true, true, c.count, c.count, &io, &oo))
       return launchZeroCopy(zc == 1 ? kNvlZcAllReduceNvls : kNvlZcAllReduceP2p, b, c, io, oo, wire_bytes / (size_t)nranks_, s);
     if (wantsZeroCopy(c.algo)) return fail(hlUnsupported, "all-reduce: zero-copy needs registered, 16-byte aligned buffers of whole 16-byte packets");
@@ -553,7 +563,7 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
   {
     uint64_t io, oo;
-    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, true) : 0;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 1, wire_bytes) : 0;
     const uint64_t stride = c.in_seg_stride ? c.in_seg_stride : c.count;
     if (zc && zeroCopyEligible(b, c, true, false, stride * (uint64_t)(nranks_ - 1) + c.count, c.count, &io, &oo))
       return launchZeroCopy(zc == 1 ? kNvlZcReduceScatterNvls : kNvlZcReduceScatterP2p, b, c, io, 0, wire_bytes / (size_t)nranks_, s);
@@ -579,7 +589,7 @@ hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   if (c.count == 0) return hlSuccess;
   {
     uint64_t io, oo;
-    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, false) : 0;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 2, 0) : 0;
     const uint64_t stride = c.out_seg_stride ? c.out_seg_stride : c.count;
     if (zc && zeroCopyEligible(b, c, false, true, c.count, stride * (uint64_t)(nranks_ - 1) + c.count, &io, &oo))
       return launchZeroCopy(zc == 1 ? kNvlZcAllGatherNvls : kNvlZcAllGatherP2p, b, c, 0, oo, c.count * hlTypeSize((hlDataType_t)c.wire_dt), s);
@@ -601,7 +611,7 @@ hlResult_t NvlPath::broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   if (c.root < 0 || c.root >= nranks_) return fail(hlInvalidArgument, "broadcast root %d out of range", c.root);
   {
     uint64_t io, oo;
-    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, false) : 0;
+    const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 2, 0) : 0;
     if (zc && zeroCopyEligible(b, c, false, true, c.count, c.count, &io, &oo))
       return launchZeroCopy(zc == 1 ? kNvlZcBroadcastNvls : kNvlZcBroadcastP2p, b, c, 0, oo, c.count * hlTypeSize((hlDataType_t)c.wire_dt), s);
     if (wantsZeroCopy(c.algo)) return fail(hlUnsupported, "broadcast: zero-copy needs a registered, 16-byte aligned buffer of whole 16-byte packets");

@@ -104,7 +104,7 @@ class NvlPath {
                         uint64_t* in_off, uint64_t* out_off) const;
   hlResult_t launchZeroCopy(int kind, const NvlBufs& b, const NvlCall& c, uint64_t in_off, uint64_t out_off, size_t bytes_per_rank,
                             cudaStream_t s);
-  int zeroCopyFlavour(const NvlCall& c, bool reduce) const;   // 0 none, 1 NVLS, 2 peer pointers
+  int zeroCopyFlavour(const NvlCall& c, int coll, size_t wire_bytes) const;   // coll: 0 all-reduce, 1 reduce-scatter, 2 gather / broadcast
   Bootstrap* bs_ = nullptr;
   bool emu_ = false;
   int emu_active_ = 0;

@@ -171,9 +171,8 @@ class SplitRatioAlgo : public AdaptiveAlgo {
     if (s.pcie_bytes == 0) return;
     const double bp = s.pcieBw(), bf = s.fastBw();
     if (bp <= 0 || bf <= 0) return;
-    const double smooth = envD({"HYLINK_SPLIT_RATIO_SMOOTHING", "AMPCCL_SPLIT_RATIO_SMOOTHING"}, 0.7);
-    const double eta = envD({"HYLINK_SPLIT_RATIO_ETA", "AMPCCL_SPLIT_RATIO_ETA"}, 0.3);
-    const size_t warmup = (size_t)envInt({"HYLINK_SPLIT_RATIO_WARMUP_STEPS", "AMPCCL_SPLIT_RATIO_WARMUP_STEPS"}, 5);
+    const double smooth = smooth_, eta = eta_;   // read from the environment once, in reset()
+    const size_t warmup = warmup_;
     // tiny PCIe parts measure latency, not bandwidth: keep them out of the estimate
     if (s.pcie_bytes >= (4u << 20) || bp_hat_ <= 0) bp_hat_ = bp_hat_ <= 0 ? bp : smooth * bp + (1 - smooth) * bp_hat_;
     const double x_star = bp_hat_ / (bp_hat_ + bf);
@@ -186,6 +185,9 @@ class SplitRatioAlgo : public AdaptiveAlgo {
   void reset() override {
     alpha_ = envD({"HYLINK_SPLIT_RATIO_INITIAL_ALPHA", "AMPCCL_SPLIT_RATIO_INITIAL_ALPHA"}, 0.05);
     min_ = envD({"HYLINK_SPLIT_RATIO_MIN_ALPHA", "AMPCCL_SPLIT_RATIO_MIN_ALPHA"}, 0.005);
+    smooth_ = envD({"HYLINK_SPLIT_RATIO_SMOOTHING", "AMPCCL_SPLIT_RATIO_SMOOTHING"}, 0.7);
+    eta_ = envD({"HYLINK_SPLIT_RATIO_ETA", "AMPCCL_SPLIT_RATIO_ETA"}, 0.3);
+    warmup_ = (size_t)envInt({"HYLINK_SPLIT_RATIO_WARMUP_STEPS", "AMPCCL_SPLIT_RATIO_WARMUP_STEPS"}, 5);
     bp_hat_ = 0;
     updates_ = 0;
     clamp();
@@ -193,8 +195,8 @@ class SplitRatioAlgo : public AdaptiveAlgo {
 
  private:
   void clamp() { alpha_ = std::min(0.999, std::max(min_, alpha_)); }
-  double alpha_ = 0.05, min_ = 0.005, bp_hat_ = 0;
-  size_t updates_ = 0;
+  double alpha_ = 0.05, min_ = 0.005, bp_hat_ = 0, smooth_ = 0.7, eta_ = 0.3;
+  size_t updates_ = 0, warmup_ = 5;
 };
 }  // namespace
 
@@ -247,7 +249,8 @@ void AdaptiveController::update(const OpKey& key, const ExecStat& s) {
       static const int streak = (int)envInt({"HYLINK_ORCH_GUARD_STREAK"}, 16);
       if (++e.value.losing_streak >= streak) {
         e.value.losing_streak = 0;
-        e.value.cooldown = (int)envInt({"HYLINK_ORCH_COOLDOWN_CALLS"}, 200);
+        static const int cooldown = (int)envInt({"HYLINK_ORCH_COOLDOWN_CALLS"}, 200);
+        e.value.cooldown = cooldown;
       }
     } else {
       e.value.losing_streak = 0;

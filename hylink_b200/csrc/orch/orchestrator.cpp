@@ -254,6 +254,7 @@ void OrchImpl::publishImmediate(uint64_t idx, const orch::Plan& plan) {
 }
 
 hlResult_t OrchImpl::fork(const Split& s, cudaStream_t user) {
+  TraceScope range("orch", "fork", comm_->rank);
   const int slot = (int)(s.idx % kRing);
   HL_CUDA(cudaEventRecord(ev_fork_[slot], user));
   HL_CUDA(cudaStreamWaitEvent(pcie_stream_, ev_fork_[slot], 0));
@@ -273,6 +274,7 @@ void CUDART_CB OrchImpl::hostCallback(void* p) {
 }
 
 hlResult_t OrchImpl::join(const Split& s, cudaStream_t user, bool fast_ok, bool pcie_ok) {
+  TraceScope range("orch", "join", comm_->rank);
   const int slot = (int)(s.idx % kRing);
   HL_CUDA(cudaEventRecord(s.rec->ev[1], user));
   HL_CUDA(cudaEventRecord(s.rec->ev[3], pcie_stream_));

@@ -84,7 +84,10 @@ struct Work {
   int scale_segs = 0;
   size_t scale_seg_stride = 0;
   std::string name;
+  int dma_lanes = 2;         // copy-engine lanes per direction this collective uses (dmaLanePolicy)
 };
+
+constexpr int kMaxDmaLanes = 8;
 
 enum LaneId { kLaneD2H = 0, kLaneH2D = 1, kLaneD2D = 2, kLaneReduce = 3, kLaneHost = 4, kNumLaneKinds = 5 };
 
@@ -93,6 +96,8 @@ struct InFlight {
   cudaEvent_t ev = nullptr;
   std::shared_ptr<HostTicket> ticket;
   uint64_t t0_ns = 0;
+  size_t bytes = 0;       // payload of the slice (trace)
+  std::vector<int> also;  // further local nodes whose slice finishes with this one (fused H2D nodes, folded reduces)
 };
 
 struct Lane {
@@ -119,6 +124,8 @@ class PcieImpl {
   hlResult_t lastResult() const { return (hlResult_t)last_result_.load(); }
   uint64_t kernelLaunches() const { return kernel_launches_.load(); }
   uint64_t copyOps() const { return copy_ops_.load(); }
+  uint64_t fusedSlices() const { return fused_slices_.load(); }
+  uint64_t foldedSources() const { return folded_sources_.load(); }
   const std::vector<int>& rankNuma() const { return numa_; }
 
  private:
@@ -131,7 +138,7 @@ class PcieImpl {
   void releaseDoorbell(uint64_t value);
   void failAll(hlResult_t r);
   char* resolve(const Work& w, const ir::Loc& l, size_t* len_bytes, bool* remote_pending);
-  Lane& laneFor(ir::Op op, int salt);
+  Lane& laneFor(ir::Op op, int salt, int active);
   cudaEvent_t getEvent(Lane& l);
 
   Bootstrap* bs_;
@@ -140,8 +147,12 @@ class PcieImpl {
   SharedArea* shared_;
   int rank_ = 0, n_ = 1;
   std::vector<int> numa_, phys_of_logical_;
+  PairTopology pairs_;                 // which GPU pairs share a PCIe switch / an NVLink / peer access
   int numa_nodes_ = 1;
   std::vector<char*> host_base_;
+  std::vector<char*> host_dev_base_;   // the same pools as the device addresses them (mapped pinned memory)
+  bool fuse_landing_ = true;           // reduce kernels read landed host chunks themselves (HYLINK_PCIE_FUSE_LANDING)
+  std::atomic<uint64_t> fused_slices_{0}, folded_sources_{0};
   std::vector<size_t> host_map_bytes_;
   std::vector<bool> host_registered_, host_cuda_alloc_;
   size_t host_bytes_ = 0;
@@ -176,6 +187,7 @@ class PcieImpl {
 hlResult_t PcieImpl::init() {
   const Config& cfg = Config::get();
   HL_CHECK(discoverRankNuma(bs_, device_, &numa_, &phys_of_logical_));
+  HL_CHECK(discoverPairTopology(bs_, cuda_ ? device_ : -1, &pairs_));
   numa_nodes_ = (int)phys_of_logical_.size();
   bs_->publishSelf(device_, numa_[(size_t)rank_]);
   host_bytes_ = cfg.host_buffer_bytes & ~(size_t)4095;
@@ -192,7 +204,7 @@ hlResult_t PcieImpl::init() {
     stream_mem_ops_ = drv && !cfg.disable_stream_mem_ops;
     int lo = 0, hi = 0;
     HL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    lanes_per_dir_ = cfg.dma_lanes > 0 ? std::min(cfg.dma_lanes, 8) : 2;
+    lanes_per_dir_ = kMaxDmaLanes;   // all created once; each collective uses as many as the lane policy says
     for (int k = 0; k < kNumLaneKinds; ++k) {
       const int count = (k == kLaneD2H || k == kLaneH2D) ? lanes_per_dir_ : 1;
       lanes_[k].resize((size_t)count);
@@ -278,6 +290,20 @@ hlResult_t PcieImpl::createHostPools() {
       host_registered_[(size_t)m] = true;
     }
   }
+  host_dev_base_ = host_base_;
+  if (cuda_) {
+    for (int m = 0; m < numa_nodes_; ++m) {
+      void* d = nullptr;
+      if (host_base_[(size_t)m] && cudaHostGetDevicePointer(&d, host_base_[(size_t)m], 0) == cudaSuccess && d) host_dev_base_[(size_t)m] = (char*)d;
+      else {
+        cudaGetLastError();
+        fuse_landing_ = false;   // a pool the device cannot address: landed chunks are copied, then reduced
+      }
+    }
+    fuse_landing_ = fuse_landing_ && envBool({"HYLINK_PCIE_FUSE_LANDING"}, true);
+  } else {
+    fuse_landing_ = false;
+  }
   return bs_->barrier(kBarExec);
 }
 
@@ -346,7 +372,13 @@ hlResult_t PcieImpl::getPlan(const std::string& collective, const std::string& f
   } else {
     const std::string file_coll = collective == "broadcast" ? "broadcast_root" + std::to_string(root) : collective;
     std::string path;
-    if (small) path = ir::findProgramFile(file_coll, pattern, "small", "");
+    // `_direct` schedules copy between GPU pairs under one PCIe switch. They are chosen by topology (never with
+    // NVLink between the GPUs) and need the peers' device buffers, which only threads of one process can reach.
+    if (directVariantAllowed(file_coll, pattern, pairs_)) {
+      if (bs_->singleProcess()) path = ir::findProgramFile(file_coll, pattern, "direct", "");
+      else HL_DBG("topology allows %s_%s_direct.xml, but ranks are processes: host-relay schedule", file_coll.c_str(), pattern.c_str());
+    }
+    if (path.empty() && small) path = ir::findProgramFile(file_coll, pattern, "small", "");
     if (path.empty()) path = ir::findProgramFile(file_coll, pattern, "", "");
     if (!path.empty()) {
       hlResult_t r = ir::loadProgramFile(path, &plan->program);
@@ -452,6 +484,7 @@ hlResult_t PcieImpl::submit(const std::string& collective, const std::string& fo
     w.last_round = done + act >= active_total;
     w.door_seq = door;
     w.name = collective;
+    w.dma_lanes = dmaLanePolicy(collective.c_str(), active_total * es * (size_t)std::max(send_segs, recv_segs), n_, kMaxDmaLanes, Config::get().dma_lanes);
     done += act;
     works.push_back(std::move(w));
   }
@@ -606,11 +639,12 @@ cudaEvent_t PcieImpl::getEvent(Lane& l) {
   return e;
 }
 
-Lane& PcieImpl::laneFor(ir::Op op, int salt) {
+Lane& PcieImpl::laneFor(ir::Op op, int salt, int active) {
   if (!cuda_) return lanes_[kLaneHost][0];
+  const size_t use = (size_t)std::max(1, std::min(active, (int)lanes_[kLaneD2H].size()));
   switch (op) {
-    case ir::Op::D2H: return lanes_[kLaneD2H][(size_t)salt % lanes_[kLaneD2H].size()];
-    case ir::Op::H2D: return lanes_[kLaneH2D][(size_t)salt % lanes_[kLaneH2D].size()];
+    case ir::Op::D2H: return lanes_[kLaneD2H][(size_t)salt % use];
+    case ir::Op::H2D: return lanes_[kLaneH2D][(size_t)salt % use];
     case ir::Op::D2D: return lanes_[kLaneD2D][0];
     case ir::Op::D2DReduce: return lanes_[kLaneReduce][0];
     default: return lanes_[kLaneHost][0];
@@ -655,6 +689,7 @@ hlResult_t PcieImpl::runWork(const Work& w) {
   const int ns = geo.nslices;
   const uint64_t tag = w.seq << kSeqShift;
   TraceScope whole("pcie", w.name.c_str(), rank_);
+  whole.setBytes((long long)(w.geo.chunk_elems * w.geo.elem) * std::max(1, std::max(g.input_chunks, g.output_chunks)));
   struct Local {
     int issued = 0, done = 0;
   };
@@ -673,6 +708,13 @@ hlResult_t PcieImpl::runWork(const Work& w) {
   shared_->ptrs[rank_][3].store((uint64_t)(uintptr_t)internal_, std::memory_order_relaxed);
   shared_->ready_seq[rank_].store(w.seq, std::memory_order_release);
 
+  // Landing fusion: an H2D whose only reader is a D2DReduce of this rank is not copied at all; the reduce kernel
+  // reads the pinned host chunk over PCIe itself, and several such reduces into one destination are folded in ONE
+  // launch (up to eight sources) when their data is there together. The H2D node still exists for everybody who
+  // waits for it: it is reported done, slice by slice, when the reduce that consumed the host chunk is done.
+  const bool fuse = fuse_landing_ && !Config::get().skip_dma;
+  std::vector<int> local_of(g.nodes.size(), -1);
+  for (size_t i = 0; i < mine.size(); ++i) local_of[(size_t)mine[i]] = (int)i;
   size_t remaining = 0;
   for (size_t i = 0; i < mine.size(); ++i) {
     const ir::Node& n = g.nodes[(size_t)mine[i]];
@@ -681,19 +723,40 @@ hlResult_t PcieImpl::runWork(const Work& w) {
       publish((int)i);
     } else {
       st[i].done = 0;
+      if (fuse && n.fused_into >= 0) st[i].issued = ns;   // never issued on its own
       publish((int)i);
       ++remaining;
     }
   }
+  // inputs of slice k of a fused reduce: its own wait list with the H2D node replaced by what the H2D waited for,
+  // and (when folded behind `after`) without the reduce that precedes it in the same launch
+  auto fusedReady = [&](const ir::Node& r, int k, int after) -> bool {
+    for (int d : r.wait_for) {
+      if (d == after) continue;
+      if (d == r.fused_h2d) {
+        for (int dd : g.nodes[(size_t)d].wait_for)
+          if (progressOf(dd) < k + 1) return false;
+        continue;
+      }
+      if (progressOf(d) < k + 1) return false;
+    }
+    return true;
+  };
   const uint64_t t0 = nowNs();
   const uint64_t limit = (uint64_t)Config::get().executor_timeout_ms * 1000000ull;
   uint32_t idle = 0;
   auto complete = [&](InFlight& f) {
+    for (int extra : f.also) {
+      Local& x = st[(size_t)extra];
+      ++x.done;
+      publish(extra);
+      if (x.done == ns) --remaining;
+    }
     Local& l = st[(size_t)f.node_slot];
     ++l.done;
     publish(f.node_slot);
     if (l.done == ns) --remaining;
-    if (traceEnabled()) traceComplete("dma", ir::opName(g.nodes[(size_t)mine[(size_t)f.node_slot]].op), rank_, f.t0_ns, nowNs());
+    if (traceEnabled()) traceComplete("dma", ir::opName(g.nodes[(size_t)mine[(size_t)f.node_slot]].op), rank_, f.t0_ns, nowNs(), (long long)f.bytes);
   };
   while (remaining) {
     bool progressed = false;
@@ -723,9 +786,62 @@ hlResult_t PcieImpl::runWork(const Work& w) {
       Local& l = st[i];
       if (l.issued >= ns) continue;
       const ir::Node& n = g.nodes[(size_t)mine[i]];
-      Lane& lane = laneFor(n.op, (int)i);
+      Lane& lane = laneFor(n.op, (int)i, w.dma_lanes);
       while (l.issued < ns && (int)lane.inflight.size() < kLaneDepth) {
         const int k = l.issued;
+        if (fuse && n.op == ir::Op::D2DReduce && n.fused_h2d >= 0) {
+          if (!fusedReady(n, k, -1)) break;
+          size_t dlen = 0, hlen = 0;
+          bool pending = false;
+          char* dst = resolve(w, n.dst, &dlen, &pending);
+          const size_t off = (size_t)k * geo.slice_bytes;
+          const size_t len = off >= dlen ? 0 : std::min(geo.slice_bytes, dlen - off);
+          InFlight f;
+          f.node_slot = (int)i;
+          f.bytes = len;
+          f.t0_ns = nowNs();
+          nvl::ReduceLandingArgs a;
+          memset(&a, 0, sizeof(a));
+          a.dst = dst + off;
+          a.accumulate = 1;
+          a.count = len / geo.elem;
+          a.dtype = w.dtype;
+          a.op = w.op;
+          a.scale = 1.0f;
+          auto hostSrc = [&](const ir::Node& h2d) {
+            (void)resolve(w, h2d.src, &hlen, &pending);
+            return host_dev_base_[(size_t)h2d.src.owner] + (size_t)h2d.src.chunk * geo.chunk_bytes + off;
+          };
+          a.src[a.nsrc++] = hostSrc(g.nodes[(size_t)n.fused_h2d]);
+          f.also.push_back(local_of[(size_t)n.fused_h2d]);
+          // fold the reduces that follow into the same destination and whose landed data is there already
+          int prev = n.id;
+          for (size_t j = i + 1; j < mine.size() && a.nsrc < 8; ++j) {
+            const ir::Node& m = g.nodes[(size_t)mine[j]];
+            if (m.op != ir::Op::D2DReduce || m.fused_h2d < 0 || !(m.dst == n.dst)) continue;
+            if (st[j].issued != k || !fusedReady(m, k, prev)) break;   // the chain is ordered: stop at the first that is not ready
+            a.src[a.nsrc++] = hostSrc(g.nodes[(size_t)m.fused_h2d]);
+            f.also.push_back((int)j);
+            f.also.push_back(local_of[(size_t)m.fused_h2d]);
+            ++st[j].issued;
+            prev = m.id;
+            folded_sources_++;
+          }
+          if (len == 0) {
+            f.ticket = std::make_shared<HostTicket>();
+          } else {
+            HL_CHECK(nvl::launchReduceLanding(a, 0, lane.stream));
+            kernel_launches_++;
+            fused_slices_++;
+            f.ev = getEvent(lane);
+            cudaError_t e = cudaEventRecord(f.ev, lane.stream);
+            if (e != cudaSuccess) return fail(hlDeviceError, "cudaEventRecord: %s", cudaGetErrorString(e));
+          }
+          lane.inflight.push_back(std::move(f));
+          ++l.issued;
+          progressed = true;
+          continue;
+        }
         bool ready = true;
         for (int d : n.wait_for)
           if (progressOf(d) < k + 1) {
@@ -754,6 +870,7 @@ hlResult_t PcieImpl::runWork(const Work& w) {
         }
         InFlight f;
         f.node_slot = (int)i;
+        f.bytes = len;
         f.t0_ns = nowNs();
         const bool host_op = !cuda_ || n.op == ir::Op::H2H || n.op == ir::Op::H2HReduce;
         if (len == 0) {
@@ -836,6 +953,20 @@ hlResult_t PcieImpl::runWork(const Work& w) {
   return bs_->barrier(kBarExec, Config::get().executor_timeout_ms);
 }
 
+int dmaLanePolicy(const char* collective, size_t message_bytes, int world, int max_lanes, int forced) {
+  const int limit = std::max(1, max_lanes);
+  auto clamp = [limit](int v) { return std::max(1, std::min(v, limit)); };
+  if (message_bytes == 0) return 1;
+  if (forced > 0) return clamp(forced);
+  const std::string c = collective ? collective : "";
+  const size_t mib = (size_t)1 << 20;
+  if (c == "allgather") return clamp(message_bytes <= 16 * mib ? 4 : 2);
+  if (c == "reducescatter") return clamp(message_bytes <= 32 * mib ? 4 : (message_bytes <= 128 * mib ? 3 : 2));
+  if (c == "allreduce") return clamp(message_bytes <= 16 * mib ? 4 : (message_bytes <= 64 * mib ? 3 : 2));
+  if (c == "alltoall") return clamp(world >= 8 ? (message_bytes <= 4 * mib ? 8 : 4) : (message_bytes <= 16 * mib ? 4 : 2));   // n - 1 peers per direction
+  return 1;
+}
+
 // ====================================================================== facade
 namespace {
 std::mutex g_reg_mu;
@@ -889,6 +1020,8 @@ hlResult_t PciePath::drain() { return impl_->drain(); }
 hlResult_t PciePath::lastResult() const { return impl_->lastResult(); }
 uint64_t PciePath::kernelLaunches() const { return impl_->kernelLaunches(); }
 uint64_t PciePath::copyOps() const { return impl_->copyOps(); }
+uint64_t PciePath::fusedSlices() const { return impl_->fusedSlices(); }
+uint64_t PciePath::foldedSources() const { return impl_->foldedSources(); }
 const std::vector<int>& PciePath::rankNuma() const { return impl_->rankNuma(); }
 
 }  // namespace hl

@@ -10,6 +10,15 @@
 
 namespace hl {
 
+// Copy-engine lanes (streams per direction) a collective of `message_bytes` uses: small messages are a burst of
+// short transfers and want many lanes so that several are in flight per direction, long ones saturate the link
+// with two and only pay for more in submission time. `forced` > 0 overrides the table (HYLINK_DMA_LANES);
+// the result lies in [1, max_lanes]. Broadcast and unknown collectives use one lane per direction.
+// Parity: pcie-ccl-ascend/src/executor/dma_lane_policy.hpp:12-67 (its table is tuned for 1-12 HCCS DMA lanes;
+// this one for the copy engines of a CUDA device).
+int dmaLanePolicy(const char* collective, size_t message_bytes, int world, int max_lanes, int forced);
+
+
 class PcieImpl;
 
 class PciePath {
@@ -39,6 +48,8 @@ class PciePath {
   hlResult_t lastResult() const;
   uint64_t kernelLaunches() const;
   uint64_t copyOps() const;
+  uint64_t fusedSlices() const;
+  uint64_t foldedSources() const;
   // Logical NUMA node of every rank.
   const std::vector<int>& rankNuma() const;
   PcieImpl* impl() { return impl_; }

@@ -500,6 +500,9 @@ class HylinkBackend : public c10d::Backend {
       d["last_pcie_ms"] = st.last_pcie_ms;
       d["nvls"] = st.nvls;
       d["symm_mode"] = st.symm_mode;
+      d["fused_landing_slices"] = st.fused_landing_slices;
+      d["folded_sources"] = st.folded_sources;
+      d["registered_bytes"] = st.registered_bytes;
     }
     return d;
   }

@@ -44,7 +44,7 @@ class DDPTrainer:
             from .backend import set_cta_budget
 
             if cta_budget is None:
-                cta_budget = int(os.environ.get("HYLINK_DDP_CTA_BUDGET", "64"))
+                cta_budget = int(os.environ.get("HYLINK_DDP_CTA_BUDGET", "32"))
             self._old_budget = set_cta_budget(cta_budget)
         self.model = model.to(device=device, dtype=dtype)
         self.registered_buckets = False

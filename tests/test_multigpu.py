@@ -39,6 +39,8 @@ def test_pcie_path_alone_is_correct():
                         "--path", "pcie", "--no-nccl"], env=env)
     assert '"failures": 0' in out, out[-3000:]
     assert '"copy_engine_ops": 0' not in out
+    # reductions read the landed host chunks themselves: no H2D copy in front of them
+    assert '"fused_landing_slices": 0' not in out
 
 
 def test_forked_collectives_are_correct_and_retune():

@@ -189,3 +189,22 @@ def test_no_gain_guard_pauses_a_split_that_keeps_losing():
         assert c.suggest() == 0.0
     c.suggest()
     assert c.suggest() > 0.0                                                       # probes again after the cool-down
+
+
+def test_dma_lane_policy_table():
+    """Lanes per direction by collective and size: many for bursts of short transfers, two for long messages,
+    one for broadcast; the forced value and the lane limit win over the table."""
+    import ctypes as C
+
+    from hylink_b200._native import lib
+
+    f = lib.hlDmaLaneCount
+    f.restype = C.c_int
+    f.argtypes = [C.c_char_p, C.c_size_t, C.c_int, C.c_int, C.c_int]
+    mib = 1 << 20
+    assert f(b"allreduce", 1 * mib, 8, 8, 0) == 4 and f(b"allreduce", 32 * mib, 8, 8, 0) == 3 and f(b"allreduce", 1024 * mib, 8, 8, 0) == 2
+    assert f(b"allgather", 16 * mib, 4, 8, 0) == 4 and f(b"allgather", 17 * mib, 4, 8, 0) == 2
+    assert f(b"reducescatter", 64 * mib, 4, 8, 0) == 3
+    assert f(b"alltoall", 2 * mib, 8, 8, 0) == 8 and f(b"alltoall", 2 * mib, 4, 8, 0) == 4
+    assert f(b"broadcast", 64 * mib, 8, 8, 0) == 1 and f(b"allreduce", 0, 8, 8, 0) == 1
+    assert f(b"allreduce", 1 * mib, 8, 8, 6) == 6 and f(b"allreduce", 1 * mib, 8, 2, 0) == 2 and f(b"allreduce", 1 * mib, 8, 8, 99) == 8

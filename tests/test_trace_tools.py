@@ -40,6 +40,14 @@ def test_trace_file_is_valid_and_analysable(tmp_path):
                          cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT), capture_output=True, text=True, timeout=120)
     assert out.returncode == 0 and "pcie/allreduce" in out.stdout, out.stdout + out.stderr
     assert len(json.load(open(merged))) > 20
+    # the per-iteration, per-size, host-slice and cross-file reports
+    for args, needle in ((["phases", files[0]], "nothing in flight"), (["by-size", files[0]], "algbw"), (["host", files[0]], "host slices"),
+                         (["compare", files[0], "rank0", files[1], "rank1", "--op", "D2H"], "rank1"), (["summary", files[0]], "dma")):
+        out = subprocess.run([sys.executable, "-m", "hylink_b200.utils.trace_analysis", *args], cwd=ROOT, env=dict(os.environ, PYTHONPATH=ROOT),
+                             capture_output=True, text=True, timeout=120)
+        assert out.returncode == 0 and needle in out.stdout, (args, out.stdout + out.stderr)
+    ev = json.load(open(merged))
+    assert any(e.get("cat") == "dma" and e.get("args", {}).get("bytes", 0) > 0 for e in ev), "slices carry their byte counts"
 
 
 def test_nccl_trace_parser(tmp_path):
