@@ -220,6 +220,7 @@ def timed_passes(tab: Table, steps: int, warmup: int, launches=None):
     torch.cuda.synchronize()
     after = launches() if launches else 0
     per_cell = [sum(ev[it][ci][0].elapsed_time(ev[it][ci][1]) for it in range(steps)) / steps for ci in range(len(tab.cells))]
+    tab.last_min_ms = [min(ev[it][ci][0].elapsed_time(ev[it][ci][1]) for it in range(steps)) for ci in range(len(tab.cells))]
     return per_cell, t0.elapsed_time(t1), after - before
 
 
@@ -421,6 +422,7 @@ def main() -> int:
         sampler.mark_begin()
     launches = (lambda: stats().get("kernel_launches", 0)) if backend == "hylink" else None
     cell_ms, region_ms, n_launch = timed_passes(tab, args.steps, args.warmup, launches)
+    cell_min_ms = list(tab.last_min_ms)
     alpha = stats().get("last_alpha", 0.0)
     cell_ms = max_over_ranks(cell_ms)
     region_ms = max_over_ranks([region_ms])[0]
@@ -454,7 +456,8 @@ def main() -> int:
         f = bus_factor(coll, world)
         b = real / cell_ms[i] / 1e6 * f
         e = real / e2e_ms[i] / 1e6 * f
-        row = {"coll": coll, "bytes": real, "ms": round(cell_ms[i], 4), "busbw_GBs": round(b, 2), "e2e_busbw_GBs": round(e, 2)}
+        row = {"coll": coll, "bytes": real, "ms": round(cell_ms[i], 4), "ms_min_rank0": round(cell_min_ms[i], 4), "busbw_GBs": round(b, 2),
+               "e2e_busbw_GBs": round(e, 2)}
         bw.append(b)
         bw_e2e.append(e)
         if nccl_ms:

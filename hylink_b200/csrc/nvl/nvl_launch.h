@@ -38,6 +38,8 @@ struct ReduceLandingArgs {
 hlResult_t launchLinkProbeBulk(const HlCommDev* dcomm, int to_peer, int blocks, uint32_t tile_bytes, uint64_t bytes, uint64_t dst_off_bytes,
                                int peer, cudaStream_t stream);
 hlResult_t launchReduceLanding(const ReduceLandingArgs& a, int blocks, cudaStream_t stream);
+// Device-to-device copy of whole 16-byte packets between 16-byte aligned buffers (streaming cache hints).
+hlResult_t launchCopy(void* dst, const void* src, size_t bytes, cudaStream_t stream);
 hlResult_t prepareReduceLanding();
 
 // Context warm-up (one trivial kernel): a context whose first work is pure

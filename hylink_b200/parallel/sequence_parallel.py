@@ -12,8 +12,14 @@ ring schedule) but built from collectives it does carry:
   causal mask for its own slice of positions. Traffic: one all-gather of K
   and V (reduce-scatter of their gradients in backward).
 
-Ring-style point-to-point schedules stay on NCCL send/recv
-(:mod:`hylink_b200.parallel.p2p`).
+* :func:`ring_attention` — context parallelism with a ring schedule: the K/V
+  blocks travel once around the ring (n - 1 point-to-point shifts on the NCCL
+  side group of :mod:`hylink_b200.parallel.p2p`, next to this library's
+  collectives), every rank attends its queries to the block it currently
+  holds and merges the partial results with a running log-sum-exp, so no rank
+  ever holds more than two K/V blocks. Blocks that lie entirely in the causal
+  future are not computed. Traffic: (n - 1)/n of K and V per rank, like the
+  all-gather, but in n - 1 steps that overlap with the block computations.
 """
 from __future__ import annotations
 
@@ -83,3 +89,68 @@ def allgather_kv_attention(q, k, v, group=None, causal: bool = True):
         mask = qpos >= torch.arange(n * tl, device=q.device)[None, :]
     a = F.scaled_dot_product_attention(q.transpose(1, 2), kf.transpose(1, 2), vf.transpose(1, 2), attn_mask=mask)
     return a.transpose(1, 2).contiguous()
+
+
+class _RingShift(torch.autograd.Function):
+    """Sends a tensor to the next rank of the ring and returns what the previous rank sent; gradients go the other way."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _shift(x, group, +1)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _shift(g, ctx.group, -1), None
+
+
+def _shift(x: torch.Tensor, group, direction: int) -> torch.Tensor:
+    from . import p2p
+
+    n, r = dist.get_world_size(group), dist.get_rank(group)
+    if n == 1:
+        return x
+    x = x.contiguous()
+    out = torch.empty_like(x)
+    dst, src = (r + direction) % n, (r - direction) % n
+    if group is not None:
+        dst, src = dist.get_global_rank(group, dst), dist.get_global_rank(group, src)
+    for req in p2p.batch_isend_irecv([("send", x, dst), ("recv", out, src)]):
+        req.wait()
+    return out
+
+
+def ring_attention(q, k, v, group=None, causal: bool = True):
+    """q, k, v: [b, t/n, heads, head_dim], sequence sharded in rank order. Returns the same layout.
+
+    Step s works on the K/V block that started on rank (r - s) mod n while the next shift is already in flight."""
+    n, r = dist.get_world_size(group), dist.get_rank(group)
+    b, tl, h, e = q.shape
+    scale = e ** -0.5
+    qh = q.transpose(1, 2)                                           # [b, h, tl, e]
+    kv = torch.stack((k, v))                                         # one message per shift
+    out = None
+    lse = None
+    tri = torch.ones(tl, tl, dtype=torch.bool, device=q.device).tril() if causal else None
+    for s_ in range(n):
+        owner = (r - s_) % n
+        nxt = _RingShift.apply(kv, group) if s_ + 1 < n else None    # issued before this block's math
+        if not causal or owner <= r:
+            kh, vh = kv[0].transpose(1, 2), kv[1].transpose(1, 2)
+            scores = torch.matmul(qh, kh.transpose(-1, -2)) * scale  # [b, h, tl, tl]
+            if causal and owner == r:
+                scores = scores.masked_fill(~tri, float("-inf"))
+            blk_lse = torch.logsumexp(scores.float(), dim=-1)        # [b, h, tl]
+            blk_out = torch.matmul(torch.exp(scores.float() - blk_lse[..., None]).to(vh.dtype), vh)
+            if out is None:
+                out, lse = blk_out.float(), blk_lse
+            else:
+                new = torch.logaddexp(lse, blk_lse)
+                out = out * torch.exp(lse - new)[..., None] + blk_out.float() * torch.exp(blk_lse - new)[..., None]
+                lse = new
+        if nxt is None:
+            # Every rank must run every shift's backward (its neighbours wait for it there), also the ranks whose
+            # last blocks lie in the causal future and never enter the math: tie the end of the chain to the result.
+            out = out + kv.float().sum() * 0.0
+        kv = nxt
+    return out.to(q.dtype).transpose(1, 2).contiguous()

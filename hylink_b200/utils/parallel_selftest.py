@@ -100,7 +100,7 @@ def check_moe(dev, rank, world, tol):
 
 
 def check_attention(dev, rank, world, tol):
-    from hylink_b200.parallel.sequence_parallel import allgather_kv_attention, ulysses_attention
+    from hylink_b200.parallel.sequence_parallel import allgather_kv_attention, ring_attention, ulysses_attention
 
     torch.manual_seed(17)
     b, t, h, e = 2, 6 * world, 2 * world, 8
@@ -110,7 +110,7 @@ def check_attention(dev, rank, world, tol):
     want.square().sum().backward()
     tl = t // world
     sl = slice(rank * tl, (rank + 1) * tl)
-    for name, fn in (("ulysses", ulysses_attention), ("allgather-kv", allgather_kv_attention)):
+    for name, fn in (("ulysses", ulysses_attention), ("allgather-kv", allgather_kv_attention), ("ring", ring_attention)):
         loc = [z[:, sl].clone().requires_grad_(True) for z in full]
         got = fn(*loc, group=None, causal=True)
         _close(got, want[:, sl].detach(), tol, f"{name} attention forward")

@@ -3,7 +3,8 @@
     python -m hylink_b200.utils.profile_kernels [--ranks 4] [--mib 48]
 
 Runs, on ONE device: the two-shot pull all-reduce, the push all-reduce, the
-pipelined all-reduce, the push reduce-scatter and the all-gather with `--ranks`
+pipelined all-reduce, the push reduce-scatter, the all-gather and the zero-copy
+kernels on registered memory (peer-pointer flavour) with `--ranks`
 emulated ranks (one cooperative launch each; `--mib` MiB of bf16 per rank, so
 the working set is larger than the 126 MB L2 while staying within a few
 hundred MB), and the landing-reduce kernel over four `--landing-mib` MiB sources. Prints the
@@ -24,6 +25,7 @@ def main(argv=None) -> int:
     ap.add_argument("--mib", type=int, default=48)
     ap.add_argument("--reps", type=int, default=2, help="timed launches after the warm-up launch (0: warm-up only)")
     ap.add_argument("--landing-mib", type=int, default=128)
+    ap.add_argument("--no-zero-copy", action="store_true")
     a = ap.parse_args(argv)
     from hylink_b200.ops import EmuGroup, reduce_landing
 
@@ -56,6 +58,18 @@ def main(argv=None) -> int:
     timed("reducescatter_push", lambda: g.run("reduce_scatter", ins, [o[:seg] for o in outs], seg, in_seg_stride=seg),
           n * nb * (2.0 * (n - 1) / n + 1 + 1.0 / n))
     timed("allgather_pull", lambda: g.run("all_gather", [t[:seg] for t in ins], gathered, seg, out_seg_stride=seg), n * (2 * seg * 2 + 2 * count * 2))
+    # zero-copy kernels on registered memory (peer-pointer flavour; the switch flavour needs real peers)
+    if not a.no_zero_copy:
+        rin = g.alloc_registered(count, torch.bfloat16)
+        rout = g.alloc_registered(count, torch.bfloat16)
+        for t, src in zip(rin, ins):
+            t.copy_(src)
+        timed("allreduce_zerocopy_p2p", lambda: g.run("all_reduce", rin, rout, count, algo="zerocopy_p2p"), n * nb * (1 + 1))
+        timed("reducescatter_zerocopy_p2p", lambda: g.run("reduce_scatter", rin, [o[:seg] for o in outs], seg, in_seg_stride=seg, algo="zerocopy_p2p"),
+              n * nb * (1 + 1.0 / n))
+        timed("allgather_zerocopy_p2p", lambda: g.run("all_gather", [t[:seg] for t in ins], rout, seg, out_seg_stride=seg, algo="zerocopy_p2p"),
+              n * (seg * 2 + count * 2))
+        del rin, rout
     srcs = [torch.randn(a.landing_mib << 19, device="cuda").to(torch.bfloat16) for _ in range(4)]
     dst = torch.empty_like(srcs[0])
     timed("reduce_landing_4way", lambda: reduce_landing(dst, srcs), 5 * srcs[0].numel() * 2)
