@@ -231,6 +231,24 @@ hlResult_t compile(const Program& p, const CompileOptions& opt, CompiledGraph* o
       }
     }
   }
+  // Round guards: for every node that writes a staging chunk, all other nodes that read or write that chunk.
+  {
+    std::map<Loc, std::vector<int>> users;
+    auto staged = [](const Loc& l) { return l.space == Buf::Host || l.space == Buf::Internal || l.space == Buf::Scratch; };
+    for (const Node& n : g.nodes) {
+      if (n.op == Op::NOP || n.skip) continue;
+      if (staged(n.src)) users[n.src].push_back(n.id);
+      if (n.op == Op::H2HReduce && staged(n.src2)) users[n.src2].push_back(n.id);
+      if (staged(n.dst)) users[n.dst].push_back(n.id);
+    }
+    for (Node& n : g.nodes) {
+      if (n.op == Op::NOP || n.skip || !staged(n.dst)) continue;
+      for (int u : users[n.dst])
+        if (u != n.id) n.round_guards.push_back(u);
+      std::sort(n.round_guards.begin(), n.round_guards.end());
+      n.round_guards.erase(std::unique(n.round_guards.begin(), n.round_guards.end()), n.round_guards.end());
+    }
+  }
   *out = std::move(g);
   return hlSuccess;
 }

@@ -54,6 +54,11 @@ struct Node {
   // `fused_h2d` names that H2D node on the reduce, `fused_into` names the reduce on the H2D node.
   int fused_h2d = -1;
   int fused_into = -1;
+  // Round guards. A message larger than the staging pools runs the same graph several times ("rounds") over the same
+  // host, internal and scratch chunks. Before this node overwrites such a chunk in round w + 1, every node (of any
+  // rank) that touched the chunk in round w must be through with it: these are those nodes. With them a round needs
+  // no barrier at its end; only the chunks that are really reused wait for their last users.
+  std::vector<int> round_guards;
 };
 
 enum class InPlace { None, Same, GatherSlot, ScatterSlot };

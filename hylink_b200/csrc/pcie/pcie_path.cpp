@@ -85,6 +85,7 @@ struct Work {
   size_t scale_seg_stride = 0;
   std::string name;
   int dma_lanes = 2;         // copy-engine lanes per direction this collective uses (dmaLanePolicy)
+  int prev_nslices = 0;      // slices per node of the previous round of the same message (0: this is the first round)
 };
 
 constexpr int kMaxDmaLanes = 8;
@@ -486,6 +487,7 @@ hlResult_t PcieImpl::submit(const std::string& collective, const std::string& fo
     w.name = collective;
     w.dma_lanes = dmaLanePolicy(collective.c_str(), active_total * es * (size_t)std::max(send_segs, recv_segs), n_, kMaxDmaLanes, Config::get().dma_lanes);
     done += act;
+    if (!works.empty()) w.prev_nslices = works.back().geo.nslices;
     works.push_back(std::move(w));
   }
   const double total_scale = (double)(scale == 0.0f ? 1.0f : scale) * (op == hlAvg ? 1.0 / n_ : 1.0);
@@ -728,6 +730,21 @@ hlResult_t PcieImpl::runWork(const Work& w) {
       ++remaining;
     }
   }
+  // Rounds of one message reuse the staging chunks without a barrier in between: a node that overwrites a chunk waits
+  // (before its first slice) until everybody who used that chunk in the previous round is through with it there.
+  static const bool round_barrier = envBool({"HYLINK_PCIE_ROUND_BARRIER"}, false);
+  auto doneInPreviousRound = [&](int node_id) -> bool {
+    const uint64_t v = shared_->progress[node_id].load(std::memory_order_acquire);
+    const uint64_t t = v >> kSeqShift;
+    if (t >= w.seq) return true;                       // its rank is already in this round: it finished the last one
+    return t + 1 == w.seq && (int)(v & kSliceMask) >= w.prev_nslices;
+  };
+  auto guardsClear = [&](const ir::Node& n) -> bool {
+    if (w.first_round || round_barrier) return true;
+    for (int gnode : n.round_guards)
+      if (!doneInPreviousRound(gnode)) return false;
+    return true;
+  };
   // inputs of slice k of a fused reduce: its own wait list with the H2D node replaced by what the H2D waited for,
   // and (when folded behind `after`) without the reduce that precedes it in the same launch
   auto fusedReady = [&](const ir::Node& r, int k, int after) -> bool {
@@ -789,6 +806,7 @@ hlResult_t PcieImpl::runWork(const Work& w) {
       Lane& lane = laneFor(n.op, (int)i, w.dma_lanes);
       while (l.issued < ns && (int)lane.inflight.size() < kLaneDepth) {
         const int k = l.issued;
+        if (k == 0 && !guardsClear(n)) break;
         if (fuse && n.op == ir::Op::D2DReduce && n.fused_h2d >= 0) {
           if (!fusedReady(n, k, -1)) break;
           size_t dlen = 0, hlen = 0;
@@ -948,8 +966,10 @@ hlResult_t PcieImpl::runWork(const Work& w) {
     }
   }
   bs_->heartbeat();
-  // Peers may still be reading this rank's staging chunks (and, for direct
-  // schedules, its device buffers): nobody moves on before everyone is done.
+  // Peers may still be reading this rank's staging chunks (and, for direct schedules, its device buffers): after the
+  // last round of a message nobody moves on before everyone is done. Between the rounds of one message the round
+  // guards order the reuse of every chunk, so no barrier is needed there.
+  if (!w.last_round && !round_barrier && !g.uses_remote_device) return hlSuccess;
   return bs_->barrier(kBarExec, Config::get().executor_timeout_ms);
 }
 

@@ -317,3 +317,35 @@ def test_eight_ranks_two_numa_nodes():
     """The 8-GPU board layout (pattern 00001111): 72 host chunks per all-reduce, generated schedules."""
     env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP="00001111", HYLINK_HOST_BUFFER_SIZE="32M", HYLINK_H2H_WORKERS="1")
     run_ranks(_eight_rank_worker, 8, env=env, timeout=300)
+
+
+def _many_rounds_worker(rank, n, uid):
+    """Every collective through pools far smaller than the message: the rounds follow one another without a barrier,
+    ordered only by the guards on the chunks they reuse."""
+    c = _comm(rank, n, uid)
+    count = 3 << 18                                   # 3 MiB of fp32 per segment
+    for rep in range(2):
+        x = _data(rank, count, torch.float32, seed=40 + rep)
+        out = torch.zeros(count)
+        c.all_reduce(x, out)
+        seg = count // n
+        part = torch.zeros(seg)
+        c.reduce_scatter(x, part)
+        full = torch.zeros(count)
+        c.all_gather(x[:seg], full)
+        a2a = torch.zeros(count)
+        c.all_to_all(x, a2a)
+        c.drain()
+        ref = sum(_data(r, count, torch.float32, seed=40 + rep).double() for r in range(n))
+        assert torch.allclose(out.double(), ref, atol=1e-5)
+        assert torch.allclose(part.double(), ref[rank * seg:(rank + 1) * seg], atol=1e-5)
+        assert torch.equal(full, torch.cat([_data(r, count, torch.float32, seed=40 + rep)[:seg] for r in range(n)]))
+        assert torch.equal(a2a, torch.cat([_data(r, count, torch.float32, seed=40 + rep)[rank * seg:(rank + 1) * seg] for r in range(n)]))
+    c.close()
+    return True
+
+
+@pytest.mark.parametrize("n,numa", [(2, "00"), (4, "0011")])
+def test_rounds_without_a_barrier_between_them(n, numa):
+    env = dict(SMALL_POOLS, HYLINK_HOST_BUFFER_SIZE="2M", HYLINK_INTERNAL_BUFFER_BYTES="1M", HYLINK_GPU_NUMA_MAP=numa)
+    run_ranks(_many_rounds_worker, n, env=env, timeout=300)
