@@ -606,6 +606,7 @@ hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out) {
   out->fused_landing_slices = comm->pcie ? comm->pcie->fusedSlices() : 0;
   out->folded_sources = comm->pcie ? comm->pcie->foldedSources() : 0;
   out->registered_bytes = comm->nvl ? comm->nvl->heapInUse() : 0;
+  out->small_path_calls = comm->pcie ? comm->pcie->smallCalls() : 0;
   if (comm->orch) comm->orch->fillStats(out);
   return hlSuccess;
 }

@@ -192,6 +192,7 @@ typedef struct {
   uint64_t fused_landing_slices; /* PCIe path: reduce launches that read landed host chunks themselves (no H2D copy) */
   uint64_t folded_sources;    /* ... and further sources folded into such launches */
   uint64_t registered_bytes;  /* bytes handed out from the registered-memory heap */
+  uint64_t small_path_calls;  /* PCIe path: collectives served by the stream-ordered small-message path (no CPU thread) */
 } hlCommStats;
 hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out);
 /* Serialises the tuned (op-key -> alpha, bandwidth) table as JSON into buf;

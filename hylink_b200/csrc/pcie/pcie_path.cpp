@@ -125,6 +125,7 @@ class PcieImpl {
   hlResult_t lastResult() const { return (hlResult_t)last_result_.load(); }
   uint64_t kernelLaunches() const { return kernel_launches_.load(); }
   uint64_t copyOps() const { return copy_ops_.load(); }
+  uint64_t smallCalls() const { return small_calls_.load(); }
   uint64_t fusedSlices() const { return fused_slices_.load(); }
   uint64_t foldedSources() const { return folded_sources_.load(); }
   const std::vector<int>& rankNuma() const { return numa_; }
@@ -135,6 +136,14 @@ class PcieImpl {
                      int recv_segs, size_t bytes, std::shared_ptr<const Plan>* out);
   void threadMain();
   hlResult_t runWork(const Work& w);
+  // Returns hlSuccess with *handled = false when the call does not qualify (the ordinary executor then runs it).
+  hlResult_t submitSmall(const std::string& collective, const void* send, void* recv, size_t seg_count, int send_segs, int recv_segs,
+                         hlDataType_t t, hlRedOp_t op, float scale, int root, cudaStream_t us, bool* handled);
+  volatile uint64_t* smallFlag(bool done, int parity, int rank, bool device) const {
+    char* base = device ? small_dev_ : small_host_;
+    return reinterpret_cast<volatile uint64_t*>(base) + ((done ? 2 : 0) + parity) * kMaxRanks + rank;
+  }
+  void watchSmallCalls();
   hlResult_t waitReady(const Work& w);
   void releaseDoorbell(uint64_t value);
   void failAll(hlResult_t r);
@@ -156,7 +165,21 @@ class PcieImpl {
   std::atomic<uint64_t> fused_slices_{0}, folded_sources_{0};
   std::vector<size_t> host_map_bytes_;
   std::vector<bool> host_registered_, host_cuda_alloc_;
-  size_t host_bytes_ = 0;
+  size_t host_bytes_ = 0;        // size of every pool
+  size_t sched_host_bytes_ = 0;  // the part of a pool that schedules use (the small-message area sits behind it in pool 0)
+  // ---- small-message path: stream-ordered one-shot exchange through pinned host memory (submitSmall)
+  char* small_host_ = nullptr;   // the area as the CPU sees it: 4 KiB of flag words, then [parity][rank] slots
+  char* small_dev_ = nullptr;    // ... and as this device addresses it
+  size_t small_slot_bytes_ = 0;
+  uint64_t small_seq_ = 0;
+  struct SmallPending {
+    uint64_t seq;
+    uint64_t t_ns;
+  };
+  std::deque<SmallPending> small_pending_;   // under mu_: calls whose completion the watchdog still has to see
+  cudaEvent_t small_ev_ = nullptr;
+  bool small_used_ = false;
+  std::atomic<uint64_t> small_calls_{0};
   char* internal_ = nullptr;
   size_t internal_bytes_ = 0;
   char* inplace_stage_ = nullptr;
@@ -192,6 +215,11 @@ hlResult_t PcieImpl::init() {
   numa_nodes_ = (int)phys_of_logical_.size();
   bs_->publishSelf(device_, numa_[(size_t)rank_]);
   host_bytes_ = cfg.host_buffer_bytes & ~(size_t)4095;
+  // behind the schedules' part of pool 0: flag words + two parities of one slot per rank
+  small_slot_bytes_ = (cfg.small_msg_fastpath && cuda_) ? ((cfg.small_msg_threshold_bytes + 4095) & ~(size_t)4095) : 0;
+  const size_t small_area = small_slot_bytes_ ? 4096 + 2 * (size_t)n_ * small_slot_bytes_ : 0;
+  if (small_area * 2 > host_bytes_) small_slot_bytes_ = 0;   // tiny pools (tests): no small-message area
+  sched_host_bytes_ = host_bytes_ - (small_slot_bytes_ ? small_area : 0);
   internal_bytes_ = cfg.internal_buffer_bytes & ~(size_t)4095;
   if (cuda_) {
     HL_CUDA(cudaSetDevice(device_));
@@ -304,6 +332,15 @@ hlResult_t PcieImpl::createHostPools() {
     fuse_landing_ = fuse_landing_ && envBool({"HYLINK_PCIE_FUSE_LANDING"}, true);
   } else {
     fuse_landing_ = false;
+  }
+  if (small_slot_bytes_ && host_base_[0] && host_dev_base_[0]) {
+    small_host_ = host_base_[0] + sched_host_bytes_;
+    small_dev_ = host_dev_base_[0] + sched_host_bytes_;
+    if (rank_ == 0) memset(small_host_, 0, 4096);   // flag words start at zero before anybody meets at the barrier below
+    if (cudaEventCreateWithFlags(&small_ev_, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      small_host_ = small_dev_ = nullptr;
+    }
   }
   return bs_->barrier(kBarExec);
 }
@@ -419,6 +456,11 @@ hlResult_t PcieImpl::submit(const std::string& collective, const std::string& fo
   if (stride > seg_count) return fail(hlInvalidArgument, "stride %zu exceeds segment length %zu", stride, seg_count);
   if (stride == seg_count) return hlSuccess;
   const size_t active_total = seg_count - stride;
+  if (stride == 0 && forced_xml.empty() && small_dev_) {
+    bool handled = false;
+    HL_CHECK(submitSmall(collective, send, recv, seg_count, send_segs, recv_segs, t, op, scale, root, (cudaStream_t)stream, &handled));
+    if (handled) return hlSuccess;
+  }
   // in-place detection by address
   ir::InPlace ip = ir::InPlace::None;
   const char* s = (const char*)send;
@@ -461,7 +503,7 @@ hlResult_t PcieImpl::submit(const std::string& collective, const std::string& fo
   // rounds: the chunk pitch must fit the staging pools and the device scratch
   const int cps = std::max(1, g.input_chunks ? g.input_chunks / g.send_segs : g.output_chunks / std::max(1, g.recv_segs));
   size_t max_chunk_bytes = (size_t)1 << 40;
-  if (g.host_chunks) max_chunk_bytes = std::min(max_chunk_bytes, host_bytes_ / (size_t)g.host_chunks);
+  if (g.host_chunks) max_chunk_bytes = std::min(max_chunk_bytes, sched_host_bytes_ / (size_t)g.host_chunks);
   const int dev_chunks = g.internal_chunks + g.scratch_chunks;
   if (dev_chunks) max_chunk_bytes = std::min(max_chunk_bytes, internal_bytes_ / (size_t)dev_chunks);
   max_chunk_bytes &= ~(size_t)255;
@@ -546,7 +588,129 @@ hlResult_t PcieImpl::submit(const std::string& collective, const std::string& fo
   return hlSuccess;
 }
 
+
+// ---------------------------------------------------------------------- small messages
+// Below HYLINK_SMALL_MSG_THRESHOLD_BYTES (1 MiB per rank) the graph executor's fixed costs dominate: a doorbell round
+// trip to the CPU thread, one event per slice, a cross-rank barrier. Small calls therefore never reach that thread.
+// Everything is enqueued on the caller's stream and ordered by stream memory operations on flag words that live in
+// the shared pinned pool, so that GPUs signal one another through host memory without any CPU in the path:
+//   wait  done[p][q] >= s - 2 for every q   (the slots of this parity are free: call s - 2 has been read everywhere)
+//   copy  the input into slot [p][rank] of the pool (copy engine, device to host)
+//   write ready[p][rank] = s ; wait ready[p][q] >= s for every q
+//   ONE launch of the landing-reduce kernel that reads all n slots over PCIe and writes the result (all-reduce,
+//   reduce-scatter), or n copy-engine transfers out of the slots (all-gather, all-to-all, broadcast)
+//   write done[p][rank] = s
+// (p = s & 1). The flag waits have no time-out of their own, so the executor thread keeps a list of the calls in
+// flight and, when one is overdue, releases every flag from the CPU (they are host memory) and latches an error:
+// a stream is never left parked.
+// Parity: the reference's small-message executor (pcie-ccl-cuda/src/fastpath/small_message_executor.cpp:239-284,
+// 555-588, 766-856) has a thread per communicator, three streams and per-slot scratch, negotiates "all direct" against
+// "host staged" per call through shared memory and ends with a shm barrier; its direct mode copies between peers,
+// which on this machine is the dedicated-link path's job.
+hlResult_t PcieImpl::submitSmall(const std::string& collective, const void* send, void* recv, size_t seg_count, int send_segs, int recv_segs,
+                                 hlDataType_t t, hlRedOp_t op, float scale, int root, cudaStream_t us, bool* handled) {
+  *handled = false;
+  const size_t es = hlTypeSize(t);
+  const size_t in_bytes = seg_count * es * (size_t)send_segs;
+  if (!cuda_ || !small_dev_ || !stream_mem_ops_ || n_ < 2 || n_ > 8 || in_bytes == 0 || in_bytes > small_slot_bytes_) return hlSuccess;
+  if (in_bytes > Config::get().small_msg_threshold_bytes) return hlSuccess;
+  const bool reduces = collective == "allreduce" || collective == "reducescatter";
+  const bool is_int = !(t == hlFloat16 || t == hlBfloat16 || t == hlFloat32 || t == hlFloat64);
+  if (reduces && op == hlAvg && is_int) return hlSuccess;   // integer averages divide: the ordinary path does that
+  if (!reduces && collective != "allgather" && collective != "alltoall" && collective != "broadcast") return hlSuccess;
+  const CudaDriver* drv = CudaDriver::get();
+  if (!drv) return hlSuccess;
+  *handled = true;
+  TraceScope range("pcie", "small-message", rank_);
+  range.setBytes((long long)in_bytes);
+  HL_CUDA(cudaSetDevice(device_));
+  const uint64_t s = ++small_seq_;
+  const int p = (int)(s & 1);
+  auto dptr = [&](bool done, int q) { return (CUdeviceptr)(uintptr_t)smallFlag(done, p, q, true); };
+  auto slot = [&](int q, bool device) { return (device ? small_dev_ : small_host_) + 4096 + ((size_t)p * n_ + (size_t)q) * small_slot_bytes_; };
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    small_pending_.push_back({s, nowNs()});
+    small_used_ = true;
+  }
+  cv_.notify_all();   // the watchdog starts counting
+  if (s > 2)
+    for (int q = 0; q < n_; ++q) HL_CU(drv, cuStreamWaitValue64((CUstream)us, dptr(true, q), s - 2, CU_STREAM_WAIT_VALUE_GEQ));
+  const bool contributes = collective != "broadcast" || rank_ == root;
+  if (contributes) {
+    HL_CUDA(cudaMemcpyAsync(slot(rank_, false), send, in_bytes, cudaMemcpyDeviceToHost, us));
+    copy_ops_++;
+  }
+  HL_CU(drv, cuStreamWriteValue64((CUstream)us, dptr(false, rank_), s, 0));
+  for (int q = 0; q < n_; ++q)
+    if (q != rank_) HL_CU(drv, cuStreamWaitValue64((CUstream)us, dptr(false, q), s, CU_STREAM_WAIT_VALUE_GEQ));
+  const size_t seg_bytes = seg_count * es;
+  if (reduces) {
+    nvl::ReduceLandingArgs a;
+    memset(&a, 0, sizeof(a));
+    a.dst = recv;
+    a.nsrc = n_;
+    for (int q = 0; q < n_; ++q) a.src[q] = slot(q, true) + (collective == "reducescatter" ? (size_t)rank_ * seg_bytes : 0);
+    a.count = seg_count;
+    a.dtype = t;
+    a.op = op == hlAvg ? hlSum : op;
+    a.scale = (scale == 0.0f ? 1.0f : scale) * (op == hlAvg ? 1.0f / (float)n_ : 1.0f);
+    HL_CHECK(nvl::launchReduceLanding(a, 0, us));
+    kernel_launches_++;
+  } else if (collective == "broadcast") {
+    if (rank_ != root || recv != send) {
+      HL_CUDA(cudaMemcpyAsync(recv, slot(root, false), in_bytes, cudaMemcpyHostToDevice, us));
+      copy_ops_++;
+    }
+  } else {
+    for (int k = 0; k < n_; ++k) {
+      const int q = (rank_ + k) % n_;
+      const char* from = slot(q, false) + (collective == "alltoall" ? (size_t)rank_ * seg_bytes : 0);
+      HL_CUDA(cudaMemcpyAsync((char*)recv + (size_t)q * seg_bytes, from, seg_bytes, cudaMemcpyHostToDevice, us));
+      copy_ops_++;
+    }
+  }
+  HL_CU(drv, cuStreamWriteValue64((CUstream)us, dptr(true, rank_), s, 0));
+  HL_CUDA(cudaEventRecord(small_ev_, us));
+  small_calls_++;
+  (void)recv_segs;
+  return hlSuccess;
+}
+
+// Executor thread, between work items: forget the small calls that are through, release everything when one is overdue.
+void PcieImpl::watchSmallCalls() {
+  if (!small_host_) return;
+  const uint64_t limit = (uint64_t)Config::get().executor_timeout_ms * 1000000ull;
+  bool overdue = false;
+  {
+    std::lock_guard<std::mutex> lk(mu_);
+    while (!small_pending_.empty()) {
+      const SmallPending& f = small_pending_.front();
+      const uint64_t seen = __atomic_load_n((uint64_t*)smallFlag(true, (int)(f.seq & 1), rank_, false), __ATOMIC_ACQUIRE);
+      if (seen >= f.seq) {
+        small_pending_.pop_front();
+        continue;
+      }
+      overdue = nowNs() - f.t_ns > limit || shared_->failed.load(std::memory_order_relaxed);
+      break;
+    }
+  }
+  if (overdue && last_result_.load() == hlSuccess) {
+    HL_ERR("rank %d: a small-message collective did not complete within %d ms: releasing every flag", rank_, Config::get().executor_timeout_ms);
+    for (int k = 0; k < 4 * kMaxRanks; ++k) __atomic_store_n((uint64_t*)small_host_ + k, kReleaseAll, __ATOMIC_RELEASE);
+    fail(hlTimeout, "small-message collective timed out (a peer never arrived)");
+    failAll(hlTimeout);
+    std::lock_guard<std::mutex> lk(mu_);
+    small_pending_.clear();
+  }
+}
+
 hlResult_t PcieImpl::drain() {
+  if (small_used_ && small_ev_) {
+    // small calls live on the caller's streams only; the watchdog releases their waits if a peer is lost
+    cudaError_t e = cudaEventSynchronize(small_ev_);
+    if (e != cudaSuccess) return fail(hlDeviceError, "drain: %s", cudaGetErrorString(e));
+  }
   std::unique_lock<std::mutex> lk(mu_);
   const uint64_t target = next_door_ - 1;
   const int tmo = Config::get().executor_timeout_ms;
@@ -578,9 +742,13 @@ void PcieImpl::threadMain() {
     Work w;
     {
       std::unique_lock<std::mutex> lk(mu_);
-      cv_.wait(lk, [&] { return stop_ || !queue_.empty(); });
+      // with small calls in flight the thread also wakes up by itself to look after their deadlines
+      if (small_pending_.empty()) cv_.wait(lk, [&] { return stop_ || !queue_.empty() || !small_pending_.empty(); });
+      else cv_.wait_for(lk, std::chrono::milliseconds(50), [&] { return stop_ || !queue_.empty(); });
       if (queue_.empty()) {
         if (stop_) return;
+        lk.unlock();
+        watchSmallCalls();
         continue;
       }
       w = std::move(queue_.front());
@@ -1041,6 +1209,7 @@ hlResult_t PciePath::lastResult() const { return impl_->lastResult(); }
 uint64_t PciePath::kernelLaunches() const { return impl_->kernelLaunches(); }
 uint64_t PciePath::copyOps() const { return impl_->copyOps(); }
 uint64_t PciePath::fusedSlices() const { return impl_->fusedSlices(); }
+uint64_t PciePath::smallCalls() const { return impl_->smallCalls(); }
 uint64_t PciePath::foldedSources() const { return impl_->foldedSources(); }
 const std::vector<int>& PciePath::rankNuma() const { return impl_->rankNuma(); }
 

@@ -49,6 +49,7 @@ class PciePath {
   uint64_t kernelLaunches() const;
   uint64_t copyOps() const;
   uint64_t fusedSlices() const;
+  uint64_t smallCalls() const;
   uint64_t foldedSources() const;
   // Logical NUMA node of every rank.
   const std::vector<int>& rankNuma() const;

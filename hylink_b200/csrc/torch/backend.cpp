@@ -503,6 +503,7 @@ class HylinkBackend : public c10d::Backend {
       d["fused_landing_slices"] = st.fused_landing_slices;
       d["folded_sources"] = st.folded_sources;
       d["registered_bytes"] = st.registered_bytes;
+      d["small_path_calls"] = st.small_path_calls;
     }
     return d;
   }

@@ -41,6 +41,8 @@ def test_pcie_path_alone_is_correct():
     assert '"copy_engine_ops": 0' not in out
     # reductions read the landed host chunks themselves: no H2D copy in front of them
     assert '"fused_landing_slices": 0' not in out
+    # and the sizes below 1 MiB never reach the executor thread
+    assert '"small_path_calls": 0' not in out
 
 
 def test_forked_collectives_are_correct_and_retune():
