@@ -271,6 +271,7 @@ hlResult_t makeGeometry(const CompiledGraph& g, size_t seg_count, size_t stride,
   geo.chunk_elems = g.input_chunks ? ce_in : ce_out;
   if (geo.chunk_elems == 0) geo.chunk_elems = 1;
   geo.chunk_bytes = (geo.chunk_elems * elem + 255) & ~(size_t)255;
+  geo.pitch_bytes = geo.chunk_bytes;
   geo.slice_bytes = subchunkSliceFor(geo.chunk_bytes);
   // slices must be element- and 16-byte aligned
   geo.slice_bytes = std::max<size_t>(256, geo.slice_bytes & ~(size_t)255);

@@ -91,7 +91,8 @@ struct Geometry {
   size_t stride = 0;         // leading elements of every segment that are skipped
   size_t active = 0;         // elements of every segment handled by this call (after `stride`)
   size_t chunk_elems = 0;    // elements per device chunk (last chunk of a segment may be shorter)
-  size_t chunk_bytes = 0;    // dense pitch of internal / scratch / host chunks (256-byte multiple)
+  size_t chunk_bytes = 0;    // bytes of one internal / scratch / host chunk (256-byte multiple)
+  size_t pitch_bytes = 0;    // distance between two such chunks in their pool (>= chunk_bytes; equal unless the caller sets it)
   size_t slice_bytes = 0;
   int nslices = 1;
   int cps_in = 1, cps_out = 1;

@@ -529,7 +529,12 @@ hlResult_t PcieImpl::submit(const std::string& collective, const std::string& fo
     w.name = collective;
     w.dma_lanes = dmaLanePolicy(collective.c_str(), active_total * es * (size_t)std::max(send_segs, recv_segs), n_, kMaxDmaLanes, Config::get().dma_lanes);
     done += act;
-    if (!works.empty()) w.prev_nslices = works.back().geo.nslices;
+    if (!works.empty()) {
+      w.prev_nslices = works.back().geo.nslices;
+      // one pitch for all rounds of a message: the round guards order reuse chunk by chunk, so chunk c must cover the
+      // same bytes of the staging pools in every round (the last round's chunks are shorter, not denser)
+      w.geo.pitch_bytes = works.front().geo.pitch_bytes;
+    }
     works.push_back(std::move(w));
   }
   const double total_scale = (double)(scale == 0.0f ? 1.0f : scale) * (op == hlAvg ? 1.0 / n_ : 1.0);
@@ -826,13 +831,13 @@ char* PcieImpl::resolve(const Work& w, const ir::Loc& l, size_t* len_bytes, bool
   const ir::CompiledGraph& g = w.plan->graph;
   const size_t full = geo.chunk_elems * geo.elem;
   *len_bytes = full;
-  if (l.space == ir::Buf::Host) return host_base_[(size_t)l.owner] + (size_t)l.chunk * geo.chunk_bytes;
+  if (l.space == ir::Buf::Host) return host_base_[(size_t)l.owner] + (size_t)l.chunk * geo.pitch_bytes;
   char* base = nullptr;
   int slot = 0;
   switch (l.space) {
     case ir::Buf::Input: slot = 0; base = (char*)w.send; break;
     case ir::Buf::Output: slot = 1; base = w.recv; break;
-    case ir::Buf::Scratch: slot = 2; base = internal_ + (size_t)g.internal_chunks * geo.chunk_bytes; break;
+    case ir::Buf::Scratch: slot = 2; base = internal_ + (size_t)g.internal_chunks * geo.pitch_bytes; break;
     default: slot = 3; base = internal_; break;
   }
   if (l.owner != rank_) {
@@ -849,7 +854,7 @@ char* PcieImpl::resolve(const Work& w, const ir::Loc& l, size_t* len_bytes, bool
     *len_bytes = bytes;
     return base + off;
   }
-  return base + (size_t)l.chunk * geo.chunk_bytes;
+  return base + (size_t)l.chunk * geo.pitch_bytes;
 }
 
 hlResult_t PcieImpl::runWork(const Work& w) {
@@ -874,7 +879,7 @@ hlResult_t PcieImpl::runWork(const Work& w) {
   // publish this rank's bases for peers that read them directly (threads-as-ranks mode)
   shared_->ptrs[rank_][0].store((uint64_t)(uintptr_t)w.send, std::memory_order_relaxed);
   shared_->ptrs[rank_][1].store((uint64_t)(uintptr_t)w.recv, std::memory_order_relaxed);
-  shared_->ptrs[rank_][2].store((uint64_t)(uintptr_t)(internal_ + (size_t)g.internal_chunks * geo.chunk_bytes), std::memory_order_relaxed);
+  shared_->ptrs[rank_][2].store((uint64_t)(uintptr_t)(internal_ + (size_t)g.internal_chunks * geo.pitch_bytes), std::memory_order_relaxed);
   shared_->ptrs[rank_][3].store((uint64_t)(uintptr_t)internal_, std::memory_order_relaxed);
   shared_->ready_seq[rank_].store(w.seq, std::memory_order_release);
 
@@ -996,7 +1001,7 @@ hlResult_t PcieImpl::runWork(const Work& w) {
           a.scale = 1.0f;
           auto hostSrc = [&](const ir::Node& h2d) {
             (void)resolve(w, h2d.src, &hlen, &pending);
-            return host_dev_base_[(size_t)h2d.src.owner] + (size_t)h2d.src.chunk * geo.chunk_bytes + off;
+            return host_dev_base_[(size_t)h2d.src.owner] + (size_t)h2d.src.chunk * geo.pitch_bytes + off;
           };
           a.src[a.nsrc++] = hostSrc(g.nodes[(size_t)n.fused_h2d]);
           f.also.push_back(local_of[(size_t)n.fused_h2d]);

@@ -118,8 +118,10 @@ def main(argv=None) -> int:
     link = min(d2h, h2d)
     nbytes = parse_size(a.size)
     n_el = nbytes // 2 // world * world
-    x = (torch.rand(n_el, device=dev) * 2 - 1).to(torch.bfloat16)
-    y = torch.empty_like(x)
+    # registered buffers: the NVLink half of every forked call runs zero-copy
+    x = comm.alloc_registered(n_el, torch.bfloat16)
+    y = comm.alloc_registered(n_el, torch.bfloat16)
+    x.copy_((torch.rand(n_el, device=dev) * 2 - 1).to(torch.bfloat16))
     seg = n_el // world
     bg = Interferer(dev, link)
     bg.start()
@@ -161,6 +163,33 @@ def main(argv=None) -> int:
                 if outf:
                     outf.write(line + "\n")
             it += 1
+    # the dedicated link alone, without interference and under the heaviest level: what forking has to beat
+    for level in (0, max(int(v) for v in a.levels.split(","))):
+        bg.percent = level
+        dist.barrier()
+        times = []
+        for _ in range(max(8, a.iters // 4)):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda._sleep(2_000_000)
+            dist.all_reduce(align)
+            e0.record()
+            if a.coll == "allreduce":
+                comm.all_reduce(x, y, path="nvlink")
+            elif a.coll == "allgather":
+                comm.all_gather(x[:seg], y, path="nvlink")
+            else:
+                comm.reduce_scatter(x, y[:seg], path="nvlink")
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append(float(t[0]))
+        if rank == 0:
+            med = sorted(times)[len(times) // 2]
+            line = json.dumps({"event": "nvlink_only", "interference_pct": level, "ms": round(med, 4), "busbw_GBs": round(n_el * 2 / med / 1e6 * factor, 1)})
+            print(line, flush=True)
+            if outf:
+                outf.write(line + "\n")
     bg.stop_flag = True
     bg.join(2)
     if rank == 0:
