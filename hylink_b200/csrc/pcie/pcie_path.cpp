@@ -127,6 +127,7 @@ class PcieImpl {
   uint64_t copyOps() const { return copy_ops_.load(); }
   uint64_t smallCalls() const { return small_calls_.load(); }
   uint64_t fusedSlices() const { return fused_slices_.load(); }
+  uint64_t rangeJobs() const { return range_jobs_.load(); }
   uint64_t foldedSources() const { return folded_sources_.load(); }
   const std::vector<int>& rankNuma() const { return numa_; }
 
@@ -162,7 +163,7 @@ class PcieImpl {
   std::vector<char*> host_base_;
   std::vector<char*> host_dev_base_;   // the same pools as the device addresses them (mapped pinned memory)
   bool fuse_landing_ = true;           // reduce kernels read landed host chunks themselves (HYLINK_PCIE_FUSE_LANDING)
-  std::atomic<uint64_t> fused_slices_{0}, folded_sources_{0};
+  std::atomic<uint64_t> fused_slices_{0}, folded_sources_{0}, range_jobs_{0};
   std::vector<size_t> host_map_bytes_;
   std::vector<bool> host_registered_, host_cuda_alloc_;
   size_t host_bytes_ = 0;        // size of every pool
@@ -416,14 +417,16 @@ hlResult_t PcieImpl::getPlan(const std::string& collective, const std::string& f
       if (bs_->singleProcess()) path = ir::findProgramFile(file_coll, pattern, "direct", "");
       else HL_DBG("topology allows %s_%s_direct.xml, but ranks are processes: host-relay schedule", file_coll.c_str(), pattern.c_str());
     }
-    if (path.empty() && small) path = ir::findProgramFile(file_coll, pattern, "small", "");
-    if (path.empty()) path = ir::findProgramFile(file_coll, pattern, "", "");
+    // A named variant (HYLINK_IR_VARIANT, e.g. host_reduce or single_d2h) comes from its own file, else from the generator.
+    const std::string variant = envStr({"HYLINK_IR_VARIANT"}, "");
+    if (path.empty() && !variant.empty()) path = ir::findProgramFile(file_coll, pattern, variant, "");
+    if (path.empty() && variant.empty() && small) path = ir::findProgramFile(file_coll, pattern, "small", "");
+    if (path.empty() && variant.empty()) path = ir::findProgramFile(file_coll, pattern, "", "");
     if (!path.empty()) {
       hlResult_t r = ir::loadProgramFile(path, &plan->program);
       if (r != hlSuccess) return r;
       plan->source = path;
     } else {
-      const std::string variant = envStr({"HYLINK_IR_VARIANT"}, "");
       HL_CHECK(ir::generate(collective, numa_, variant, root, &plan->program));
       plan->source = "generated";
     }
@@ -948,8 +951,36 @@ hlResult_t PcieImpl::runWork(const Work& w) {
     if (l.done == ns) --remaining;
     if (traceEnabled()) traceComplete("dma", ir::opName(g.nodes[(size_t)mine[(size_t)f.node_slot]].op), rank_, f.t0_ns, nowNs(), (long long)f.bytes);
   };
+  struct RangeRun {
+    int node_slot = -1;
+    std::shared_ptr<HostTicket> ticket;
+    uint64_t t0_ns = 0;
+    size_t bytes = 0;
+  };
+  std::vector<RangeRun> ranges;   // H2H nodes that a worker team owns (worker_pool.h: RangeJob)
+  static const bool range_jobs = envBool({"HYLINK_H2H_RANGE_JOBS"}, true);
+  static const int range_team = (int)envInt({"HYLINK_H2H_RANGE_THREADS"}, 4);
   while (remaining) {
     bool progressed = false;
+    // 1a. nodes owned by worker teams: their progress word is written by the workers
+    for (size_t ri = 0; ri < ranges.size();) {
+      RangeRun& rr = ranges[ri];
+      if (rr.ticket->failed.load()) return fail(hlInternalError, "host range job failed (a wait ran out, a peer failed, or unsupported type/op)");
+      Local& l = st[(size_t)rr.node_slot];
+      const int now_done = progressOf(g.nodes[(size_t)mine[(size_t)rr.node_slot]].id);
+      if (now_done > l.done) {
+        l.done = now_done;
+        progressed = true;
+      }
+      if (l.done >= ns && rr.ticket->done()) {
+        --remaining;
+        if (traceEnabled()) traceComplete("h2h", ir::opName(g.nodes[(size_t)mine[(size_t)rr.node_slot]].op), rank_, rr.t0_ns, nowNs(), (long long)rr.bytes);
+        ranges[ri] = std::move(ranges.back());
+        ranges.pop_back();
+        continue;
+      }
+      ++ri;
+    }
     // 1. retire finished transfers, lane by lane, in issue order
     for (int k = 0; k < kNumLaneKinds; ++k)
       for (auto& lane : lanes_[k]) {
@@ -1047,6 +1078,40 @@ hlResult_t PcieImpl::runWork(const Work& w) {
         char* src2 = n.op == ir::Op::H2HReduce ? resolve(w, n.src2, &s2len, &pending) : nullptr;
         if (pending) break;
         const size_t node_len = std::min(slen, dlen);
+        if (k == 0 && range_jobs && ns > 1 && (n.op == ir::Op::H2H || n.op == ir::Op::H2HReduce)) {
+          // The whole node goes to a team of workers that follows the inputs slice by slice and publishes the node's
+          // progress word itself; this thread only reads the word back (step 1).
+          RangeJob job;
+          job.kind = n.op == ir::Op::H2HReduce ? HostJob::Reduce : HostJob::Copy;
+          job.dst = dst;
+          job.a = src;
+          job.b = src2;
+          job.bytes = n.op == ir::Op::H2HReduce ? std::min(node_len, s2len) : node_len;
+          job.slice_bytes = geo.slice_bytes;
+          job.nslices = ns;
+          job.dtype = w.dtype;
+          job.op = w.op;
+          job.non_temporal = true;
+          job.numa = n.dst.space == ir::Buf::Host ? n.dst.owner : numa_[(size_t)rank_];
+          job.team = range_team;
+          job.out = &shared_->progress[n.id];
+          for (int d : n.wait_for) job.deps.push_back(&shared_->progress[d]);
+          job.seq = w.seq;
+          job.seq_shift = kSeqShift;
+          job.abort = &shared_->failed;
+          job.deadline_ns = t0 + limit;
+          RangeRun rr;
+          rr.node_slot = (int)i;
+          rr.ticket = std::make_shared<HostTicket>();
+          rr.t0_ns = nowNs();
+          rr.bytes = job.bytes;
+          pool_->submitRange(job, rr.ticket);
+          ranges.push_back(std::move(rr));
+          range_jobs_++;
+          l.issued = ns;
+          progressed = true;
+          break;
+        }
         const size_t off = (size_t)k * geo.slice_bytes;
         const size_t len = off >= node_len ? 0 : std::min(geo.slice_bytes, node_len - off);
         {
@@ -1214,6 +1279,7 @@ hlResult_t PciePath::lastResult() const { return impl_->lastResult(); }
 uint64_t PciePath::kernelLaunches() const { return impl_->kernelLaunches(); }
 uint64_t PciePath::copyOps() const { return impl_->copyOps(); }
 uint64_t PciePath::fusedSlices() const { return impl_->fusedSlices(); }
+uint64_t PciePath::rangeJobs() const { return impl_->rangeJobs(); }
 uint64_t PciePath::smallCalls() const { return impl_->smallCalls(); }
 uint64_t PciePath::foldedSources() const { return impl_->foldedSources(); }
 const std::vector<int>& PciePath::rankNuma() const { return impl_->rankNuma(); }

@@ -49,6 +49,7 @@ class PciePath {
   uint64_t kernelLaunches() const;
   uint64_t copyOps() const;
   uint64_t fusedSlices() const;
+  uint64_t rangeJobs() const;   // H2H nodes handed to worker teams as a whole
   uint64_t smallCalls() const;
   uint64_t foldedSources() const;
   // Logical NUMA node of every rank.

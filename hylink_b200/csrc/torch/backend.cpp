@@ -504,6 +504,7 @@ class HylinkBackend : public c10d::Backend {
       d["folded_sources"] = st.folded_sources;
       d["registered_bytes"] = st.registered_bytes;
       d["small_path_calls"] = st.small_path_calls;
+      d["h2h_range_jobs"] = st.h2h_range_jobs;
     }
     return d;
   }

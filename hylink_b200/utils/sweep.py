@@ -67,6 +67,7 @@ def main(argv=None) -> int:
     ap.add_argument("--blocks", dest="max_blocks", type=int, default=0)
     ap.add_argument("--deterministic", action="store_true")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--registered", action="store_true", help="buffers from the library's registered memory (zero-copy kernels)")
     ap.add_argument("--out", default="")
     a = ap.parse_args(argv)
 
@@ -98,8 +99,13 @@ def main(argv=None) -> int:
             dt = DT[dname]
             es = torch.empty((), dtype=dt).element_size()
             # `size` is the nccl-tests message size: AR total bytes; RS/AG/A2A the FULL buffer (n segments)
-            pool_in = torch.empty(pool_bytes // es, dtype=dt, device="cuda")
-            pool_out = torch.empty(pool_bytes // es, dtype=dt, device="cuda")
+            pool_in = pool_out = want = got = None   # registered memory is handed out in call order: release before asking again
+            if a.registered:
+                pool_in = comm.alloc_registered(pool_bytes // es, dt)
+                pool_out = comm.alloc_registered(pool_bytes // es, dt)
+            else:
+                pool_in = torch.empty(pool_bytes // es, dtype=dt, device="cuda")
+                pool_out = torch.empty(pool_bytes // es, dtype=dt, device="cuda")
             if dt.is_floating_point:
                 pool_in.copy_((torch.rand(pool_in.numel(), device="cuda") * 2 - 1) if coll == "allreduce"
                               else torch.randn(pool_in.numel(), device="cuda"))
@@ -167,7 +173,10 @@ def main(argv=None) -> int:
                        "busbw_GBs": round(nbytes / t_ours / 1e6 * f, 2),
                        "nccl_ms": round(t_ref, 5) if t_ref else None,
                        "nccl_busbw_GBs": round(nbytes / t_ref / 1e6 * f, 2) if t_ref else None,
-                       "speedup": round(t_ref / t_ours, 3) if t_ref else None, "ok": ok, "algo": a.algo, "path": a.path}
+                       "speedup": round(t_ref / t_ours, 3) if t_ref else None, "ok": ok, "algo": a.algo, "path": a.path,
+                       "registered": bool(a.registered)}
+                if a.path in ("split", "auto"):
+                    rec["pcie_share"] = round(float(comm.stats()["last_alpha"]), 4)   # share of the bytes the PCIe path carried in the latest call
                 if rank == 0:
                     line = json.dumps(rec)
                     print(line, flush=True)

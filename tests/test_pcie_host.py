@@ -349,3 +349,34 @@ def _many_rounds_worker(rank, n, uid):
 def test_rounds_without_a_barrier_between_them(n, numa):
     env = dict(SMALL_POOLS, HYLINK_HOST_BUFFER_SIZE="2M", HYLINK_INTERNAL_BUFFER_BYTES="1M", HYLINK_GPU_NUMA_MAP=numa)
     run_ranks(_many_rounds_worker, n, env=env, timeout=300)
+
+
+def _range_job_worker(rank, n, uid, variant):
+    c = _comm(rank, n, uid)
+    count = 1 << 20                                      # 4 MiB of fp32: several slices per chunk
+    x = _data(rank, count, torch.float32, seed=7)
+    out = torch.zeros(count)
+    c.all_reduce(x, out)
+    seg = count // n
+    full = torch.zeros(count)
+    c.all_gather(x[:seg], full)
+    c.drain()
+    ref = sum(_data(r, count, torch.float32, seed=7).double() for r in range(n))
+    assert torch.allclose(out.double(), ref, atol=1e-5)
+    assert torch.equal(full, torch.cat([_data(r, count, torch.float32, seed=7)[:seg] for r in range(n)]))
+    st = c.stats()
+    c.close()
+    return st["h2h_range_jobs"]
+
+
+@pytest.mark.parametrize("workers", ["1", "3"])
+def test_h2h_nodes_run_as_worker_owned_ranges(workers):
+    """The host_reduce schedules fold on the CPU (H2HReduce chains): those nodes are handed to worker teams as whole
+    nodes that follow their inputs slice by slice. One worker per pool is the hard case: the same worker must also
+    run the plain copies the range waits for."""
+    env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP="0011", HYLINK_H2H_WORKERS=workers, HYLINK_IR_VARIANT="host_reduce")
+    jobs = run_ranks(_range_job_worker, 4, "host_reduce", env=env, timeout=300)
+    assert all(j > 0 for j in (jobs.values() if isinstance(jobs, dict) else jobs))
+    env["HYLINK_H2H_RANGE_JOBS"] = "0"
+    jobs = run_ranks(_range_job_worker, 4, "host_reduce", env=env, timeout=300)
+    assert all(j == 0 for j in (jobs.values() if isinstance(jobs, dict) else jobs))
