@@ -56,7 +56,7 @@ class CommStats(C.Structure):
                 ("kernel_launches", C.c_uint64), ("copy_engine_ops", C.c_uint64), ("last_alpha", C.c_double),
                 ("last_fast_ms", C.c_double), ("last_pcie_ms", C.c_double), ("nvls", C.c_int), ("symm_mode", C.c_int),
                 ("fused_landing_slices", C.c_uint64), ("folded_sources", C.c_uint64), ("registered_bytes", C.c_uint64), ("small_path_calls", C.c_uint64),
-                ("h2h_range_jobs", C.c_uint64)]
+                ("h2h_range_jobs", C.c_uint64), ("composed_allreduces", C.c_uint64)]
 
 
 def _sig(name, restype, *argtypes):

@@ -32,9 +32,13 @@ template <typename F> F next(const char* name) {
   return reinterpret_cast<F>(dlsym(RTLD_NEXT, name));
 }
 thread_local int g_depth = 0;
+std::atomic<unsigned long long> g_drains{0};
 struct Guard {
   Guard() {
-    if (active() && g_depth++ == 0) hlDrainAllExecutors();
+    if (active() && g_depth++ == 0) {
+      hlDrainAllExecutors();
+      g_drains.fetch_add(1, std::memory_order_relaxed);
+    }
   }
   ~Guard() {
     if (active()) --g_depth;
@@ -43,6 +47,9 @@ struct Guard {
 }  // namespace
 
 extern "C" {
+
+// How often a blocking call drained the executors first (0 while the shim is not active).
+__attribute__((visibility("default"))) unsigned long long hlBlockShimDrains(void) { return g_drains.load(std::memory_order_relaxed); }
 
 __attribute__((visibility("default"))) cudaError_t cudaStreamSynchronize(cudaStream_t s) {
   static auto fn = next<cudaError_t (*)(cudaStream_t)>("cudaStreamSynchronize");

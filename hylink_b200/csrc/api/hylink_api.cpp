@@ -608,6 +608,7 @@ hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out) {
   out->registered_bytes = comm->nvl ? comm->nvl->heapInUse() : 0;
   out->small_path_calls = comm->pcie ? comm->pcie->smallCalls() : 0;
   out->h2h_range_jobs = comm->pcie ? comm->pcie->rangeJobs() : 0;
+  out->composed_allreduces = comm->pcie ? comm->pcie->composedAllReduces() : 0;
   if (comm->orch) comm->orch->fillStats(out);
   return hlSuccess;
 }

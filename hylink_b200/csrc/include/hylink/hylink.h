@@ -194,6 +194,7 @@ typedef struct {
   uint64_t registered_bytes;  /* bytes handed out from the registered-memory heap */
   uint64_t small_path_calls;  /* PCIe path: collectives served by the stream-ordered small-message path (no CPU thread) */
   uint64_t h2h_range_jobs;    /* PCIe path: host-to-host nodes handed to a worker team as a whole (worker-side progress) */
+  uint64_t composed_allreduces; /* PCIe path: all-reduces run as reduce-scatter + in-place all-gather (HYLINK_PCIE_AR_COMPOSE=1) */
 } hlCommStats;
 hlResult_t hlCommGetStats(hlComm_t comm, hlCommStats* out);
 /* Serialises the tuned (op-key -> alpha, bandwidth) table as JSON into buf;

@@ -356,7 +356,16 @@ int NvlPath::zeroCopyFlavour(const NvlCall& c, int coll, size_t wire_bytes) cons
   const int pref = reduce ? reduce_pref : gather_pref;
   if (!mc_ok || pref == 0) return 2;
   if (pref == 1) return 1;
-  if (coll != 0 || nranks_ < Config::get().nvls_min_ranks) return 2;
+  if (nranks_ < Config::get().nvls_min_ranks) return 2;
+  if (coll == 1) {
+    // Reduce-scatter: one multimem.ld_reduce per packet instead of a load from every peer is the shorter chain while
+    // latency decides (4 GPUs, whole input 2 / 4 / 16 MiB: 59 / 109 / 267 GB/s through the switch, 54 / 100 / 265
+    // with peer loads); from 32 MiB on the switch flavour is bound by outbound traffic (every GPU sends its whole
+    // input, its own segment included) and peer loads win (1 GiB: 522 against 638 GB/s).
+    static const long long rs_nvls_max = envInt({"HYLINK_ZC_RS_NVLS_MAX"}, 32LL << 20);
+    return wire_bytes < (size_t)rs_nvls_max ? 1 : 2;
+  }
+  if (coll != 0) return 2;
   // A call with a CTA budget shares the GPU with compute kernels (gradient buckets under a backward pass): the
   // switch does the adding and every byte crosses this GPU's memory system once, which needs the fewest SMs
   // (GPT-2-medium DDP on 4 GPUs, 25 MB buckets, 32 CTAs: 54.45 ms per step through the switch, 54.62 with peer

@@ -232,6 +232,12 @@ hlResult_t PcieImpl::init() {
     HL_CUDA(cudaHostGetDevicePointer((void**)&door_dev_, h, 0));
     const CudaDriver* drv = CudaDriver::get();
     stream_mem_ops_ = drv && !cfg.disable_stream_mem_ops;
+    // The executor drives many streams from the CPU while a user stream sits parked on a stream-memory wait: with
+    // a single hardware connection the copies queue up behind that wait and nothing moves
+    // (pcie-ccl-cuda/README.md:665 asks for 8).
+    const long long conns = envInt({"CUDA_DEVICE_MAX_CONNECTIONS"}, 8);
+    if (conns < 8 && rank_ == 0)
+      HL_WARN("CUDA_DEVICE_MAX_CONNECTIONS=%lld: the PCIe path needs independent hardware queues for its copy streams; use 8 or more", conns);
     int lo = 0, hi = 0;
     HL_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     lanes_per_dir_ = kMaxDmaLanes;   // all created once; each collective uses as many as the lane policy says
@@ -1254,8 +1260,28 @@ hlResult_t PciePath::create(Bootstrap* bs, int device, void* ctrl_area, PciePath
 }
 
 hlResult_t PciePath::allReduce(const void* send, void* recv, size_t count, hlDataType_t t, hlRedOp_t op, float scale, hlStream_t stream) {
+  // Optional composition (HYLINK_PCIE_AR_COMPOSE=1): an out-of-place all-reduce whose count divides by the rank count
+  // runs as reduce-scatter into this rank's slot of the output followed by an in-place all-gather, the way
+  // pcie-ccl-ascend/src/api/pccl_api.cpp:572-607 does. Off by default: the all-reduce schedules here already are a
+  // reduce-scatter phase and a gather phase in ONE graph, without the barrier between two messages.
+  static const bool compose = envBool({"HYLINK_PCIE_AR_COMPOSE", "PCCL_ALLREDUCE_RS_AG"}, false);
+  const size_t es = hlTypeSize(t);
+  const int n = impl_->n_;
+  if (compose && es && n > 1 && count % (size_t)n == 0 && count >= (size_t)n) {
+    const size_t seg = count / (size_t)n, bytes = count * es;
+    const char* s = (const char*)send;
+    char* r = (char*)recv;
+    const bool disjoint = s + bytes <= r || r + bytes <= s;
+    if (disjoint) {
+      char* slot = r + (size_t)impl_->rank_ * seg * es;
+      HL_CHECK(impl_->submit("reducescatter", "", send, slot, seg, 0, n, 1, t, op, scale, 0, stream));
+      composed_.fetch_add(1, std::memory_order_relaxed);
+      return impl_->submit("allgather", "", slot, recv, seg, 0, 1, n, t, hlSum, 1.0f, 0, stream);
+    }
+  }
   return impl_->submit("allreduce", "", send, recv, count, 0, 1, 1, t, op, scale, 0, stream);
 }
+uint64_t PciePath::composedAllReduces() const { return composed_.load(); }
 hlResult_t PciePath::reduceScatter(const void* send, void* recv, size_t seg_count, size_t stride, hlDataType_t t, hlRedOp_t op,
                                    float scale, hlStream_t stream) {
   return impl_->submit("reducescatter", "", send, recv, seg_count, stride, impl_->n_, 1, t, op, scale, 0, stream);

@@ -1,6 +1,7 @@
 // PCIe path facade: host-staged collectives driven by the schedule IR.
 // See pcie/pcie_path.cpp for the design notes.
 #pragma once
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <vector>
@@ -52,6 +53,7 @@ class PciePath {
   uint64_t rangeJobs() const;   // H2H nodes handed to worker teams as a whole
   uint64_t smallCalls() const;
   uint64_t foldedSources() const;
+  uint64_t composedAllReduces() const;   // all-reduces run as reduce-scatter + in-place all-gather (HYLINK_PCIE_AR_COMPOSE)
   // Logical NUMA node of every rank.
   const std::vector<int>& rankNuma() const;
   PcieImpl* impl() { return impl_; }
@@ -59,6 +61,7 @@ class PciePath {
  private:
   PciePath() = default;
   PcieImpl* impl_ = nullptr;
+  std::atomic<uint64_t> composed_{0};
 };
 
 }  // namespace hl

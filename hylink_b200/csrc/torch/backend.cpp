@@ -505,6 +505,7 @@ class HylinkBackend : public c10d::Backend {
       d["registered_bytes"] = st.registered_bytes;
       d["small_path_calls"] = st.small_path_calls;
       d["h2h_range_jobs"] = st.h2h_range_jobs;
+      d["composed_allreduces"] = st.composed_allreduces;
     }
     return d;
   }

@@ -186,7 +186,16 @@ def main(argv=None) -> int:
                 results.append(rec)
             del pool_in, pool_out
     if rank == 0:
-        print(json.dumps({"event": "done", "failures": failures, "stats": comm.stats()}), flush=True)
+        done = {"event": "done", "failures": failures, "stats": comm.stats()}
+        try:   # present when the interposers of blocking CUDA calls are preloaded (libhylink_cudashim.so)
+            import ctypes
+
+            fn = ctypes.CDLL(None).hlBlockShimDrains
+            fn.restype = ctypes.c_ulonglong
+            done["block_shim_drains"] = int(fn())
+        except (AttributeError, OSError):
+            pass
+        print(json.dumps(done), flush=True)
     dist.barrier()
     comm.close()
     dist.destroy_process_group()

@@ -45,6 +45,22 @@ def test_pcie_path_alone_is_correct():
     assert '"small_path_calls": 0' not in out
 
 
+def test_blocking_cuda_calls_drain_the_executors_first():
+    """The interposers of host-blocking CUDA calls, preloaded and switched on, under a program that synchronises and
+    reads results back between PCIe-path collectives (the pattern of the reference's deadlock_repro.py)."""
+    shim = os.path.join(ROOT, "hylink_b200", "lib", "libhylink_cudashim.so")
+    assert os.path.exists(shim), "libhylink_cudashim.so is not built"
+    env = {"HYLINK_PCIE_ENABLE": "1", "HYLINK_HOST_BUFFER_SIZE": "256M", "HYLINK_INTERNAL_BUFFER_BYTES": "128M",
+           "LD_PRELOAD": shim, "HYLINK_CUDA_BLOCK_SHIM": "1"}
+    out = _torchrun(2, ["-m", "hylink_b200.utils.sweep", "--bytes-from", "256K", "--bytes-to", "16M", "--factor", "8", "--check",
+                        "--colls", "allreduce,allgather", "--dtypes", "fp32", "--iters", "3", "--path", "pcie", "--no-nccl"], env=env)
+    assert '"failures": 0' in out, out[-3000:]
+    import json
+
+    done = [json.loads(l) for l in out.splitlines() if l.startswith('{"event": "done"')][0]
+    assert done.get("block_shim_drains", 0) > 0, done
+
+
 def test_forked_collectives_are_correct_and_retune():
     """Every collective forked over NVLink kernels + PCIe schedules, with the feedback controller running."""
     env = {"HYLINK_ORCH_ENABLE": "1", "HYLINK_MIN_MSG_SIZE": "1M", "HYLINK_MIN_MSG_SIZE_8": "1M",

@@ -380,3 +380,39 @@ def test_h2h_nodes_run_as_worker_owned_ranges(workers):
     env["HYLINK_H2H_RANGE_JOBS"] = "0"
     jobs = run_ranks(_range_job_worker, 4, "host_reduce", env=env, timeout=300)
     assert all(j == 0 for j in (jobs.values() if isinstance(jobs, dict) else jobs))
+
+
+def _composed_worker(rank, n, uid):
+    c = _comm(rank, n, uid)
+    count = n * 30001                                    # divisible by the rank count, odd segment length
+    x = _data(rank, count, torch.float32, seed=11)
+    out = torch.zeros(count)
+    c.all_reduce(x, out, op="avg")
+    inplace = x.clone()
+    c.all_reduce(inplace, inplace)                       # in place: never composed
+    odd = torch.zeros(count + 1)
+    longer = torch.cat([x, x[:1]])                       # the call is asynchronous: inputs must outlive it
+    c.all_reduce(longer, odd)                            # count not divisible: never composed
+    c.drain()
+    ref = sum(_data(r, count, torch.float32, seed=11).double() for r in range(n))
+    assert torch.allclose(out.double(), ref / n, atol=1e-5)
+    assert torch.allclose(inplace.double(), ref, atol=1e-5)
+    assert torch.allclose(odd[:count].double(), ref, atol=1e-5)
+    st = c.stats()
+    c.close()
+    return st["composed_allreduces"]
+
+
+@pytest.mark.parametrize("n,numa", [(2, "00"), (4, "0011")])
+def test_allreduce_composed_of_reduce_scatter_and_all_gather(n, numa):
+    env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP=numa, HYLINK_PCIE_AR_COMPOSE="1")
+    res = run_ranks(_composed_worker, n, env=env, timeout=300)
+    assert all(v == 1 for v in (res.values() if isinstance(res, dict) else res))
+
+
+@pytest.mark.parametrize("n,numa", [(2, "00"), (4, "0011")])
+def test_allreduce_fp16(n, numa):
+    """fp16 through every node type (the reference carries an unresolved fp16 hang repro, tests/dev/repro_fp16_allreduce.cpp)."""
+    env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP=numa)
+    run_ranks(_allreduce_worker, n, 3 << 18, "float16", False, env=env)
+    run_ranks(_allreduce_worker, n, 100003, "float16", True, env=dict(env, HYLINK_IR_VARIANT="host_reduce"))
