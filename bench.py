@@ -163,8 +163,23 @@ class Table:
             # the library's allocator (hylink_b200.parallel.symmetric_empty): registered memory, collectives run zero-copy
             from hylink_b200.parallel import symmetric_empty
 
-            self.inp = [symmetric_empty(top // self.es, dtype) for _ in range(self.slots)]
-            self.out = [symmetric_empty(top // self.es, dtype) for _ in range(self.slots)]
+            import torch.distributed as dist
+
+            try:
+                self.inp = [symmetric_empty(top // self.es, dtype) for _ in range(self.slots)]
+                self.out = [symmetric_empty(top // self.es, dtype) for _ in range(self.slots)]
+                ok = 1
+            except RuntimeError as e:   # no registered heap on this machine (no peer mapping, out of address space ...)
+                print(f"[bench] registered memory unavailable on rank {dist.get_rank()}: {e}", file=sys.stderr, flush=True)
+                self.inp = self.out = None
+                ok = 0
+            # all ranks use registered buffers or none does: the buffers must sit at the same heap offset everywhere
+            agree = torch.tensor([ok], device="cuda", dtype=torch.int32)
+            dist.all_reduce(agree, op=dist.ReduceOp.MIN, group=group)
+            if int(agree.item()) == 0:
+                self.inp = self.out = None
+                self.registered = False
+        if self.registered:
             for t in self.inp:
                 t.copy_((torch.rand(top // self.es, device="cuda") * 2 - 1).to(dtype))
         else:
@@ -408,6 +423,7 @@ def main() -> int:
     sizes = size_list(parse_size(args.lo), parse_size(args.hi))
     registered = backend == "hylink" and not args.unregistered and world > 1
     tab = Table(dtype, sizes, world, registered=registered)
+    registered = tab.registered   # False when the machine could not provide registered memory
 
     def stats():
         if backend != "hylink":

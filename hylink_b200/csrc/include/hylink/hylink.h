@@ -73,7 +73,8 @@ typedef enum {
   hlAlgoPush = 5,        /* peer stores only: push shards to their owner, fold locally, push results */
   hlAlgoZeroCopy = 6,    /* registered (hlMemAlloc) buffers read and written in place on every rank; refused for others */
   hlAlgoZeroCopyNvls = 7,/* ... through NVSwitch (multimem) */
-  hlAlgoZeroCopyP2p = 8  /* ... with plain peer loads and stores, fixed sum order */
+  hlAlgoZeroCopyP2p = 8, /* ... with plain peer loads and stores, fixed sum order */
+  hlAlgoLowLatency = 9   /* small messages: every 16-byte store carries its arrival flag, no cross-GPU barrier; fixed sum order */
 } hlAlgo_t;
 
 #define HL_UNIQUE_ID_BYTES 128

@@ -12,6 +12,8 @@ namespace nvl {
 // nranks picks the variant of the kernels that are compiled per rank-count class (<= 2, <= 4, <= 8).
 const void* kernelFor(int kind, int wire_dt, int nranks = HL_MAX_RANKS);
 const char* kernelName(int kind);
+// The barrier-free small-message kernels live in a file of their own (nvl_ll_kernels.cu).
+const void* lowLatencyKernelFor(int kind, int wire_dt);
 // emu_ranks > 1: cooperative launch with one grid row per emulated rank.
 hlResult_t launch(int kind, int wire_dt, const HlCommDev* dcomms, const HlEmuCalls& calls, int emu_ranks, int blocks,
                   cudaStream_t stream, int nranks = HL_MAX_RANKS);

@@ -12,6 +12,15 @@ static constexpr size_t kZcArgBytes = (size_t)HL_MAX_RANKS * 2 * sizeof(uint64_t
 
 static size_t flagAreaBytes() { return (kFlagBytes + kZcArgBytes + 4095) & ~(size_t)4095; }
 
+// Low-latency region behind the flag area: [2 parities][2 phases][HL_MAX_RANKS sources] slots (nvl_ll_kernels.cu).
+static constexpr size_t kLlSlots = 2 * 2 * HL_MAX_RANKS;
+static size_t llSlotBytesFromEnv(bool emu) {
+  static const long long v = envInt({"HYLINK_LL_SLOT_BYTES"}, 4LL << 20);   // 0: no low-latency kernels
+  size_t s = v <= 0 ? 0 : ((size_t)v + 4095) & ~(size_t)4095;
+  if (emu && s > ((size_t)1 << 20)) s = (size_t)1 << 20;   // emulated groups (tests) hold nranks regions on one GPU
+  return s;
+}
+
 NvlPath::~NvlPath() {
   if (device_ >= 0) cudaSetDevice(device_);
   cudaDeviceSynchronize();
@@ -60,6 +69,11 @@ hlResult_t NvlPath::finishInit(int timeout_ms) {
       c.stage[q] = base;
       c.flags[q] = (uint64_t*)(base + stage_bytes_);
     }
+    for (int q = 0; q < nranks_ && ll_slot_bytes_; ++q) {
+      uint8_t* base = (uint8_t*)(emu_ ? emu_mem_[q] : region_.ptr[q]);
+      c.ll[q] = base + stage_bytes_ + flagAreaBytes();
+    }
+    c.ll_slot_bytes = ll_slot_bytes_;
     c.mc_stage = emu_ ? nullptr : (uint8_t*)region_.mc;
     c.status = status_dev + 8 * i;
     c.abort_word = abort_dev_ + 16 * i;
@@ -86,10 +100,11 @@ hlResult_t NvlPath::createReal(Bootstrap* bs, int device, NvlPath** out) {
   p->device_ = device;
   p->stage_bytes_ = (cfg.symm_stage_bytes + 4095) & ~(size_t)4095;
   HL_CUDA(cudaSetDevice(device));
-  HL_CHECK(symmAlloc(bs, device, p->stage_bytes_ + flagAreaBytes(), cfg.nvls, cfg.symm_mode, &p->region_));
+  p->ll_slot_bytes_ = p->nranks_ > 1 ? llSlotBytesFromEnv(false) : 0;
+  HL_CHECK(symmAlloc(bs, device, p->stage_bytes_ + flagAreaBytes() + kLlSlots * p->ll_slot_bytes_, cfg.nvls, cfg.symm_mode, &p->region_));
   p->has_mc_ = p->region_.mc != nullptr;
-  // flags start at zero on every rank before anybody launches
-  HL_CUDA(cudaMemset((uint8_t*)p->region_.ptr[p->rank_] + p->stage_bytes_, 0, flagAreaBytes()));
+  // flags (and the tags of the low-latency region) start at zero on every rank before anybody launches
+  HL_CUDA(cudaMemset((uint8_t*)p->region_.ptr[p->rank_] + p->stage_bytes_, 0, flagAreaBytes() + kLlSlots * p->ll_slot_bytes_));
   HL_CUDA(cudaDeviceSynchronize());
   HL_CHECK(p->finishInit(cfg.nvl_timeout_ms));
   HL_CHECK(bs->barrier(kBarSymm));
@@ -108,9 +123,10 @@ hlResult_t NvlPath::createEmu(int nranks, int device, size_t stage_bytes, int ti
   p->device_ = device;
   p->stage_bytes_ = (stage_bytes + 4095) & ~(size_t)4095;
   HL_CUDA(cudaSetDevice(device));
+  p->ll_slot_bytes_ = nranks > 1 ? llSlotBytesFromEnv(true) : 0;
   for (int q = 0; q < nranks; ++q) {
-    HL_CUDA(cudaMalloc(&p->emu_mem_[q], p->stage_bytes_ + flagAreaBytes()));
-    HL_CUDA(cudaMemset((uint8_t*)p->emu_mem_[q] + p->stage_bytes_, 0, flagAreaBytes()));
+    HL_CUDA(cudaMalloc(&p->emu_mem_[q], p->stage_bytes_ + flagAreaBytes() + kLlSlots * p->ll_slot_bytes_));
+    HL_CUDA(cudaMemset((uint8_t*)p->emu_mem_[q] + p->stage_bytes_, 0, flagAreaBytes() + kLlSlots * p->ll_slot_bytes_));
   }
   HL_CHECK(p->finishInit(timeout_ms));
   *out = p.release();
@@ -130,9 +146,9 @@ hlResult_t NvlPath::resetAfterError() {
   const int nl = localRanks();
   if (!emu_ && bs_) HL_CHECK(bs_->barrier(kBarSymm));
   if (emu_) {
-    for (int q = 0; q < nranks_; ++q) HL_CUDA(cudaMemset((uint8_t*)emu_mem_[q] + stage_bytes_, 0, flagAreaBytes()));
+    for (int q = 0; q < nranks_; ++q) HL_CUDA(cudaMemset((uint8_t*)emu_mem_[q] + stage_bytes_, 0, flagAreaBytes() + kLlSlots * ll_slot_bytes_));
   } else {
-    HL_CUDA(cudaMemset((uint8_t*)region_.ptr[rank_] + stage_bytes_, 0, flagAreaBytes()));
+    HL_CUDA(cudaMemset((uint8_t*)region_.ptr[rank_] + stage_bytes_, 0, flagAreaBytes() + kLlSlots * ll_slot_bytes_));
   }
   HL_CUDA(cudaMemset(abort_dev_, 0, sizeof(uint32_t) * 16 * nl));
   HL_CUDA(cudaMemset(seq_dev_, 0, sizeof(uint64_t) * 8 * nl));
@@ -535,11 +551,103 @@ hlResult_t NvlPath::launchSliced(int kind, const NvlBufs& b, const NvlCall& c, b
   return hlSuccess;
 }
 
+// ---- barrier-free small-message kernels ------------------------------------------------------------------------
+static bool disjoint(const void* a, size_t na, const void* b, size_t nb) {
+  const char* x = (const char*)a;
+  const char* y = (const char*)b;
+  return x + na <= y || y + nb <= x;
+}
+
+int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size_t wire_bytes) const {
+  const bool asked = c.algo == hlAlgoLowLatency;
+  if (!asked && c.algo != hlAlgoAuto) return 0;
+  const int no = asked ? -1 : 0;
+  if (!ll_slot_bytes_ || nranks_ < 2) return no;
+  if (!asked) {
+    // Measured on 4 GPUs (device time between two events, bf16): the barrier-based kernels spend 10 to 20 us in their
+    // two flag rounds whatever the size; flagged packets halve the link rate instead, which is the better deal up to
+    // a few MiB.
+    static const long long ar_max = envInt({"HYLINK_LL_AR_MAX"}, 2LL << 20), rs_max = envInt({"HYLINK_LL_RS_MAX"}, 4LL << 20),
+                           ag_max = envInt({"HYLINK_LL_AG_MAX"}, 4LL << 20);
+    const long long lim = coll == 0 ? ar_max : (coll == 1 ? rs_max : ag_max);
+    if ((long long)wire_bytes > lim) return 0;
+  }
+  if (c.in_dt != c.wire_dt || c.out_dt != c.wire_dt) return no;
+  const uint64_t ws = hlTypeSize((hlDataType_t)c.wire_dt);
+  if (!ws) return no;
+  const uint64_t epp = 16 / ws;
+  const uint64_t istride = c.in_seg_stride ? c.in_seg_stride : c.count, ostride = c.out_seg_stride ? c.out_seg_stride : c.count;
+  if (c.count % epp || (coll == 1 && istride % epp) || (coll == 2 && ostride % epp)) return no;
+  const uint64_t np = c.count / epp;
+  const uint64_t per_src = coll == 0 ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;   // packets one rank sends to one peer
+  if (per_src * 32 > ll_slot_bytes_) return no;
+  const size_t n = (size_t)nranks_;
+  for (int i = 0; i < localRanks(); ++i) {
+    const char* in = (const char*)b.in[i];
+    const char* out = (const char*)b.out[i];
+    if (!in || !out || (((uintptr_t)in | (uintptr_t)out) & 15)) return no;
+    // in place only where every location is read by the thread that later overwrites it
+    if (coll == 0) {
+      if (in != out && !disjoint(in, c.count * ws, out, c.count * ws)) return no;
+    } else if (coll == 1) {
+      const size_t in_bytes = ((n - 1) * istride + c.count) * ws;
+      bool slot = false;
+      for (size_t q = 0; q < n; ++q) slot = slot || out == in + q * istride * ws;
+      if (!slot && !disjoint(in, in_bytes, out, c.count * ws)) return no;
+    } else {
+      const size_t out_bytes = ((n - 1) * ostride + c.count) * ws;
+      bool slot = false;
+      for (size_t q = 0; q < n; ++q) slot = slot || in == out + q * ostride * ws;
+      if (!slot && !disjoint(in, c.count * ws, out, out_bytes)) return no;
+    }
+  }
+  return 1;
+}
+
+hlResult_t NvlPath::launchLowLatency(int kind, const NvlBufs& b, const NvlCall& c, uint64_t packets, cudaStream_t s) {
+  HL_CUDA(cudaSetDevice(device_));
+  HL_CHECK(orderAfterPrevious(s));
+  const int nl = localRanks();
+  HlEmuCalls calls;
+  memset(&calls, 0, sizeof(calls));
+  for (int i = 0; i < nl; ++i) {
+    HlCallArgs& a = calls.c[i];
+    a.in = b.in[i];
+    a.out = b.out[i];
+    a.count = c.count;
+    a.in_seg_stride = c.in_seg_stride ? c.in_seg_stride : c.count;
+    a.out_seg_stride = c.out_seg_stride ? c.out_seg_stride : c.count;
+    a.scale = (c.scale == 0.0f ? 1.0f : c.scale) * (c.op == hlAvg ? 1.0f / (float)nranks_ : 1.0f);
+    a.op = c.op;
+    a.in_dt = c.in_dt;
+    a.out_dt = c.out_dt;
+    a.int_div = (c.op == hlAvg) ? nranks_ : 0;
+    a.kind = kind;
+  }
+  // one thread per packet it sends to (and receives from) every peer; at most one CTA per SM, so that the CTAs
+  // with the same index are resident on every rank at the same time (they wait for one another's packets)
+  int cap = c.max_blocks > 0 ? std::min(c.max_blocks, 148) : 148;
+  if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));
+  const uint64_t want = std::max<uint64_t>(1, (packets + HL_NVL_THREADS - 1) / HL_NVL_THREADS);
+  const int blocks = (int)std::min<uint64_t>(want, (uint64_t)cap);
+  HL_CHECK(nvl::launch(kind, c.wire_dt, dcomm_, calls, emu_ ? emu_active_ : 1, blocks, s, nranks_));
+  ++launches_;
+  return hlSuccess;
+}
+
 static bool wantsZeroCopy(int algo) { return algo == hlAlgoZeroCopy || algo == hlAlgoZeroCopyNvls || algo == hlAlgoZeroCopyP2p; }
 
 hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
+  {
+    const int ll = lowLatencyChoice(b, c, 0, wire_bytes);
+    if (ll < 0) return fail(hlUnsupported, "all-reduce: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
+    if (ll > 0) {
+      const uint64_t np = wire_bytes / 16;
+      return launchLowLatency(kNvlLlAllReduce, b, c, (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_, s);
+    }
+  }
   {
     uint64_t io, oo;
     const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 0, wire_bytes) : 0;
@@ -576,6 +684,11 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
   if (c.count == 0) return hlSuccess;
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
   {
+    const int ll = lowLatencyChoice(b, c, 1, wire_bytes);
+    if (ll < 0) return fail(hlUnsupported, "reduce-scatter: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
+    if (ll > 0) return launchLowLatency(kNvlLlReduceScatter, b, c, wire_bytes / (size_t)nranks_ / 16, s);
+  }
+  {
     uint64_t io, oo;
     const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 1, wire_bytes) : 0;
     const uint64_t stride = c.in_seg_stride ? c.in_seg_stride : c.count;
@@ -601,6 +714,12 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
 
 hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
+  {
+    const size_t seg_wire = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
+    const int ll = lowLatencyChoice(b, c, 2, seg_wire * (size_t)nranks_);
+    if (ll < 0) return fail(hlUnsupported, "all-gather: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
+    if (ll > 0) return launchLowLatency(kNvlLlAllGather, b, c, seg_wire / 16, s);
+  }
   {
     uint64_t io, oo;
     const int zc = nranks_ > 1 ? zeroCopyFlavour(c, 2, 0) : 0;

@@ -104,12 +104,17 @@ class NvlPath {
                         uint64_t* in_off, uint64_t* out_off) const;
   hlResult_t launchZeroCopy(int kind, const NvlBufs& b, const NvlCall& c, uint64_t in_off, uint64_t out_off, size_t bytes_per_rank,
                             cudaStream_t s);
-  int zeroCopyFlavour(const NvlCall& c, int coll, size_t wire_bytes) const;   // coll: 0 all-reduce, 1 reduce-scatter, 2 gather / broadcast
+  int zeroCopyFlavour(const NvlCall& c, int coll, size_t wire_bytes) const;
+  // Barrier-free small-message kernels: 1 when the call should and can take them, 0 when not, -1 when the caller
+  // asked for them by name and the call does not qualify. coll: 0 all-reduce, 1 reduce-scatter, 2 all-gather.
+  int lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size_t wire_bytes) const;
+  hlResult_t launchLowLatency(int kind, const NvlBufs& b, const NvlCall& c, uint64_t packets_per_thread_range, cudaStream_t s);   // coll: 0 all-reduce, 1 reduce-scatter, 2 gather / broadcast
   Bootstrap* bs_ = nullptr;
   bool emu_ = false;
   int emu_active_ = 0;
   int rank_ = 0, nranks_ = 1, device_ = 0;
   size_t stage_bytes_ = 0;
+  size_t ll_slot_bytes_ = 0;   // one slot of the low-latency region (0: the region does not exist)
   bool has_mc_ = false;
   SymmRegion region_;
   void* emu_mem_[HL_MAX_RANKS] = {nullptr};

@@ -47,6 +47,10 @@ struct HlCommDev {
   uint8_t* heap[HL_MAX_RANKS];
   uint8_t* mc_heap;                // NVSwitch multicast alias of the heap (null without NVLS)
   uint64_t heap_bytes;
+  // Low-latency region of the barrier-free kernels (nvl_ll_kernels.cu), behind the flag area of every rank:
+  // [2 parities][2 phases][HL_MAX_RANKS sources] slots of ll_slot_bytes; null / 0 when the region does not exist.
+  uint8_t* ll[HL_MAX_RANKS];
+  uint64_t ll_slot_bytes;
 };
 // Behind the flag words of every rank sit [HL_MAX_RANKS][2] words in which peer q announces the heap offsets
 // (in, out) of its buffers for the running zero-copy call; they must equal the local ones.
@@ -110,5 +114,9 @@ enum HlNvlKernel {
   kNvlZcAllGatherP2p = 24,
   kNvlZcBroadcastNvls = 25,
   kNvlZcBroadcastP2p = 26,
+  // barrier-free kernels for small messages: every 16-byte store carries its own arrival flag
+  kNvlLlAllReduce = 27,
+  kNvlLlReduceScatter = 28,
+  kNvlLlAllGather = 29,
 };
 #define HL_DEV_ASYMMETRIC 4   // zero-copy call whose buffers do not sit at the same heap offset on every rank

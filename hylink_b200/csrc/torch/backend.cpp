@@ -198,6 +198,7 @@ class HylinkBackend : public c10d::Backend {
     // finishes each gradient bucket sooner but stalls the GEMMs beside it for longer than it saves (GPT-2-medium
     // DDP on 2 GPUs: 55.4 ms per step with 148 CTAs, 54.5 ms with 48 to 96). Stand-alone collectives keep the table.
     if (const char* e = getenv("HYLINK_TORCH_MAX_BLOCKS")) max_blocks_ = atoi(e);
+    if (const char* e = getenv("HYLINK_TORCH_SYNC_INLINE")) sync_inline_ = atoi(e) != 0;
   }
   ~HylinkBackend() override { shutdown(); }
 
@@ -253,12 +254,16 @@ class HylinkBackend : public c10d::Backend {
     return slot;
   }
 
+  // `async_op` is the caller's async_op flag (c10d passes it in every options struct). A synchronous call is waited
+  // for on the caller's stream right after it returns, so it runs ON that stream: no ready event, no hop to the
+  // communication stream and back (two event records and two stream waits, several microseconds of a small
+  // collective). Asynchronous calls (DDP buckets, overlap) keep the communication stream.
   template <typename F>
-  c10::intrusive_ptr<c10d::Work> run(OpType type, const at::Tensor& probe, std::vector<at::Tensor> outputs,
+  c10::intrusive_ptr<c10d::Work> run(bool async_op, OpType type, const at::Tensor& probe, std::vector<at::Tensor> outputs,
                                      std::vector<at::Tensor> keep, F&& body) {
     hlComm_t comm = commFor(probe);
     auto work = c10::make_intrusive<HylinkWork>(getRank(), type, std::move(outputs), std::move(keep));
-    if (probe.is_cuda() && getSize() == 1) {
+    if (probe.is_cuda() && (getSize() == 1 || (!async_op && sync_inline_))) {
       // one rank: every collective is local work; it runs on the caller's stream, with no hop to another stream
       c10::cuda::CUDAGuard dg(probe.device());
       auto cur = c10::cuda::getCurrentCUDAStream(probe.device().index());
@@ -290,7 +295,7 @@ class HylinkBackend : public c10d::Backend {
     at::Tensor t = tensors[0];
     checkContig(t);
     const OpInfo oi = toHlOp(opts.reduceOp);
-    return run(OpType::ALLREDUCE, t, {t}, {t}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::ALLREDUCE, t, {t}, {t}, [&](hlComm_t c, hlStream_t s) {
       hlCallOpts o;
       memset(&o, 0, sizeof(o));
       o.scale = fused_scale_ != 0.0f ? fused_scale_ : oi.scale;
@@ -304,7 +309,7 @@ class HylinkBackend : public c10d::Backend {
     TORCH_CHECK(!tensors.empty(), "hylink: empty tensor list");
     const OpInfo oi = toHlOp(opts.reduceOp);
     std::vector<at::Tensor> ts = tensors;
-    return run(OpType::ALLREDUCE_COALESCED, ts[0], ts, ts, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::ALLREDUCE_COALESCED, ts[0], ts, ts, [&](hlComm_t c, hlStream_t s) {
       for (auto& t : ts) {
         checkContig(t);
         hlCheck(hlAllReduce(t.data_ptr(), t.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), oi.op, c, s), "allreduce_coalesced");
@@ -317,17 +322,17 @@ class HylinkBackend : public c10d::Backend {
     at::Tensor t = tensors[0];
     checkContig(t);
     const int root = (int)opts.rootRank;
-    return run(OpType::BROADCAST, t, {t}, {t}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::BROADCAST, t, {t}, {t}, [&](hlComm_t c, hlStream_t s) {
       hlCheck(hlBroadcast(t.data_ptr(), t.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), root, c, s), "broadcast");
     });
   }
 
-  c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& out, at::Tensor& in, const c10d::AllgatherOptions&) override {
+  c10::intrusive_ptr<c10d::Work> _allgather_base(at::Tensor& out, at::Tensor& in, const c10d::AllgatherOptions& opts) override {
     checkContig(out);
     checkContig(in);
     TORCH_CHECK(out.numel() == in.numel() * getSize(), "hylink: all_gather_into_tensor size mismatch");
     at::Tensor o = out, i = in;
-    return run(OpType::_ALLGATHER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::_ALLGATHER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
       hlCallOpts co;
       memset(&co, 0, sizeof(co));
       co.max_blocks = max_blocks_;
@@ -336,13 +341,13 @@ class HylinkBackend : public c10d::Backend {
   }
 
   c10::intrusive_ptr<c10d::Work> allgather(std::vector<std::vector<at::Tensor>>& outs, std::vector<at::Tensor>& ins,
-                                           const c10d::AllgatherOptions&) override {
+                                           const c10d::AllgatherOptions& opts) override {
     TORCH_CHECK(ins.size() == 1 && outs.size() == 1, "hylink: one input per allgather");
     at::Tensor in = ins[0].contiguous();
     std::vector<at::Tensor> dst = outs[0];
     TORCH_CHECK((int)dst.size() == getSize(), "hylink: allgather output list must have world_size entries");
     at::Tensor flat = at::empty({(int64_t)getSize() * in.numel()}, in.options());
-    return run(OpType::ALLGATHER, in, dst, {in, flat}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::ALLGATHER, in, dst, {in, flat}, [&](hlComm_t c, hlStream_t s) {
       hlCheck(hlAllGather(in.data_ptr(), flat.data_ptr(), (size_t)in.numel(), toHl(in.scalar_type()), c, s), "allgather");
       c10::OptionalStreamGuard sg;
       if (in.is_cuda()) sg.reset_stream(c10::cuda::getStreamFromExternal((cudaStream_t)s, in.device().index()));
@@ -352,11 +357,11 @@ class HylinkBackend : public c10d::Backend {
   }
 
   c10::intrusive_ptr<c10d::Work> allgather_into_tensor_coalesced(std::vector<at::Tensor>& outs, std::vector<at::Tensor>& ins,
-                                                                 const c10d::AllgatherOptions&) override {
+                                                                 const c10d::AllgatherOptions& opts) override {
     TORCH_CHECK(outs.size() == ins.size() && !ins.empty(), "hylink: list size mismatch");
     std::vector<at::Tensor> o = outs, i = ins, keep = ins;
     keep.insert(keep.end(), o.begin(), o.end());
-    return run(OpType::ALLGATHER_COALESCED, i[0], o, keep, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::ALLGATHER_COALESCED, i[0], o, keep, [&](hlComm_t c, hlStream_t s) {
       for (size_t k = 0; k < i.size(); ++k) {
         checkContig(i[k]);
         checkContig(o[k]);
@@ -371,7 +376,7 @@ class HylinkBackend : public c10d::Backend {
     TORCH_CHECK(in.numel() == out.numel() * getSize(), "hylink: reduce_scatter_tensor size mismatch");
     const OpInfo oi = toHlOp(opts.reduceOp);
     at::Tensor o = out, i = in;
-    return run(OpType::_REDUCE_SCATTER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::_REDUCE_SCATTER_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
       hlCallOpts co;
       memset(&co, 0, sizeof(co));
       co.max_blocks = max_blocks_;
@@ -387,7 +392,7 @@ class HylinkBackend : public c10d::Backend {
     const OpInfo oi = toHlOp(opts.reduceOp);
     std::vector<at::Tensor> parts = ins[0];
     at::Tensor probe = out;
-    return run(OpType::REDUCE_SCATTER, probe, {out}, parts, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::REDUCE_SCATTER, probe, {out}, parts, [&](hlComm_t c, hlStream_t s) {
       c10::OptionalStreamGuard sg;
       if (out.is_cuda()) sg.reset_stream(c10::cuda::getStreamFromExternal((cudaStream_t)s, out.device().index()));
       std::vector<at::Tensor> flat_parts;
@@ -405,7 +410,7 @@ class HylinkBackend : public c10d::Backend {
     const OpInfo oi = toHlOp(opts.reduceOp);
     std::vector<at::Tensor> o = outs, i = ins, keep = ins;
     keep.insert(keep.end(), o.begin(), o.end());
-    return run(OpType::COALESCED, i[0], o, keep, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::COALESCED, i[0], o, keep, [&](hlComm_t c, hlStream_t s) {
       for (size_t k = 0; k < i.size(); ++k) {
         checkContig(i[k]);
         checkContig(o[k]);
@@ -415,13 +420,13 @@ class HylinkBackend : public c10d::Backend {
   }
 
   c10::intrusive_ptr<c10d::Work> alltoall_base(at::Tensor& out, at::Tensor& in, std::vector<int64_t>& outSplit,
-                                               std::vector<int64_t>& inSplit, const c10d::AllToAllOptions&) override {
+                                               std::vector<int64_t>& inSplit, const c10d::AllToAllOptions& opts) override {
     TORCH_CHECK(outSplit.empty() && inSplit.empty(), "hylink: only equal splits are supported by all_to_all_single");
     checkContig(out);
     checkContig(in);
     TORCH_CHECK(out.numel() == in.numel() && in.numel() % getSize() == 0, "hylink: all_to_all_single size mismatch");
     at::Tensor o = out, i = in;
-    return run(OpType::ALLTOALL_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::ALLTOALL_BASE, i, {o}, {i, o}, [&](hlComm_t c, hlStream_t s) {
       hlCheck(hlAllToAll(i.data_ptr(), o.data_ptr(), (size_t)i.numel() / getSize(), toHl(i.scalar_type()), c, s), "all_to_all");
     });
   }
@@ -435,7 +440,7 @@ class HylinkBackend : public c10d::Backend {
     const OpInfo oi = toHlOp(opts.reduceOp);
     const bool root = (int)opts.rootRank == getRank();
     at::Tensor dst = root ? t : at::empty_like(t);
-    return run(OpType::REDUCE, t, {t}, {t, dst}, [&](hlComm_t c, hlStream_t s) {
+    return run(opts.asyncOp, OpType::REDUCE, t, {t}, {t, dst}, [&](hlComm_t c, hlStream_t s) {
       hlCheck(hlAllReduce(t.data_ptr(), dst.data_ptr(), (size_t)t.numel(), toHl(t.scalar_type()), oi.op, c, s), "reduce");
     });
   }
@@ -448,7 +453,7 @@ class HylinkBackend : public c10d::Backend {
       if (dev >= 0) probe = at::empty({1}, at::TensorOptions().device(at::kCUDA, dev).dtype(at::kFloat));
     }
     if (!probe.defined()) probe = at::empty({1}, at::TensorOptions().dtype(at::kFloat));
-    return run(OpType::BARRIER, probe, {}, {probe}, [&](hlComm_t c, hlStream_t s) { hlCheck(hlBarrier(c, s), "barrier"); });
+    return run(opts.asyncOp, OpType::BARRIER, probe, {}, {probe}, [&](hlComm_t c, hlStream_t s) { hlCheck(hlBarrier(c, s), "barrier"); });
   }
 
   c10::intrusive_ptr<c10d::Work> send(std::vector<at::Tensor>&, int, int) override {
@@ -525,6 +530,7 @@ class HylinkBackend : public c10d::Backend {
   std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
   float fused_scale_ = 0.0f;
   int max_blocks_ = 0;
+  bool sync_inline_ = true;   // synchronous calls run on the caller's stream (HYLINK_TORCH_SYNC_INLINE=0: always the communication stream)
   std::shared_ptr<std::atomic<bool>> alive_ = std::make_shared<std::atomic<bool>>(true);
 };
 

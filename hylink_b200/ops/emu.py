@@ -18,7 +18,7 @@ from .._native import OPS, check, lib, torch_dtype_code
 
 KINDS = {"all_reduce": 0, "reduce_scatter": 1, "all_gather": 2, "broadcast": 3, "all_to_all": 4, "barrier": 5}
 ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5, "zerocopy": 6, "zerocopy_nvls": 7,
-         "zerocopy_p2p": 8}
+         "zerocopy_p2p": 8, "ll": 9}
 
 
 class EmuGroup:

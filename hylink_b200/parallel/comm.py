@@ -12,7 +12,7 @@ from .._native import CallOpts, CommStats, OPS, UniqueId, check, lib, torch_dtyp
 
 PATHS = {"auto": 0, "nvlink": 1, "pcie": 2, "split": 3}
 ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "pipelined": 4, "push": 5, "zerocopy": 6, "zerocopy_nvls": 7,
-         "zerocopy_p2p": 8}
+         "zerocopy_p2p": 8, "ll": 9}
 
 
 def unique_id() -> bytes:

@@ -79,7 +79,8 @@ def main(argv=None) -> int:
         dt = DT[dname]
         es = torch.empty((), dtype=dt).element_size()
         # per-rank element counts: tiny, odd, one around a CTA's share, and the largest asked for
-        seg_counts = sorted({1, 7, 4099, (1 << 20) // es + 3, top // es // world})
+        # ... plus two whole-packet sizes for the kernels that want them (zero-copy, low-latency)
+        seg_counts = sorted({1, 7, 4099, (1 << 20) // es + 3, top // es // world, 3 * (16 // es), (256 << 10) // es})
         for si, seg in enumerate(seg_counts):
             n_el = seg * world
             ins = _inputs(world, n_el, dt, 7 + si)
@@ -163,6 +164,40 @@ def main(argv=None) -> int:
                 torch.cuda.synchronize()
                 verdict("zc-mixed", "auto", dname, n_el, rout[pad:pad + n_el], torch.cat([want_sum[:seg]] * world), not nvls or world < 4)
                 del rin, rout
+            # barrier-free small-message kernels: any memory, whole 16-byte packets, a segment that fits a slot
+            if n_el * es % 16 == 0 and seg * es % 16 == 0 and seg * es <= (2 << 20):
+                pad = 16 // es
+                for rep in range(3):   # consecutive calls alternate the two halves of the low-latency region
+                    out = torch.full((n_el + 2 * pad,), 3.0, device="cuda", dtype=dt)
+                    comm.all_reduce(ins[rank], out[pad:pad + n_el], algo="ll")
+                    torch.cuda.synchronize()
+                    verdict("ll-allreduce", "ll", dname, n_el, out[pad:pad + n_el], want_sum, True)
+                    if not (bool((out[:pad] == 3.0).all()) and bool((out[pad + n_el:] == 3.0).all())):
+                        failures.append({"coll": "ll-allreduce", "algo": "ll", "dtype": dname, "elems": n_el, "rank": rank, "guard": True})
+                    part = torch.full((seg + 2 * pad,), 3.0, device="cuda", dtype=dt)
+                    comm.reduce_scatter(ins[rank], part[pad:pad + seg], algo="ll")
+                    torch.cuda.synchronize()
+                    verdict("ll-reducescatter", "ll", dname, seg, part[pad:pad + seg], want_sum[rank * seg:(rank + 1) * seg], True)
+                    if not (bool((part[:pad] == 3.0).all()) and bool((part[pad + seg:] == 3.0).all())):
+                        failures.append({"coll": "ll-reducescatter", "algo": "ll", "dtype": dname, "elems": seg, "rank": rank, "guard": True})
+                    out.fill_(3.0)
+                    comm.all_gather(ins[rank][:seg], out[pad:pad + n_el], algo="ll")
+                    torch.cuda.synchronize()
+                    verdict("ll-allgather", "ll", dname, n_el, out[pad:pad + n_el], want_gather, True)
+                # back to back without host synchronisation, mixed with barrier kernels, in place
+                a1 = ins[rank].clone()
+                a2 = torch.empty(n_el, device="cuda", dtype=dt)
+                a3 = torch.empty(seg, device="cuda", dtype=dt)
+                for _ in range(4):
+                    a1.copy_(ins[rank])
+                    comm.all_reduce(a1, a1, algo="ll")
+                    comm.all_gather(a1[:seg], a2, algo="ll")
+                    comm.all_reduce(ins[rank], a2, algo="push")
+                    comm.reduce_scatter(ins[rank], a3, algo="ll")
+                    comm.all_gather(a3, a2, algo="ll")
+                torch.cuda.synchronize()
+                verdict("ll-mixed", "ll", dname, n_el, a1, want_sum, True)
+                verdict("ll-mixed-gather", "ll", dname, n_el, a2, want_sum, True)
             # calls of different sizes and kinds back to back, no host synchronisation in between: the staging
             # hand-over from one kernel to the next
             big, small = ins[rank], ins[rank][:max(1, n_el // 3)]

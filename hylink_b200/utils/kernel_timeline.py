@@ -24,7 +24,8 @@ KINDS = {0: "barrier", 1: "allreduce_oneshot", 2: "allreduce_twoshot", 3: "allre
          14: "reducescatter_pipelined_nvls", 15: "allreduce_push", 16: "reducescatter_push", 17: "allgather_push", 18: "allgather_lanes",
          19: "zerocopy_allreduce_nvls", 20: "zerocopy_allreduce_p2p", 21: "zerocopy_reducescatter_nvls",
          22: "zerocopy_reducescatter_p2p", 23: "zerocopy_allgather_nvls", 24: "zerocopy_allgather_p2p",
-         25: "zerocopy_broadcast_nvls", 26: "zerocopy_broadcast_p2p"}
+         25: "zerocopy_broadcast_nvls", 26: "zerocopy_broadcast_p2p",
+         27: "lowlatency_allreduce", 28: "lowlatency_reducescatter", 29: "lowlatency_allgather"}
 PHASE_NAMES = ["entry", "arrive1", "leave1", "arrive2", "leave2", "arrive3", "leave3", "exit"]
 
 

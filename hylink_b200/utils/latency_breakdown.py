@@ -72,7 +72,7 @@ def main(argv=None) -> int:
     x, y = comm.alloc_registered(top, torch.bfloat16), comm.alloc_registered(top, torch.bfloat16)
     x.fill_(1.0)
     dist.all_reduce(torch.zeros(1, device=dev), group=hl_group)   # the backend's communicator exists from here on
-    bx, by = symmetric_empty(top, torch.bfloat16), symmetric_empty(top, torch.bfloat16)
+    bx, by = symmetric_empty(top, torch.bfloat16, group=hl_group), symmetric_empty(top, torch.bfloat16, group=hl_group)
     bx.fill_(1.0)
     nx, ny = torch.ones(top, device=dev, dtype=torch.bfloat16), torch.empty(top, device=dev, dtype=torch.bfloat16)
     outf = open(a.out, "a") if (a.out and rank == 0) else None

@@ -119,7 +119,7 @@ def test_auto_uses_zero_copy_only_when_every_condition_holds():
     n = 4
     g = _group(n, stage_bytes=256 << 10)        # staging far smaller than the message: staged calls need several launches
     dtype = torch.float32
-    count = (2 << 20) // 4
+    count = (8 << 20) // 4                      # above the sizes the barrier-free small-message kernels take
     ins = g.alloc_registered(count, dtype)
     outs = g.alloc_registered(count, dtype)
     _fill(ins, dtype, 11)
