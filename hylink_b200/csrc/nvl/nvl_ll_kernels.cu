@@ -41,11 +41,15 @@ __device__ __forceinline__ uint8_t* llSlot(const HlCommDev& c, int owner, int pa
   return c.ll[owner] + ((size_t)((parity * 2 + phase) * HL_MAX_RANKS + src)) * c.ll_slot_bytes;
 }
 
-// One 16-byte data packet = two flagged 16-byte stores at byte offset 32 * j of the slot.
+// One 16-byte data packet = two flagged 16-byte stores. Packets are laid out in groups of 32 (one warp): the 32
+// first halves side by side (512 bytes), then the 32 second halves, so that each of the two store instructions of
+// a warp — and each of the two polling loads — covers 512 contiguous bytes instead of every other 16.
+__device__ __forceinline__ uint64_t llOffset(uint64_t j) { return (j >> 5) * 1024 + (j & 31) * 16; }
+
 __device__ __forceinline__ void llSend(uint8_t* slot, uint64_t j, const uint4& v, uint32_t tag) {
-  uint8_t* p = slot + j * 32;
+  uint8_t* p = slot + llOffset(j);
   asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(tag), "r"(v.y), "r"(tag) : "memory");
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p + 16), "r"(v.z), "r"(tag), "r"(v.w), "r"(tag) : "memory");
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p + 512), "r"(v.z), "r"(tag), "r"(v.w), "r"(tag) : "memory");
 }
 
 struct LlWait {
@@ -56,12 +60,12 @@ struct LlWait {
 // Spins until both halves of packet j carry the tag. Bounded: after timeout_ns (or when the communicator is
 // poisoned) it records where it gave up, poisons the communicator and returns false; the caller leaves the kernel.
 __device__ __forceinline__ bool llRecv(const HlCommDev& c, const uint8_t* slot, uint64_t j, uint32_t tag, int src, LlWait& w, uint4* out) {
-  const uint8_t* p = slot + j * 32;
+  const uint8_t* p = slot + llOffset(j);
   uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
   uint32_t spins = 0;
   for (;;) {
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "l"(p) : "memory");
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "l"(p + 16) : "memory");
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "l"(p + 512) : "memory");
     if (a1 == tag && a3 == tag && b1 == tag && b3 == tag) break;
     if ((++spins & 63u) == 0) {
       const uint64_t now = globalTimerNs();

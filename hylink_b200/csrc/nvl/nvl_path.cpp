@@ -564,10 +564,12 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
   const int no = asked ? -1 : 0;
   if (!ll_slot_bytes_ || nranks_ < 2) return no;
   if (!asked) {
-    // Measured on 4 GPUs (device time between two events, bf16): the barrier-based kernels spend 10 to 20 us in their
-    // two flag rounds whatever the size; flagged packets halve the link rate instead, which is the better deal up to
-    // a few MiB.
-    static const long long ar_max = envInt({"HYLINK_LL_AR_MAX"}, 2LL << 20), rs_max = envInt({"HYLINK_LL_RS_MAX"}, 4LL << 20),
+    // Measured on 4 GPUs (kernel time from the timeline, bf16; barrier-based zero-copy kernel -> this one): 64 KiB
+    // reduce-scatter 12.1 -> 4.2 us, all-gather 10.1 -> 6.8; 1 MiB all-reduce 18.0 -> 12.4, reduce-scatter 19.8 -> 8.2,
+    // all-gather 17.1 -> 6.8; 2 MiB 20.1 -> 15.3, 17.4 -> 12.0, 16.9 -> 7.9; 4 MiB 23.2 -> 25.2, 21.5 -> 16.6,
+    // 20.4 -> 13.8; 8 MiB reduce-scatter 28.2 -> 23.7, all-gather 23.2 -> 24.3. The two flag rounds of the other
+    // kernels cost 10-15 us whatever the size; flagged packets cost half the link rate instead.
+    static const long long ar_max = envInt({"HYLINK_LL_AR_MAX"}, 2LL << 20), rs_max = envInt({"HYLINK_LL_RS_MAX"}, 8LL << 20),
                            ag_max = envInt({"HYLINK_LL_AG_MAX"}, 4LL << 20);
     const long long lim = coll == 0 ? ar_max : (coll == 1 ? rs_max : ag_max);
     if ((long long)wire_bytes > lim) return 0;
@@ -580,7 +582,7 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
   if (c.count % epp || (coll == 1 && istride % epp) || (coll == 2 && ostride % epp)) return no;
   const uint64_t np = c.count / epp;
   const uint64_t per_src = coll == 0 ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;   // packets one rank sends to one peer
-  if (per_src * 32 > ll_slot_bytes_) return no;
+  if (((per_src + 31) / 32) * 1024 > ll_slot_bytes_) return no;   // packets are stored in groups of 32 (1 KiB)
   const size_t n = (size_t)nranks_;
   for (int i = 0; i < localRanks(); ++i) {
     const char* in = (const char*)b.in[i];

@@ -255,9 +255,11 @@ class HylinkBackend : public c10d::Backend {
   }
 
   // `async_op` is the caller's async_op flag (c10d passes it in every options struct). A synchronous call is waited
-  // for on the caller's stream right after it returns, so it runs ON that stream: no ready event, no hop to the
-  // communication stream and back (two event records and two stream waits, several microseconds of a small
-  // collective). Asynchronous calls (DDP buckets, overlap) keep the communication stream.
+  // for on the caller's stream right after it returns, so it CAN run on that stream (HYLINK_TORCH_SYNC_INLINE=1): no
+  // ready event, no hop to the communication stream and back. Off by default, by measurement on 4 GPUs: a call
+  // queued behind other work is 1-3 us shorter inline, but a sequence of collectives that are each bracketed by
+  // timing events is 2-3 us per call LONGER inline (geometric mean of the 1 MiB-1 GiB table 278.8 against 289.8 GB/s):
+  // on its own stream the kernel is set up while the caller's stream is still busy with the events around it.
   template <typename F>
   c10::intrusive_ptr<c10d::Work> run(bool async_op, OpType type, const at::Tensor& probe, std::vector<at::Tensor> outputs,
                                      std::vector<at::Tensor> keep, F&& body) {
@@ -530,7 +532,7 @@ class HylinkBackend : public c10d::Backend {
   std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
   float fused_scale_ = 0.0f;
   int max_blocks_ = 0;
-  bool sync_inline_ = true;   // synchronous calls run on the caller's stream (HYLINK_TORCH_SYNC_INLINE=0: always the communication stream)
+  bool sync_inline_ = false;  // HYLINK_TORCH_SYNC_INLINE=1: synchronous calls run on the caller's stream instead of the communication stream
   std::shared_ptr<std::atomic<bool>> alive_ = std::make_shared<std::atomic<bool>>(true);
 };
 

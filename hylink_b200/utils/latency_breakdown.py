@@ -3,15 +3,16 @@
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 \
         -m hylink_b200.utils.latency_breakdown [--bytes 1M,2M,4M] [--colls allreduce,reducescatter,allgather]
 
-For every collective and size, on registered buffers (the zero-copy kernels), three nested measurements, each the
-median over `--iters` calls that were queued behind a short sleep kernel so that the GPU, not the host, sets the pace:
+For every collective and size, on registered buffers, three nested measurements, each the median over `--iters`
+calls that were queued behind a short sleep kernel so that the GPU, not the host, sets the pace:
 
-* ``kernel_us`` and ``phases``: from the kernel timeline (``%globaltimer`` stamps inside the kernel): entry to the
-  first barrier, the barrier itself (it also absorbs the skew between the ranks' launches), the transfer, the
-  closing barrier;
+* ``kernel_us`` and ``phases``: from the kernel timeline (``%globaltimer`` stamps inside the kernel). Barrier-based
+  kernels: entry to the first barrier, the barrier itself (it also absorbs the skew between the ranks' launches),
+  the transfer, the closing barrier; the low-latency kernels have no barrier, so only entry to exit;
 * ``direct_us``: CUDA events around the C API call on one stream (launch gap + kernel);
-* ``backend_us``: CUDA events around ``torch.distributed`` on backend ``hylink`` (adds the hop to the communication
-  stream and back: two events and two stream waits);
+* ``backend_us``: CUDA events around ``torch.distributed`` on backend ``hylink`` (synchronous calls run on the
+  caller's stream; with ``HYLINK_TORCH_SYNC_INLINE=0`` they hop to the communication stream and back, which adds two
+  events and two stream waits);
 * ``nccl_us``: the same around the NCCL backend, for comparison.
 
 All figures are from rank 0 except the event times, which are the maximum over ranks.

@@ -3,8 +3,8 @@
     python -m hylink_b200.utils.profile_kernels [--ranks 4] [--mib 48]
 
 Runs, on ONE device: the two-shot pull all-reduce, the push all-reduce, the
-pipelined all-reduce, the push reduce-scatter, the all-gather and the zero-copy
-kernels on registered memory (peer-pointer flavour) with `--ranks`
+pipelined all-reduce, the push reduce-scatter, the all-gather, the zero-copy
+kernels on registered memory (peer-pointer flavour) and the low-latency kernels with `--ranks`
 emulated ranks (one cooperative launch each; `--mib` MiB of bf16 per rank, so
 the working set is larger than the 126 MB L2 while staying within a few
 hundred MB), and the landing-reduce kernel over four `--landing-mib` MiB sources. Prints the
@@ -70,6 +70,15 @@ def main(argv=None) -> int:
         timed("allgather_zerocopy_p2p", lambda: g.run("all_gather", [t[:seg] for t in ins], rout, seg, out_seg_stride=seg, algo="zerocopy_p2p"),
               n * (seg * 2 + count * 2))
         del rin, rout
+    # low-latency kernels (flag in every 16-byte store): small by design, 512 KiB per source
+    lc = (512 << 10) // 2
+    lins = [t[:lc * n] for t in ins]
+    louts = [t[:lc * n] for t in outs]
+    timed("allreduce_lowlatency", lambda: g.run("all_reduce", [t[:lc] for t in lins], [t[:lc] for t in louts], lc, algo="ll"), n * lc * 2 * (2 + 8.0 * (n - 1) / n))
+    timed("reducescatter_lowlatency", lambda: g.run("reduce_scatter", lins, [t[:lc] for t in louts], lc, in_seg_stride=lc, algo="ll"),
+          n * lc * 2 * (n + 4.0 * (n - 1) + 1))
+    timed("allgather_lowlatency", lambda: g.run("all_gather", [t[:lc] for t in lins], louts, lc, out_seg_stride=lc, algo="ll"),
+          n * lc * 2 * (1 + 4.0 * (n - 1) + n))
     srcs = [torch.randn(a.landing_mib << 19, device="cuda").to(torch.bfloat16) for _ in range(4)]
     dst = torch.empty_like(srcs[0])
     timed("reduce_landing_4way", lambda: reduce_landing(dst, srcs), 5 * srcs[0].numel() * 2)
