@@ -1282,7 +1282,7 @@ static const void* pickKernelT(int kind, int nranks) {
 
 const void* kernelFor(int kind, int wire_dt, int nranks) {
   if (kind == kNvlBarrier) return (const void*)dev::kBarrier;
-  if (kind == kNvlLlAllReduce || kind == kNvlLlReduceScatter || kind == kNvlLlAllGather) return lowLatencyKernelFor(kind, wire_dt);
+  if (kind == kNvlLlAllReduce || kind == kNvlLlReduceScatter || kind == kNvlLlAllGather || kind == kNvlLlAllToAll) return lowLatencyKernelFor(kind, wire_dt);
   switch (wire_dt) {
     case hlInt8: return pickKernelT<int8_t>(kind, nranks);
     case hlUint8: return pickKernelT<uint8_t>(kind, nranks);
@@ -1330,6 +1330,7 @@ const char* kernelName(int kind) {
     case kNvlLlAllReduce: return "allreduce_lowlatency";
     case kNvlLlReduceScatter: return "reducescatter_lowlatency";
     case kNvlLlAllGather: return "allgather_lowlatency";
+    case kNvlLlAllToAll: return "alltoall_lowlatency";
     default: return "?";
   }
 }
@@ -1368,7 +1369,7 @@ hlResult_t prepareKernels() {
                               kNvlReduceScatterPush, kNvlAllGatherPush, kNvlAllGatherLanes, kNvlZcAllReduceNvls,
                               kNvlZcAllReduceP2p, kNvlZcReduceScatterNvls, kNvlZcReduceScatterP2p, kNvlZcAllGatherNvls,
                               kNvlZcAllGatherP2p, kNvlZcBroadcastNvls, kNvlZcBroadcastP2p, kNvlLlAllReduce,
-                              kNvlLlReduceScatter, kNvlLlAllGather};
+                              kNvlLlReduceScatter, kNvlLlAllGather, kNvlLlAllToAll};
   for (int k : kinds)
     for (int dt = 0; dt < hlNumTypes; ++dt) {
       for (int nr : {2, 4, HL_MAX_RANKS}) {   // rank-count classes (only the pipelined push kernels differ by it)

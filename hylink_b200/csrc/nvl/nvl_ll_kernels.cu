@@ -16,6 +16,7 @@
 // all ranks anyway. The tag is the call index + 1 (never 0, the value of cleared memory) and differs from the tag
 // that the same slot held two calls earlier.
 //
+// all-to-all:      send segment q to rank q       | receive segment s from rank s into slot s of the output
 // all-gather:      send own segment to every peer | receive the others' segments into the output
 // reduce-scatter:  send segment q to rank q       | receive n-1 contributions, add in rank order, store
 // all-reduce:      reduce-scatter of the n shards (phase 0), then all-gather of the reduced shards (phase 1)
@@ -35,7 +36,7 @@
 namespace hl {
 namespace dev {
 
-constexpr int kLlAllReduce = 0, kLlReduceScatter = 1, kLlAllGather = 2;
+constexpr int kLlAllReduce = 0, kLlReduceScatter = 1, kLlAllGather = 2, kLlAllToAll = 3;
 
 __device__ __forceinline__ uint8_t* llSlot(const HlCommDev& c, int owner, int parity, int phase, int src) {
   return c.ll[owner] + ((size_t)((parity * 2 + phase) * HL_MAX_RANKS + src)) * c.ll_slot_bytes;
@@ -140,6 +141,25 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kLowLatency(const HlCommDev* c
         if (!llRecv(c, llSlot(c, r, parity, 0, s), j, tag, s, w, &v)) break;
         out[(uint64_t)s * ostride + j] = v;
       }
+  } else if constexpr (kColl == kLlAllToAll) {
+    const uint64_t istride = a.in_seg_stride / N, ostride = a.out_seg_stride / N;
+    for (uint64_t j = g0; j < np; j += gstride) {
+      uint4 own;
+      for (int k = 0; k < n; ++k) {
+        const int q = (r + k) % n;
+        const uint4 v = in[(uint64_t)q * istride + j];
+        if (k == 0) own = v;
+        else llSend(llSlot(c, q, parity, 0, r), j, v, tag);
+      }
+      out[(uint64_t)r * ostride + j] = own;   // after every read of this thread's column: in place is safe
+    }
+    for (uint64_t j = g0; j < np && w.ok; j += gstride)
+      for (int k = 1; k < n; ++k) {
+        const int s = (r + n - k) % n;
+        uint4 v;
+        if (!llRecv(c, llSlot(c, r, parity, 0, s), j, tag, s, w, &v)) break;
+        out[(uint64_t)s * ostride + j] = v;
+      }
   } else if constexpr (kColl == kLlReduceScatter) {
     const uint64_t istride = a.in_seg_stride / N;
     for (uint64_t j = g0; j < np; j += gstride)
@@ -207,6 +227,7 @@ static const void* pickLl(int kind) {
     case kNvlLlAllReduce: return (const void*)kLowLatency<W, kLlAllReduce>;
     case kNvlLlReduceScatter: return (const void*)kLowLatency<W, kLlReduceScatter>;
     case kNvlLlAllGather: return (const void*)kLowLatency<W, kLlAllGather>;
+    case kNvlLlAllToAll: return (const void*)kLowLatency<W, kLlAllToAll>;
     default: return nullptr;
   }
 }

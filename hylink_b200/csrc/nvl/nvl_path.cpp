@@ -570,8 +570,8 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
     // 20.4 -> 13.8; 8 MiB reduce-scatter 28.2 -> 23.7, all-gather 23.2 -> 24.3. The two flag rounds of the other
     // kernels cost 10-15 us whatever the size; flagged packets cost half the link rate instead.
     static const long long ar_max = envInt({"HYLINK_LL_AR_MAX"}, 2LL << 20), rs_max = envInt({"HYLINK_LL_RS_MAX"}, 8LL << 20),
-                           ag_max = envInt({"HYLINK_LL_AG_MAX"}, 4LL << 20);
-    const long long lim = coll == 0 ? ar_max : (coll == 1 ? rs_max : ag_max);
+                           ag_max = envInt({"HYLINK_LL_AG_MAX"}, 4LL << 20), a2a_max = envInt({"HYLINK_LL_A2A_MAX"}, 4LL << 20);
+    const long long lim = coll == 0 ? ar_max : (coll == 1 ? rs_max : (coll == 2 ? ag_max : a2a_max));
     if ((long long)wire_bytes > lim) return 0;
   }
   if (c.in_dt != c.wire_dt || c.out_dt != c.wire_dt) return no;
@@ -579,7 +579,7 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
   if (!ws) return no;
   const uint64_t epp = 16 / ws;
   const uint64_t istride = c.in_seg_stride ? c.in_seg_stride : c.count, ostride = c.out_seg_stride ? c.out_seg_stride : c.count;
-  if (c.count % epp || (coll == 1 && istride % epp) || (coll == 2 && ostride % epp)) return no;
+  if (c.count % epp || ((coll == 1 || coll == 3) && istride % epp) || ((coll == 2 || coll == 3) && ostride % epp)) return no;
   const uint64_t np = c.count / epp;
   const uint64_t per_src = coll == 0 ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;   // packets one rank sends to one peer
   if (((per_src + 31) / 32) * 1024 > ll_slot_bytes_) return no;   // packets are stored in groups of 32 (1 KiB)
@@ -596,11 +596,14 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
       bool slot = false;
       for (size_t q = 0; q < n; ++q) slot = slot || out == in + q * istride * ws;
       if (!slot && !disjoint(in, in_bytes, out, c.count * ws)) return no;
-    } else {
+    } else if (coll == 2) {
       const size_t out_bytes = ((n - 1) * ostride + c.count) * ws;
       bool slot = false;
       for (size_t q = 0; q < n; ++q) slot = slot || in == out + q * ostride * ws;
       if (!slot && !disjoint(in, c.count * ws, out, out_bytes)) return no;
+    } else {
+      const size_t in_bytes = ((n - 1) * istride + c.count) * ws, out_bytes = ((n - 1) * ostride + c.count) * ws;
+      if (!(in == out && istride == ostride) && !disjoint(in, in_bytes, out, out_bytes)) return no;
     }
   }
   return 1;
@@ -757,6 +760,12 @@ hlResult_t NvlPath::broadcast(const NvlBufs& b, const NvlCall& c, cudaStream_t s
 
 hlResult_t NvlPath::allToAll(const NvlBufs& b, const NvlCall& c, cudaStream_t s) {
   if (c.count == 0) return hlSuccess;
+  {
+    const size_t seg_wire = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
+    const int ll = lowLatencyChoice(b, c, 3, seg_wire * (size_t)nranks_);
+    if (ll < 0) return fail(hlUnsupported, "all-to-all: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
+    if (ll > 0) return launchLowLatency(kNvlLlAllToAll, b, c, seg_wire / 16, s);
+  }
   return launchSliced(kNvlAllToAll, b, c, true, s);
 }
 

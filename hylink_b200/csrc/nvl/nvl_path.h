@@ -106,7 +106,7 @@ class NvlPath {
                             cudaStream_t s);
   int zeroCopyFlavour(const NvlCall& c, int coll, size_t wire_bytes) const;
   // Barrier-free small-message kernels: 1 when the call should and can take them, 0 when not, -1 when the caller
-  // asked for them by name and the call does not qualify. coll: 0 all-reduce, 1 reduce-scatter, 2 all-gather.
+  // asked for them by name and the call does not qualify. coll: 0 all-reduce, 1 reduce-scatter, 2 all-gather, 3 all-to-all.
   int lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size_t wire_bytes) const;
   hlResult_t launchLowLatency(int kind, const NvlBufs& b, const NvlCall& c, uint64_t packets_per_thread_range, cudaStream_t s);   // coll: 0 all-reduce, 1 reduce-scatter, 2 gather / broadcast
   Bootstrap* bs_ = nullptr;

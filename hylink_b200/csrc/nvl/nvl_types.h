@@ -118,5 +118,6 @@ enum HlNvlKernel {
   kNvlLlAllReduce = 27,
   kNvlLlReduceScatter = 28,
   kNvlLlAllGather = 29,
+  kNvlLlAllToAll = 30,
 };
 #define HL_DEV_ASYMMETRIC 4   // zero-copy call whose buffers do not sit at the same heap offset on every rank

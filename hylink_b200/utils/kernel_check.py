@@ -184,6 +184,10 @@ def main(argv=None) -> int:
                     comm.all_gather(ins[rank][:seg], out[pad:pad + n_el], algo="ll")
                     torch.cuda.synchronize()
                     verdict("ll-allgather", "ll", dname, n_el, out[pad:pad + n_el], want_gather, True)
+                x2 = torch.full((n_el + 2 * pad,), 3.0, device="cuda", dtype=dt)
+                comm.all_to_all(ins[rank], x2[pad:pad + n_el], algo="ll")
+                torch.cuda.synchronize()
+                verdict("ll-alltoall", "ll", dname, n_el, x2[pad:pad + n_el], torch.cat([p[rank * seg:(rank + 1) * seg] for p in ins]), True)
                 # back to back without host synchronisation, mixed with barrier kernels, in place
                 a1 = ins[rank].clone()
                 a2 = torch.empty(n_el, device="cuda", dtype=dt)

@@ -25,7 +25,7 @@ KINDS = {0: "barrier", 1: "allreduce_oneshot", 2: "allreduce_twoshot", 3: "allre
          19: "zerocopy_allreduce_nvls", 20: "zerocopy_allreduce_p2p", 21: "zerocopy_reducescatter_nvls",
          22: "zerocopy_reducescatter_p2p", 23: "zerocopy_allgather_nvls", 24: "zerocopy_allgather_p2p",
          25: "zerocopy_broadcast_nvls", 26: "zerocopy_broadcast_p2p",
-         27: "lowlatency_allreduce", 28: "lowlatency_reducescatter", 29: "lowlatency_allgather"}
+         27: "lowlatency_allreduce", 28: "lowlatency_reducescatter", 29: "lowlatency_allgather", 30: "lowlatency_alltoall"}
 PHASE_NAMES = ["entry", "arrive1", "leave1", "arrive2", "leave2", "arrive3", "leave3", "exit"]
 
 

@@ -108,6 +108,27 @@ def test_reduce_scatter_and_all_gather(n, dtype):
     g.close()
 
 
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_all_to_all(n):
+    g = _group(n, stage_bytes=1 << 20)
+    dtype = torch.float32
+    for seg in [4, 777 * 4, (128 << 10) // 4]:
+        ins = _inputs(n, seg * n, dtype, seg + 5)
+        outs = [torch.zeros(seg * n, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("all_to_all", ins, outs, seg, in_seg_stride=seg, out_seg_stride=seg, algo="ll")
+        torch.cuda.synchronize()
+        for r in range(n):
+            want = torch.cat([ins[s][r * seg:(r + 1) * seg] for s in range(n)])
+            assert torch.equal(outs[r], want), (n, seg, r)
+        work = [t.clone() for t in ins]                  # in place
+        g.run("all_to_all", work, work, seg, in_seg_stride=seg, out_seg_stride=seg, algo="ll")
+        torch.cuda.synchronize()
+        for r in range(n):
+            assert torch.equal(work[r], torch.cat([ins[s][r * seg:(r + 1) * seg] for s in range(n)]))
+        assert g.status(0)[0] == 0
+    g.close()
+
+
 def test_auto_takes_the_low_latency_kernels_for_small_messages_and_mixes_with_the_others(monkeypatch):
     """Small calls, large calls (barrier kernels) and small calls again: the region's halves stay consistent."""
     monkeypatch.setenv("HYLINK_KERNEL_TIMELINE", "1")
