@@ -1,19 +1,21 @@
-// Low-latency kernels of the dedicated-link path for small messages: all-reduce, reduce-scatter and all-gather
-// with NO cross-GPU barrier at all.
+// Low-latency kernels of the dedicated-link path for small messages: all-reduce, reduce-scatter, all-gather and
+// all-to-all with NO cross-GPU barrier at all.
 //
 // The barrier-based kernels (nvl_kernels.cu) pay two flag round trips per call — about 3 to 8 microseconds each
 // once the stores in front of them have to be acknowledged — which is most of the time of a message of a few MiB.
-// Here every 16-byte store carries its own arrival flag: a packet of 8 data bytes and two copies of a 32-bit call
-// tag ({d0, tag, d1, tag}, one st.volatile.v4), written straight into the receiver's low-latency region; the
-// receiver spins on the packet itself until both tags match. One network traversal per hop, no fence, no second
-// trip. The price is half the link bandwidth, so the host side uses these kernels only while latency decides.
+// Here every 16-byte store carries its own arrival flag: 8 data bytes and two copies of a 32-bit call tag
+// ({d0, tag, d1, tag}, one st.volatile.v4, so each 8-byte half validates itself), written straight into the
+// receiver's low-latency region; the receiver spins on the packet itself until all tags match. One network
+// traversal per hop, no fence, no second trip. The price is half the link bandwidth, so the host side uses these
+// kernels only while latency decides (measured limits in NvlPath::lowLatencyChoice). An all-reduce in the case
+// of np < n packets still ends only after some shard owner heard from every rank, which keeps the argument below.
 //
 // Region (per rank, behind the flag words of the symmetric region): [2 parities][2 phases][HL_MAX_RANKS sources]
 // slots of ll_slot_bytes. A call uses the parity of its call index, so the slots it writes were last used two calls
 // ago. That reuse is safe without any handshake: in each of these collectives every rank receives from every other
-// rank, so a rank can only FINISH call k+1 after every peer has STARTED sending in call k+1, i.e. after every peer
-// has left call k (launches of one communicator are stream-ordered); barrier-based kernels in between synchronise
-// all ranks anyway. The tag is the call index + 1 (never 0, the value of cleared memory) and differs from the tag
+// rank (directly, or through a shard owner that did), so a rank can only FINISH call k+1 after every peer has
+// STARTED sending in call k+1, i.e. after every peer has left call k (launches of one communicator are
+// stream-ordered); barrier-based kernels in between synchronise all ranks anyway. The tag is the call index + 1 (never 0, the value of cleared memory) and differs from the tag
 // that the same slot held two calls earlier.
 //
 // all-to-all:      send segment q to rank q       | receive segment s from rank s into slot s of the output
@@ -68,7 +70,10 @@ __device__ __forceinline__ bool llRecv(const HlCommDev& c, const uint8_t* slot, 
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3) : "l"(p) : "memory");
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "l"(p + 512) : "memory");
     if (a1 == tag && a3 == tag && b1 == tag && b3 == tag) break;
-    if ((++spins & 63u) == 0) {
+    // a late peer (milliseconds, when the call overlaps with compute) must not have thousands of threads hammer L2
+    // (an ordinary wait is a handful of polls and never gets here)
+    if (++spins > 64) __nanosleep(spins > 1024 ? 400 : 50);
+    if ((spins & 63u) == 0) {
       const uint64_t now = globalTimerNs();
       if (w.t0 == 0) w.t0 = now;
       const bool aborted = *reinterpret_cast<volatile uint32_t*>(c.abort_word) != 0;

@@ -563,6 +563,9 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
   if (!asked && c.algo != hlAlgoAuto) return 0;
   const int no = asked ? -1 : 0;
   if (!ll_slot_bytes_ || nranks_ < 2) return no;
+  // A call with a small CTA budget overlaps with compute kernels and may wait long for a late peer: thousands of
+  // polling threads are the wrong neighbour for a GEMM; the barrier-based kernels wait with n threads per CTA.
+  if (!asked && c.max_blocks > 0 && c.max_blocks <= 64) return 0;
   if (!asked) {
     // Measured on 4 GPUs (kernel time from the timeline, bf16; barrier-based zero-copy kernel -> this one): 64 KiB
     // reduce-scatter 12.1 -> 4.2 us, all-gather 10.1 -> 6.8; 1 MiB all-reduce 18.0 -> 12.4, reduce-scatter 19.8 -> 8.2,

@@ -62,7 +62,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=0, help="0 = by size")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--check", action="store_true")
-    ap.add_argument("--algo", default="auto", help="auto|oneshot|twoshot|nvls|pipelined|push")
+    ap.add_argument("--algo", default="auto", help="auto|oneshot|twoshot|nvls|pipelined|push|zerocopy|zerocopy_nvls|zerocopy_p2p|ll")
     ap.add_argument("--path", default="nvlink", help="nvlink|pcie|split|auto")
     ap.add_argument("--blocks", dest="max_blocks", type=int, default=0)
     ap.add_argument("--deterministic", action="store_true")
@@ -127,7 +127,7 @@ def main(argv=None) -> int:
                     ref = lambda i: dist.reduce_scatter_tensor(bufs(i)[1][:seg], bufs(i)[0])
                 elif coll == "allgather":
                     ours = lambda i: comm.all_gather(bufs(i)[0][:seg], bufs(i)[1], path=a.path, max_blocks=a.max_blocks,
-                                                     algo=a.algo if a.algo in ("twoshot", "pipelined", "nvls") else "auto")
+                                                     algo=a.algo if a.algo in ("twoshot", "pipelined", "nvls", "ll", "zerocopy", "zerocopy_nvls", "zerocopy_p2p") else "auto")
                     ref = lambda i: dist.all_gather_into_tensor(bufs(i)[1], bufs(i)[0][:seg])
                 elif coll == "alltoall":
                     ours = lambda i: comm.all_to_all(bufs(i)[0], bufs(i)[1], path=a.path, max_blocks=a.max_blocks)
