@@ -3,6 +3,7 @@
     python -m hylink_b200.utils.compare sweeps nccl_vs_ours.jsonl [more.jsonl ...] [--csv out.csv] [--md out.md]
     python -m hylink_b200.utils.compare logs run.log [--csv per_call.csv]
     python -m hylink_b200.utils.compare pipeline --gpus 2,4,8 --out results/ [--bytes-from 1K --bytes-to 1G --factor 4]
+    python -m hylink_b200.utils.compare plot nvlink_2gpu.jsonl adaptive_2gpu.jsonl ... --out charts/ [--dtype bf16]
 
 * ``sweeps`` merges the JSON lines written by ``hylink_b200.utils.sweep`` (one file per configuration, the file
   name is the label) into one table: a row per (collective, dtype, bytes, ranks), the bus bandwidth of every
@@ -12,6 +13,9 @@
   path, the split, per-path and bus bandwidth. The wording of those lines is the reference's
   (multipath-orchestrator/libampccl/core/shm_store.cc:372-412), so its own post-processor
   (tests/nccl_test/test_scripts/process_compare_logs.py:36-38) reads them too.
+* ``plot`` draws one chart per collective from sweep files (bus bandwidth against message size, log x axis, one
+  line per file plus NCCL's per rank count) as plain SVG, written without any plotting library
+  (tests/nccl_test/test_scripts/plot_bw_comparison.py in the reference, which needs matplotlib). ``pipeline`` calls it.
 * ``pipeline`` runs the sweep for every GPU count in two configurations — NVLink kernels only, and the adaptive
   multipath split — each against NCCL in the same process, and merges the results
   (tests/nccl_test/test_scripts/run_full_pipeline.sh in the reference: baseline vs adaptive x {AG, AR, RS} x
@@ -108,6 +112,99 @@ def write_sweep_tables(labels, table, csv_path=None, md_path=None, out=sys.stdou
     return rows
 
 
+_COLOURS = ["#1f77b4", "#d62728", "#2ca02c", "#9467bd", "#ff7f0e", "#8c564b", "#17becf", "#7f7f7f", "#bcbd22", "#e377c2"]
+
+
+def _size_label(b: int) -> str:
+    for unit, sh in (("G", 30), ("M", 20), ("K", 10)):
+        if b >= 1 << sh:
+            v = b / (1 << sh)
+            return (f"{v:.0f}" if v == int(v) else f"{v:.1f}") + unit
+    return str(b)
+
+
+def svg_chart(title: str, series: dict, path: str, width: int = 860, height: int = 480) -> None:
+    """series: label -> [(bytes, GB/s), ...]. Log2 x axis, linear y axis, dashed lines for labels that start with
+    'NCCL'. Plain SVG text, no dependencies."""
+    import math
+
+    pts = [p for v in series.values() for p in v]
+    if not pts:
+        return
+    x0, x1 = math.log2(min(p[0] for p in pts)), math.log2(max(p[0] for p in pts))
+    if x1 == x0:
+        x1 = x0 + 1
+    ymax = max(p[1] for p in pts) * 1.08 or 1.0
+    step = 10 ** math.floor(math.log10(ymax / 4))
+    step = step * (5 if ymax / step > 20 else (2 if ymax / step > 8 else 1))
+    ml, mr, mt, mb = 64, 190, 40, 48
+    pw, ph = width - ml - mr, height - mt - mb
+
+    def sx(b):
+        return ml + (math.log2(b) - x0) / (x1 - x0) * pw
+
+    def sy(v):
+        return mt + ph - v / ymax * ph
+
+    o = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" font-family="sans-serif" font-size="12">',
+         f'<rect width="{width}" height="{height}" fill="white"/>',
+         f'<text x="{ml + pw / 2}" y="22" text-anchor="middle" font-size="15">{title}</text>',
+         f'<rect x="{ml}" y="{mt}" width="{pw}" height="{ph}" fill="none" stroke="#444"/>']
+    v = 0.0
+    while v <= ymax:
+        y = sy(v)
+        o.append(f'<line x1="{ml}" y1="{y:.1f}" x2="{ml + pw}" y2="{y:.1f}" stroke="#ddd"/>')
+        o.append(f'<text x="{ml - 6}" y="{y + 4:.1f}" text-anchor="end">{v:g}</text>')
+        v += step
+    xs = sorted({p[0] for p in pts})
+    every = max(1, len(xs) // 10)
+    for i, b in enumerate(xs):
+        if i % every:
+            continue
+        x = sx(b)
+        o.append(f'<line x1="{x:.1f}" y1="{mt + ph}" x2="{x:.1f}" y2="{mt + ph + 5}" stroke="#444"/>')
+        o.append(f'<text x="{x:.1f}" y="{mt + ph + 20}" text-anchor="middle">{_size_label(b)}</text>')
+    o.append(f'<text x="{ml + pw / 2}" y="{height - 8}" text-anchor="middle">message size (bytes)</text>')
+    o.append(f'<text x="16" y="{mt + ph / 2}" text-anchor="middle" transform="rotate(-90 16 {mt + ph / 2})">bus bandwidth (GB/s)</text>')
+    for i, (label, data) in enumerate(series.items()):
+        col = _COLOURS[i % len(_COLOURS)]
+        data = sorted(data)
+        dash = ' stroke-dasharray="6 4"' if label.startswith("NCCL") else ""
+        o.append(f'<polyline fill="none" stroke="{col}" stroke-width="2"{dash} points="' +
+                 " ".join(f"{sx(b):.1f},{sy(v):.1f}" for b, v in data) + '"/>')
+        for b, v in data:
+            o.append(f'<circle cx="{sx(b):.1f}" cy="{sy(v):.1f}" r="3" fill="{col}"/>')
+        ly = mt + 14 + 18 * i
+        o.append(f'<line x1="{ml + pw + 12}" y1="{ly - 4}" x2="{ml + pw + 36}" y2="{ly - 4}" stroke="{col}" stroke-width="2"{dash}/>')
+        o.append(f'<text x="{ml + pw + 42}" y="{ly}">{label}</text>')
+    o.append("</svg>")
+    with open(path, "w") as fh:
+        fh.write("\n".join(o) + "\n")
+
+
+def plot_sweeps(files, out_dir: str, dtype: str = "bf16"):
+    """One SVG per collective: a line per (file label, rank count) and NCCL's line per rank count."""
+    os.makedirs(out_dir, exist_ok=True)
+    labels, table = merge_sweeps(files)
+    charts = {}
+    for (coll, dt, nbytes, n), row in table.items():
+        if dt != dtype:
+            continue
+        series = charts.setdefault(coll, {})
+        for l in labels:
+            if l in row:
+                name = l if l.endswith("gpu") else f"{l} ({n} GPUs)"
+                series.setdefault(name, []).append((nbytes, row[l]))
+        if row.get("nccl"):
+            series.setdefault(f"NCCL ({n} GPUs)", []).append((nbytes, row["nccl"]))
+    written = []
+    for coll, series in sorted(charts.items()):
+        path = os.path.join(out_dir, f"busbw_{coll}_{dtype}.svg")
+        svg_chart(f"{coll} - bus bandwidth ({dtype})", dict(sorted(series.items())), path)
+        written.append(path)
+    return written
+
+
 def run_pipeline(args) -> int:
     os.makedirs(args.out, exist_ok=True)
     produced = []
@@ -129,6 +226,9 @@ def run_pipeline(args) -> int:
     labels, table = merge_sweeps(produced)
     write_sweep_tables(labels, table, os.path.join(args.out, "summary.csv"), os.path.join(args.out, "summary.md"))
     print("wrote", os.path.join(args.out, "summary.csv"))
+    for dt in args.dtypes.split(","):
+        for path in plot_sweeps(produced, args.out, dt):
+            print("wrote", path)
     return 0
 
 
@@ -152,7 +252,15 @@ def main(argv=None) -> int:
     p.add_argument("--factor", type=int, default=4)
     p.add_argument("--iters", type=int, default=0)
     p.add_argument("--port", type=int, default=29671)
+    p = sub.add_parser("plot")
+    p.add_argument("files", nargs="+")
+    p.add_argument("--out", default=".")
+    p.add_argument("--dtype", default="bf16")
     args = ap.parse_args(argv)
+    if args.cmd == "plot":
+        for path in plot_sweeps(args.files, args.out, args.dtype):
+            print("wrote", path)
+        return 0
     if args.cmd == "sweeps":
         labels, table = merge_sweeps(args.files)
         write_sweep_tables(labels, table, args.csv, args.md)

@@ -103,6 +103,32 @@ def test_sweep_files_merge_into_one_table(tmp_path):
     assert "nvlink_2gpu/NCCL" in (tmp_path / "s.md").read_text()
 
 
+def test_sweep_files_plot_as_svg_without_a_plotting_library(tmp_path):
+    import json
+    import xml.dom.minidom
+
+    from hylink_b200.utils import compare
+
+    def rows(scale, n):
+        return "\n".join(json.dumps({"coll": c, "dtype": "bf16", "bytes": 1 << s, "n": n, "ms": 0.1, "busbw_GBs": scale * s,
+                                     "nccl_ms": 0.1, "nccl_busbw_GBs": 0.8 * scale * s, "speedup": 1.25, "ok": True,
+                                     "algo": "auto", "path": "x"}) for c in ("allreduce", "allgather") for s in range(10, 31, 4)) + "\n"
+
+    (tmp_path / "nvlink_2gpu.jsonl").write_text(rows(10.0, 2))
+    (tmp_path / "nvlink_4gpu.jsonl").write_text(rows(12.0, 4))
+    out = tmp_path / "charts"
+    assert compare.main(["plot", str(tmp_path / "nvlink_2gpu.jsonl"), str(tmp_path / "nvlink_4gpu.jsonl"), "--out", str(out)]) == 0
+    files = sorted(p.name for p in out.iterdir())
+    assert files == ["busbw_allgather_bf16.svg", "busbw_allreduce_bf16.svg"]
+    doc = xml.dom.minidom.parse(str(out / "busbw_allreduce_bf16.svg"))
+    lines = doc.getElementsByTagName("polyline")
+    assert len(lines) == 4                                   # two runs and NCCL's line for each rank count
+    assert sum(1 for l in lines if l.getAttribute("stroke-dasharray")) == 2
+    assert all(len(l.getAttribute("points").split()) == 6 for l in lines)
+    labels = [t.firstChild.data for t in doc.getElementsByTagName("text") if t.firstChild]
+    assert "nvlink_2gpu" in labels and "NCCL (4 GPUs)" in labels and "1G" in labels
+
+
 def test_kernel_timeline_decoder_on_a_synthetic_ring():
     from hylink_b200.utils import kernel_timeline as kt
 
