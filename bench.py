@@ -156,6 +156,7 @@ class Table:
         self.dtype, self.sizes, self.world, self.group = dtype, sizes, world, group
         self.es = torch.empty((), dtype=dtype).element_size()
         self.cells = [(c, s) for c in COLLS for s in sizes]
+        self._views = {}
         top = max(sizes)
         self.slots = 2
         # rotating buffers: between two timed calls of one cell a whole pass (> 4 GiB of traffic) goes through L2
@@ -197,15 +198,22 @@ class Table:
     def call(self, coll, nbytes, it):
         import torch.distributed as dist
 
-        n_el, seg = self.elems(nbytes)
-        a, b = self.inp[it % self.slots], self.out[it % self.slots]
+        # the views of a cell are made once: slicing a tensor costs a microsecond or two of host time, which is all
+        # there is to a collective of one rank
+        key = (coll, nbytes, it % self.slots)
+        v = self._views.get(key)
+        if v is None:
+            n_el, seg = self.elems(nbytes)
+            a, b = self.inp[it % self.slots], self.out[it % self.slots]
+            v = self._views[key] = (a, b, a[:n_el], a[:seg], b[:n_el], b[:seg])
+        a, b, a_all, a_seg, b_all, b_seg = v
         if coll == "allreduce":
-            dist.all_reduce(a[:n_el], group=self.group)     # in place, as torch.distributed defines it
+            dist.all_reduce(a_all, group=self.group)        # in place, as torch.distributed defines it
             return a
         if coll == "reducescatter":
-            dist.reduce_scatter_tensor(b[:seg], a[:n_el], group=self.group)
+            dist.reduce_scatter_tensor(b_seg, a_all, group=self.group)
             return b
-        dist.all_gather_into_tensor(b[:n_el], a[:seg], group=self.group)
+        dist.all_gather_into_tensor(b_all, a_seg, group=self.group)
         return b
 
 
@@ -249,19 +257,27 @@ def e2e_passes(tab: Table, steps: int):
     host.uniform_(-1, 1)
     back = torch.empty(4096 // tab.es, dtype=tab.dtype).pin_memory()
     sums = [0.0] * len(tab.cells)
+    stream = torch.cuda.current_stream()
+    # views made once per (cell, buffer slot): the timed region holds the copies and the call, not tensor slicing
+    plan = {}
+    for ci, (coll, nbytes) in enumerate(tab.cells):
+        n_el, seg = tab.elems(nbytes)
+        k = seg if coll == "allgather" else n_el
+        for slot in range(tab.slots):
+            res = tab.inp[slot] if coll == "allreduce" else tab.out[slot]
+            plan[(ci, slot)] = (tab.inp[slot][:k], host[:k], res[:back.numel()])
     for it in range(2 + steps):
         for ci, (coll, nbytes) in enumerate(tab.cells):
-            n_el, seg = tab.elems(nbytes)
-            k = seg if coll == "allgather" else n_el
             if it == 2 and ci == 0:
                 torch.cuda.synchronize()
                 dist.barrier()
                 torch.cuda.synchronize()
+            dst, src, res = plan[(ci, it % tab.slots)]
             t0 = time.perf_counter()
-            tab.inp[it % tab.slots][:k].copy_(host[:k], non_blocking=True)
-            res = tab.call(coll, nbytes, it)
-            back.copy_(res[:back.numel()], non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            dst.copy_(src, non_blocking=True)
+            tab.call(coll, nbytes, it)
+            back.copy_(res, non_blocking=True)
+            stream.synchronize()
             if it >= 2:
                 sums[ci] += (time.perf_counter() - t0) * 1e3
     h2d = sum(tab.input_bytes(c, s) for c, s in tab.cells)
