@@ -208,9 +208,36 @@ def run_single(steps: int, warmup: int, colls, sizes, e2e: bool = True) -> dict:
     return res
 
 
+def probe_multi(n: int) -> None:
+    """One small pass of the reference on n GPUs in a CHILD process. The library ends the process with abort() on some
+    set-up failures (host pool, schedule lookup); in a child that becomes an error message here instead of the end
+    of the caller. Raises RuntimeError with the child's last words when it did not get through."""
+    import subprocess
+    import sys
+
+    cmd = [sys.executable, str(Path(__file__).resolve()), "--probe", str(n)]
+    try:
+        p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+    except subprocess.TimeoutExpired:
+        raise RuntimeError(f"a one-pass trial of the reference on {n} GPUs did not finish within 300 s") from None
+    if p.returncode != 0 or "PROBE OK" not in p.stdout:
+        tail = " ".join((p.stderr or p.stdout)[-400:].split())
+        raise RuntimeError(f"a one-pass trial of the reference on {n} GPUs ended with exit code {p.returncode}: {tail}")
+
+
 def run(n: int, steps: int, warmup: int, colls, sizes, e2e: bool = True) -> dict:
     if n == 1:
         return run_single(steps, warmup, colls, sizes, e2e)
     if n not in NUMA_MAPS:
         raise RuntimeError(f"the reference ships no schedule set for {n} GPUs (it has 2, 4 and 8)")
+    if os.environ.get("HYLINK_REFERENCE_PROBE", "1") != "0":
+        probe_multi(n)
     return run_multi(n, steps, warmup, colls, sizes, e2e)
+
+
+if __name__ == "__main__":
+    import sys
+
+    if len(sys.argv) == 3 and sys.argv[1] == "--probe":
+        run_multi(int(sys.argv[2]), 1, 1, ("allreduce", "reducescatter", "allgather"), [1 << 20, 64 << 20], e2e=False)
+        print("PROBE OK", flush=True)

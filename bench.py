@@ -359,7 +359,16 @@ def reference_arm(args, rank: int, world: int) -> int:
         sampler = ClockSampler(0)
         sampler.start()
         sampler.mark_begin()
-        res = ref.run(n, args.steps, args.warmup, COLLS, sizes, e2e=True)
+        # the library logs to stdout from C: keep stdout for the one JSON line, send its log lines to stderr
+        sys.stdout.flush()
+        saved_out = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            res = ref.run(n, args.steps, args.warmup, COLLS, sizes, e2e=True)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_out, 1)
+            os.close(saved_out)
         sampler.mark_end()
         clocks = sampler.stop()
     except Exception as ex:  # noqa: BLE001 - whatever stopped the reference is the answer
