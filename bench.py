@@ -367,6 +367,12 @@ def reference_arm(args, rank: int, world: int) -> int:
             res = ref.run(n, args.steps, args.warmup, COLLS, sizes, e2e=True)
         finally:
             sys.stdout.flush()
+            try:   # what the library left in the C library's stdout buffer goes the same way
+                import ctypes
+
+                ctypes.CDLL(None).fflush(None)
+            except (OSError, AttributeError):
+                pass
             os.dup2(saved_out, 1)
             os.close(saved_out)
         sampler.mark_end()
