@@ -359,22 +359,7 @@ def reference_arm(args, rank: int, world: int) -> int:
         sampler = ClockSampler(0)
         sampler.start()
         sampler.mark_begin()
-        # the library logs to stdout from C: keep stdout for the one JSON line, send its log lines to stderr
-        sys.stdout.flush()
-        saved_out = os.dup(1)
-        os.dup2(2, 1)
-        try:
-            res = ref.run(n, args.steps, args.warmup, COLLS, sizes, e2e=True)
-        finally:
-            sys.stdout.flush()
-            try:   # what the library left in the C library's stdout buffer goes the same way
-                import ctypes
-
-                ctypes.CDLL(None).fflush(None)
-            except (OSError, AttributeError):
-                pass
-            os.dup2(saved_out, 1)
-            os.close(saved_out)
+        res = ref.run(n, args.steps, args.warmup, COLLS, sizes, e2e=True)
         sampler.mark_end()
         clocks = sampler.stop()
     except Exception as ex:  # noqa: BLE001 - whatever stopped the reference is the answer
@@ -553,5 +538,37 @@ def main() -> int:
     return 0
 
 
+def _main_with_clean_stdout() -> int:
+    """Libraries underneath print to stdout from C (NCCL its version line, the reference its log): everything that is
+    not a JSON record of this script goes to stderr, so that stdout carries the record alone."""
+    import builtins
+    import ctypes
+
+    sys.stdout.flush()
+    real_out = os.dup(1)
+    os.dup2(2, 1)
+    plain_print = builtins.print
+
+    def record_print(*a, **kw):
+        text = " ".join(str(x) for x in a)
+        if kw.get("file") is None and text.startswith("{"):
+            os.write(real_out, (text + "\n").encode())
+        else:
+            plain_print(*a, **kw)
+
+    builtins.print = record_print
+    try:
+        return main()
+    finally:
+        builtins.print = plain_print
+        sys.stdout.flush()
+        try:
+            ctypes.CDLL(None).fflush(None)
+        except (OSError, AttributeError):
+            pass
+        os.dup2(real_out, 1)
+        os.close(real_out)
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    sys.exit(_main_with_clean_stdout())
