@@ -23,8 +23,7 @@
 // reduce-scatter:  send segment q to rank q       | receive n-1 contributions, add in rank order, store
 // all-reduce:      reduce-scatter of the n shards (phase 0), then all-gather of the reduced shards (phase 1)
 //
-// Buffers: any device memory, 16-byte aligned, whole 16-byte packets (the host side sends everything else to the
-// other kernels); no type conversion. Sum order is by rank index on every rank: results are bitwise identical
+// Buffers: any device memory, any alignment, any element count; no type conversion. Sum order is by rank index on every rank: results are bitwise identical
 // across ranks and runs.
 //
 // The reference has no kernels of its own on this path (it calls the vendor library:
@@ -112,9 +111,13 @@ __device__ __forceinline__ uint4 llReduce(const uint4* v, int n, int op, float s
   return Packet<W>::pack(acc);
 }
 
-// `count`: elements of the whole buffer (all-reduce) or of one segment (reduce-scatter, all-gather); a whole number
-// of 16-byte packets. Every thread keeps the same packet indices in every loop of the kernel, which is what makes
-// the in-place forms safe (a location is read by the thread that later overwrites it, earlier in program order).
+// `count`: elements of the whole buffer (all-reduce) or of one segment (the others). User buffers may have any
+// alignment and any element count: packets are loaded and stored through loadUserPacket / storeUserPacket (vector
+// accesses when the segment is 16-byte aligned and the packet whole, element by element otherwise; lanes past the
+// end travel as zeros and are never stored). Whether a call takes these kernels therefore depends on sizes and
+// types only, which are the same on every rank - never on a pointer, which need not be.
+// Every thread keeps the same packet indices in every loop of the kernel, which is what makes the in-place forms
+// safe (a location is read by the thread that later overwrites it, earlier in program order).
 template <typename W, int kColl>
 __global__ void __launch_bounds__(HL_NVL_THREADS) kLowLatency(const HlCommDev* comms, HlEmuCalls calls) {
   const HlCommDev& c = comms[blockIdx.y];
@@ -126,65 +129,66 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kLowLatency(const HlCommDev* c
   const uint64_t call = a.seq / HL_SEQ_STRIDE;
   const uint32_t tag = (uint32_t)(call % 0xfffffffeull) + 1u;
   const int parity = (int)(call & 1);
-  const uint4* in = reinterpret_cast<const uint4*>(a.in);
-  uint4* out = reinterpret_cast<uint4*>(a.out);
-  const uint64_t np = a.count / N;
+  const W* in = reinterpret_cast<const W*>(a.in);
+  W* out = reinterpret_cast<W*>(a.out);
+  const uint64_t cnt = a.count;
+  const uint64_t np = (cnt + N - 1) / N;
+  // packet j of the segment that starts at element `base` of a buffer
+  auto ld = [&](const W* seg, uint64_t j) { return loadUserPacket<W, W>(seg, j * N, cnt, aligned16(seg)); };
+  auto st = [&](W* seg, uint64_t j, const uint4& v) { storeUserPacket<W, W>(seg, j * N, cnt, aligned16(seg), v); };
   LlWait w;
   w.t0 = 0;
   w.ok = true;
   if constexpr (kColl == kLlAllGather) {
-    const uint64_t ostride = a.out_seg_stride / N;
     for (uint64_t j = g0; j < np; j += gstride) {
-      const uint4 v = in[j];
+      const uint4 v = ld(in, j);
       for (int k = 1; k < n; ++k) llSend(llSlot(c, (r + k) % n, parity, 0, r), j, v, tag);
-      out[(uint64_t)r * ostride + j] = v;
+      st(out + (uint64_t)r * a.out_seg_stride, j, v);
     }
     for (uint64_t j = g0; j < np && w.ok; j += gstride)
       for (int k = 1; k < n; ++k) {
         const int s = (r + n - k) % n;
         uint4 v;
         if (!llRecv(c, llSlot(c, r, parity, 0, s), j, tag, s, w, &v)) break;
-        out[(uint64_t)s * ostride + j] = v;
+        st(out + (uint64_t)s * a.out_seg_stride, j, v);
       }
   } else if constexpr (kColl == kLlAllToAll) {
-    const uint64_t istride = a.in_seg_stride / N, ostride = a.out_seg_stride / N;
     for (uint64_t j = g0; j < np; j += gstride) {
       uint4 own;
       for (int k = 0; k < n; ++k) {
         const int q = (r + k) % n;
-        const uint4 v = in[(uint64_t)q * istride + j];
+        const uint4 v = ld(in + (uint64_t)q * a.in_seg_stride, j);
         if (k == 0) own = v;
         else llSend(llSlot(c, q, parity, 0, r), j, v, tag);
       }
-      out[(uint64_t)r * ostride + j] = own;   // after every read of this thread's column: in place is safe
+      st(out + (uint64_t)r * a.out_seg_stride, j, own);   // after every read of this thread's column: in place is safe
     }
     for (uint64_t j = g0; j < np && w.ok; j += gstride)
       for (int k = 1; k < n; ++k) {
         const int s = (r + n - k) % n;
         uint4 v;
         if (!llRecv(c, llSlot(c, r, parity, 0, s), j, tag, s, w, &v)) break;
-        out[(uint64_t)s * ostride + j] = v;
+        st(out + (uint64_t)s * a.out_seg_stride, j, v);
       }
   } else if constexpr (kColl == kLlReduceScatter) {
-    const uint64_t istride = a.in_seg_stride / N;
     for (uint64_t j = g0; j < np; j += gstride)
       for (int k = 1; k < n; ++k) {
         const int q = (r + k) % n;
-        llSend(llSlot(c, q, parity, 0, r), j, in[(uint64_t)q * istride + j], tag);
+        llSend(llSlot(c, q, parity, 0, r), j, ld(in + (uint64_t)q * a.in_seg_stride, j), tag);
       }
     for (uint64_t j = g0; j < np && w.ok; j += gstride) {
       uint4 v[HL_MAX_RANKS];   // indexed by compile-time constants only: stays in registers
 #pragma unroll
       for (int q = 0; q < HL_MAX_RANKS; ++q)
         if (q < n) {
-          if (q == r) v[q] = in[(uint64_t)r * istride + j];
+          if (q == r) v[q] = ld(in + (uint64_t)r * a.in_seg_stride, j);
           else if (w.ok) llRecv(c, llSlot(c, r, parity, 0, q), j, tag, q, w, &v[q]);
         }
       if (!w.ok) break;
-      out[j] = llReduce<W>(v, n, a.op, a.scale, a.int_div);
+      st(out, j, llReduce<W>(v, n, a.op, a.scale, a.int_div));
     }
   } else {
-    // shard q = packets [q * sp, min(np, (q + 1) * sp)); rank q reduces it
+    // shard q = packets [q * sp, min(np, (q + 1) * sp)) of the whole buffer; rank q reduces it
     const uint64_t sp = (np + n - 1) / n;
     const uint64_t first = (uint64_t)r * sp;
     const uint64_t mine = first >= np ? 0 : (np - first < sp ? np - first : sp);
@@ -192,20 +196,20 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kLowLatency(const HlCommDev* c
       for (int k = 1; k < n; ++k) {
         const int q = (r + k) % n;
         const uint64_t e = (uint64_t)q * sp + j;
-        if (e < np) llSend(llSlot(c, q, parity, 0, r), j, in[e], tag);
+        if (e < np) llSend(llSlot(c, q, parity, 0, r), j, ld(in, e), tag);
       }
     for (uint64_t j = g0; j < mine && w.ok; j += gstride) {
       uint4 v[HL_MAX_RANKS];
 #pragma unroll
       for (int q = 0; q < HL_MAX_RANKS; ++q)
         if (q < n) {
-          if (q == r) v[q] = in[first + j];
+          if (q == r) v[q] = ld(in, first + j);
           else if (w.ok) llRecv(c, llSlot(c, r, parity, 0, q), j, tag, q, w, &v[q]);
         }
       if (!w.ok) break;
       const uint4 red = llReduce<W>(v, n, a.op, a.scale, a.int_div);
       for (int k = 1; k < n; ++k) llSend(llSlot(c, (r + k) % n, parity, 1, r), j, red, tag);
-      out[first + j] = red;
+      st(out, first + j, red);
     }
     for (uint64_t j = g0; j < sp && w.ok; j += gstride)
       for (int k = 1; k < n; ++k) {
@@ -214,7 +218,7 @@ __global__ void __launch_bounds__(HL_NVL_THREADS) kLowLatency(const HlCommDev* c
         if (e >= np) continue;
         uint4 v;
         if (!llRecv(c, llSlot(c, r, parity, 1, s), j, tag, s, w, &v)) break;
-        out[e] = v;
+        st(out, e, v);
       }
   }
   // a thread that gave up has poisoned the communicator; the others find the abort word in their own waits

@@ -582,15 +582,16 @@ int NvlPath::lowLatencyChoice(const NvlBufs& b, const NvlCall& c, int coll, size
   if (!ws) return no;
   const uint64_t epp = 16 / ws;
   const uint64_t istride = c.in_seg_stride ? c.in_seg_stride : c.count, ostride = c.out_seg_stride ? c.out_seg_stride : c.count;
-  if (c.count % epp || ((coll == 1 || coll == 3) && istride % epp) || ((coll == 2 || coll == 3) && ostride % epp)) return no;
-  const uint64_t np = c.count / epp;
+  // Nothing below depends on a pointer's alignment or on the count being whole packets: ranks must agree on the
+  // kernel, and only sizes and types are the same on all of them by the definition of a collective.
+  const uint64_t np = (c.count + epp - 1) / epp;
   const uint64_t per_src = coll == 0 ? (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_ : np;   // packets one rank sends to one peer
   if (((per_src + 31) / 32) * 1024 > ll_slot_bytes_) return no;   // packets are stored in groups of 32 (1 KiB)
   const size_t n = (size_t)nranks_;
   for (int i = 0; i < localRanks(); ++i) {
     const char* in = (const char*)b.in[i];
     const char* out = (const char*)b.out[i];
-    if (!in || !out || (((uintptr_t)in | (uintptr_t)out) & 15)) return no;
+    if (!in || !out) return no;
     // in place only where every location is read by the thread that later overwrites it
     if (coll == 0) {
       if (in != out && !disjoint(in, c.count * ws, out, c.count * ws)) return no;
@@ -650,9 +651,9 @@ hlResult_t NvlPath::allReduce(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
   {
     const int ll = lowLatencyChoice(b, c, 0, wire_bytes);
-    if (ll < 0) return fail(hlUnsupported, "all-reduce: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
+    if (ll < 0) return fail(hlUnsupported, "all-reduce: the low-latency kernel converts no types and needs a message that fits its slots");
     if (ll > 0) {
-      const uint64_t np = wire_bytes / 16;
+      const uint64_t np = (wire_bytes + 15) / 16;
       return launchLowLatency(kNvlLlAllReduce, b, c, (np + (uint64_t)nranks_ - 1) / (uint64_t)nranks_, s);
     }
   }
@@ -693,8 +694,8 @@ hlResult_t NvlPath::reduceScatter(const NvlBufs& b, const NvlCall& c, cudaStream
   const size_t wire_bytes = c.count * hlTypeSize((hlDataType_t)c.wire_dt) * (size_t)nranks_;
   {
     const int ll = lowLatencyChoice(b, c, 1, wire_bytes);
-    if (ll < 0) return fail(hlUnsupported, "reduce-scatter: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
-    if (ll > 0) return launchLowLatency(kNvlLlReduceScatter, b, c, wire_bytes / (size_t)nranks_ / 16, s);
+    if (ll < 0) return fail(hlUnsupported, "reduce-scatter: the low-latency kernel converts no types and needs a message that fits its slots");
+    if (ll > 0) return launchLowLatency(kNvlLlReduceScatter, b, c, (wire_bytes / (size_t)nranks_ + 15) / 16, s);
   }
   {
     uint64_t io, oo;
@@ -725,8 +726,8 @@ hlResult_t NvlPath::allGather(const NvlBufs& b, const NvlCall& c, cudaStream_t s
   {
     const size_t seg_wire = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
     const int ll = lowLatencyChoice(b, c, 2, seg_wire * (size_t)nranks_);
-    if (ll < 0) return fail(hlUnsupported, "all-gather: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
-    if (ll > 0) return launchLowLatency(kNvlLlAllGather, b, c, seg_wire / 16, s);
+    if (ll < 0) return fail(hlUnsupported, "all-gather: the low-latency kernel converts no types and needs a message that fits its slots");
+    if (ll > 0) return launchLowLatency(kNvlLlAllGather, b, c, (seg_wire + 15) / 16, s);
   }
   {
     uint64_t io, oo;
@@ -766,8 +767,8 @@ hlResult_t NvlPath::allToAll(const NvlBufs& b, const NvlCall& c, cudaStream_t s)
   {
     const size_t seg_wire = c.count * hlTypeSize((hlDataType_t)c.wire_dt);
     const int ll = lowLatencyChoice(b, c, 3, seg_wire * (size_t)nranks_);
-    if (ll < 0) return fail(hlUnsupported, "all-to-all: the low-latency kernel needs 16-byte aligned buffers of whole 16-byte packets, no conversion, and a message that fits its slots");
-    if (ll > 0) return launchLowLatency(kNvlLlAllToAll, b, c, seg_wire / 16, s);
+    if (ll < 0) return fail(hlUnsupported, "all-to-all: the low-latency kernel converts no types and needs a message that fits its slots");
+    if (ll > 0) return launchLowLatency(kNvlLlAllToAll, b, c, (seg_wire + 15) / 16, s);
   }
   return launchSliced(kNvlAllToAll, b, c, true, s);
 }

@@ -157,16 +157,56 @@ def test_auto_takes_the_low_latency_kernels_for_small_messages_and_mixes_with_th
 
 def test_named_request_is_refused_when_the_call_does_not_qualify():
     g = _group(2, stage_bytes=1 << 20)
-    ins = [torch.ones(1001, dtype=torch.float32, device="cuda") for _ in range(2)]     # not whole 16-byte packets
-    outs = [torch.empty_like(t) for t in ins]
-    with pytest.raises(RuntimeError):
-        g.run("all_reduce", ins, outs, 1001, algo="ll")
     big = [torch.ones(8 << 20, dtype=torch.float32, device="cuda") for _ in range(2)]  # 32 MiB: no slot holds it
     with pytest.raises(RuntimeError):
         g.run("all_reduce", big, [torch.empty_like(t) for t in big], 8 << 20, algo="ll")
-    g.run("all_reduce", ins, outs, 1001)                                               # the default still serves it
-    torch.cuda.synchronize()
-    assert torch.equal(outs[0], torch.full((1001,), 2.0, device="cuda"))
+    with pytest.raises(RuntimeError):                                                  # no type conversion
+        g.run("all_reduce", [t[:4096] for t in big], [torch.empty(4096, dtype=torch.bfloat16, device="cuda") for _ in range(2)], 4096, algo="ll")
+    g.close()
+
+
+@pytest.mark.parametrize("n", [2, 4])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_any_alignment_and_any_count(n, dtype):
+    """Which kernel a call takes must not depend on a pointer (ranks need not agree on those): views that start in
+    the middle of a packet and counts that end in one go through the same kernels."""
+    g = _group(n, stage_bytes=1 << 20)
+    es = torch.empty((), dtype=dtype).element_size()
+    epp = 16 // es
+    for count, off_in, off_out in [(1, 0, 0), (epp + 1, 1, 0), (1001, 0, 3), (4099 * epp + 5, 1, 1)]:
+        base = _inputs(n, count + off_in, dtype, count)
+        ins = [t[off_in:] for t in base]
+        outs = [torch.full((count + off_out + epp,), 7, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("all_reduce", ins, [o[off_out:off_out + count] for o in outs], count, algo="ll")
+        torch.cuda.synchronize()
+        ref = _ordered_sum(ins, dtype)
+        for o in outs:
+            assert torch.equal(o[off_out:off_out + count], ref), (n, dtype, count, off_in, off_out)
+            assert bool((o[:off_out] == 7).all()) and bool((o[off_out + count:] == 7).all()), "wrote outside the buffer"
+        # reduce-scatter and all-gather with segments that are neither aligned nor whole packets
+        seg = count
+        full = _inputs(n, seg * n + off_in, dtype, count + 1)
+        fin = [t[off_in:] for t in full]
+        want = _ordered_sum(fin, dtype)
+        parts = [torch.full((seg + off_out + epp,), 7, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("reduce_scatter", fin, [p[off_out:off_out + seg] for p in parts], seg, in_seg_stride=seg, algo="ll")
+        torch.cuda.synchronize()
+        for r, p in enumerate(parts):
+            assert torch.equal(p[off_out:off_out + seg], want[r * seg:(r + 1) * seg]), (n, dtype, seg, r)
+            assert bool((p[off_out + seg:] == 7).all())
+        gathered = [torch.full((seg * n + off_out + epp,), 7, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("all_gather", [t[:seg] for t in fin], [t[off_out:off_out + seg * n] for t in gathered], seg, out_seg_stride=seg, algo="ll")
+        torch.cuda.synchronize()
+        refg = torch.cat([t[:seg] for t in fin])
+        for t in gathered:
+            assert torch.equal(t[off_out:off_out + seg * n], refg)
+            assert bool((t[off_out + seg * n:] == 7).all())
+        a2a = [torch.full((seg * n + off_out + epp,), 7, dtype=dtype, device="cuda") for _ in range(n)]
+        g.run("all_to_all", fin, [t[off_out:off_out + seg * n] for t in a2a], seg, in_seg_stride=seg, out_seg_stride=seg, algo="ll")
+        torch.cuda.synchronize()
+        for r, t in enumerate(a2a):
+            assert torch.equal(t[off_out:off_out + seg * n], torch.cat([fin[s][r * seg:(r + 1) * seg] for s in range(n)]))
+        assert g.status(0)[0] == 0
     g.close()
 
 
