@@ -55,7 +55,11 @@ void setLogLevel(int level) { g_log_level.store(level, std::memory_order_relaxed
 
 static bool useColour() {
   static int c = -1;
-  if (c < 0) c = (getenv("NO_COLOR") == nullptr && isatty(2)) ? 1 : 0;
+  if (c < 0) {
+    const char* force = envFirst({"HYLINK_LOG_COLOR", "AMPCCL_LOG_COLOR"});   // 0 / 1 overrides the terminal test
+    if (force) c = (force[0] == '1' || force[0] == 'y' || force[0] == 'Y' || force[0] == 't' || force[0] == 'T') ? 1 : 0;
+    else c = (getenv("NO_COLOR") == nullptr && isatty(2)) ? 1 : 0;
+  }
   return c == 1;
 }
 
@@ -160,6 +164,7 @@ static Config* loadConfig() {
   c->small_ir_max_bytes = (size_t)envInt({"HYLINK_SMALL_IR_MAX_BYTES", "PCCL_SMALL_IR_MAX_BYTES"}, 4LL << 20);
   c->small_msg_threshold_bytes = (size_t)envInt({"HYLINK_SMALL_MSG_THRESHOLD_BYTES", "PCCL_SMALL_MSG_THRESHOLD_BYTES"}, 1LL << 20);
   c->small_msg_fastpath = envBool({"HYLINK_SMALL_MSG_FASTPATH", "PCCL_SMALL_MSG_FASTPATH"}, true);
+  c->small_msg_timeout_ms = (int)envInt({"HYLINK_SMALL_MSG_FASTPATH_TIMEOUT_MS", "PCCL_SMALL_MSG_FASTPATH_TIMEOUT_MS"}, 0);   // 0: the executor's
   c->executor_queue_depth = (int)envInt({"HYLINK_EXECUTOR_QUEUE_DEPTH", "PCCL_EXECUTOR_QUEUE_DEPTH"}, 64);
   c->executor_timeout_ms = (int)envInt({"HYLINK_EXECUTOR_TIMEOUT_MS", "PCCL_EXECUTOR_TIMEOUT_MS"}, 60000);
   c->barrier_timeout_ms = (int)envInt({"HYLINK_BARRIER_TIMEOUT_MS", "PCCL_BARRIER_TIMEOUT_MS"}, 120000);
@@ -182,6 +187,24 @@ static Config* loadConfig() {
   c->symm_mode = envStr({"HYLINK_SYMM_MODE"}, "auto");
   c->symm_heap_bytes = (size_t)envInt({"HYLINK_SYMM_HEAP_BYTES"}, 8LL << 30);
   c->zero_copy = envBool({"HYLINK_ZERO_COPY"}, true);
+  // the reference's switches for peers reading user buffers in place (its CUDA-IPC buffer registry)
+  if (envBool({"PCCL_DISABLE_DEVICE_IPC"}, false)) c->zero_copy = false;
+  if (envBool({"PCCL_FORCE_DEVICE_IPC"}, false)) c->zero_copy = true;
+  c->ipc_close_on_finalize = envBool({"HYLINK_CUDA_IPC_CLOSE_ON_FINALIZE", "PCCL_CUDA_IPC_CLOSE_ON_FINALIZE"}, true);
+  // Settings of the reference that have nothing to switch here: say so once instead of ignoring them silently.
+  static const struct { const char* name; const char* why; } kNoEffect[] = {
+      {"PCCL_NRANKS", "the rank count comes from the communicator"},
+      {"PCCL_BOOTSTRAP_ADDR", "single node only: the control plane is shared memory"},
+      {"PCCL_D2D_PUSH", "peer copies between GPUs ride the NVLink kernels"},
+      {"PCCL_D2D_INPUT_FIRST", "peer copies between GPUs ride the NVLink kernels"},
+      {"PCCL_NCCL_COMPAT_MODE", "threads and processes use the same rendezvous; nothing to detect"},
+      {"PCCL_HOST_POOL_SHM", "shared host pools are always memfd-backed and registered"},
+      {"PCCL_COLD_START_DRAIN", "the context is warmed up by a kernel at communicator creation"},
+      {"AMPCCL_PCCL_UNIQUE_ID", "both paths share one communicator and one id"},
+      {"AMPCCL_PCCL_FORCE_ZERO_UNIQUE_ID", "both paths share one communicator and one id"},
+  };
+  for (const auto& e : kNoEffect)
+    if (const char* v = getenv(e.name)) HL_INFO("%s=%s is accepted and has no effect here: %s", e.name, v, e.why);
   c->oneshot_max_bytes = (size_t)envInt({"HYLINK_ONESHOT_MAX_BYTES"}, 128LL << 10);
   c->pipe_min_bytes = (size_t)envInt({"HYLINK_PIPE_MIN_BYTES"}, 0);
   c->push_min_bytes = (size_t)envInt({"HYLINK_PUSH_MIN_BYTES"}, 32LL << 20);
@@ -287,3 +310,21 @@ int hlVersion(void) { return 100; }
 
 // Re-reads every environment variable (tests flip settings between communicators).
 extern "C" void hlConfigReload(void) { hl::Config::reload(); }
+
+// A few settings by name, as the library resolved them from the environment (-1: unknown name). For tests and for
+// "which value did my variable end up as" questions.
+extern "C" long long hlConfigValue(const char* name) {
+  const hl::Config& c = hl::Config::get();
+  const std::string k = name ? name : "";
+  if (k == "zero_copy") return c.zero_copy ? 1 : 0;
+  if (k == "ipc_close_on_finalize") return c.ipc_close_on_finalize ? 1 : 0;
+  if (k == "small_msg_timeout_ms") return c.small_msg_timeout_ms;
+  if (k == "small_msg_threshold_bytes") return (long long)c.small_msg_threshold_bytes;
+  if (k == "executor_timeout_ms") return c.executor_timeout_ms;
+  if (k == "barrier_timeout_ms") return c.barrier_timeout_ms;
+  if (k == "host_buffer_bytes") return (long long)c.host_buffer_bytes;
+  if (k == "internal_buffer_bytes") return (long long)c.internal_buffer_bytes;
+  if (k == "orch_enable") return c.orch_enable ? 1 : 0;
+  if (k == "min_msg_bytes") return (long long)c.min_msg_bytes;
+  return -1;
+}

@@ -82,6 +82,7 @@ struct Config {
   size_t small_ir_max_bytes;
   size_t small_msg_threshold_bytes;
   bool small_msg_fastpath;
+  int small_msg_timeout_ms;      // bound of a stream-ordered small call before the watchdog releases its flags
   int executor_queue_depth;
   int executor_timeout_ms;
   int barrier_timeout_ms;
@@ -104,6 +105,7 @@ struct Config {
   std::string symm_mode;         // auto | vmm | ipc
   size_t symm_heap_bytes;        // registered-memory heap per rank (created at the first hlMemAlloc)
   bool zero_copy;                // use the zero-copy kernels when a call's buffers are registered
+  bool ipc_close_on_finalize;    // CUDA-IPC fallback: close the peers' mappings at teardown (off: left to process exit)
   size_t oneshot_max_bytes;
   size_t pipe_min_bytes;         // from this size on the pipelined NVLS kernels are used (0 = by rank count)
   size_t push_min_bytes;         // with NVLS available: from this size on the stores-only kernels are used

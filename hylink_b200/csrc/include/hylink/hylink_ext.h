@@ -120,6 +120,8 @@ int hlHostNumaNodes(void);
 void hlTraceOpen(const char* path, int rank);
 void hlTraceFlush(void);
 void hlConfigReload(void);
+/* A setting by name as resolved from the environment (zero_copy, small_msg_timeout_ms, host_buffer_bytes, ...); -1 for an unknown name. */
+long long hlConfigValue(const char* name);
 /* Arms the SIGUSR1 all-threads stack dump (needs HYLINK_SIGDUMP=1). */
 void hlInstallSigdump(void);
 

@@ -293,7 +293,8 @@ void symmFree(Bootstrap* bs, SymmRegion* r, bool peers_gone) {
       if (r->handle[q]) drv->cuMemRelease((CUmemGenericAllocationHandle)r->handle[q]);
     }
   } else if (r->mode == kSymmIpc) {
-    for (int q = 0; q < r->nranks; ++q)
+    // (the reference leaves this to process exit by default: pcie-ccl-cuda/src/core/process_state.cpp:512-525)
+    for (int q = 0; q < r->nranks && Config::get().ipc_close_on_finalize; ++q)
       if (q != r->rank && r->ptr[q]) cudaIpcCloseMemHandle(r->ptr[q]);
     if (!peers_gone && bs) bs->barrier(kBarSymm, 10000);
     cudaFree(r->ptr[r->rank]);

@@ -694,7 +694,8 @@ hlResult_t PcieImpl::submitSmall(const std::string& collective, const void* send
 // Executor thread, between work items: forget the small calls that are through, release everything when one is overdue.
 void PcieImpl::watchSmallCalls() {
   if (!small_host_) return;
-  const uint64_t limit = (uint64_t)Config::get().executor_timeout_ms * 1000000ull;
+  const int limit_ms = Config::get().small_msg_timeout_ms > 0 ? Config::get().small_msg_timeout_ms : Config::get().executor_timeout_ms;
+  const uint64_t limit = (uint64_t)limit_ms * 1000000ull;
   bool overdue = false;
   {
     std::lock_guard<std::mutex> lk(mu_);
@@ -710,7 +711,7 @@ void PcieImpl::watchSmallCalls() {
     }
   }
   if (overdue && last_result_.load() == hlSuccess) {
-    HL_ERR("rank %d: a small-message collective did not complete within %d ms: releasing every flag", rank_, Config::get().executor_timeout_ms);
+    HL_ERR("rank %d: a small-message collective did not complete within %d ms: releasing every flag", rank_, limit_ms);
     for (int k = 0; k < 4 * kMaxRanks; ++k) __atomic_store_n((uint64_t*)small_host_ + k, kReleaseAll, __ATOMIC_RELEASE);
     fail(hlTimeout, "small-message collective timed out (a peer never arrived)");
     failAll(hlTimeout);

@@ -116,3 +116,27 @@ def test_two_in_process_groups_of_the_same_size_at_once():
         t.join(60)
     assert not errors, errors
     assert results == {(0, 0): 3.0, (0, 1): 3.0, (1, 0): 23.0, (1, 1): 23.0}
+
+
+def test_reference_environment_names_are_understood():
+    """Variables of the reference: aliases where this library has the same knob, a notice where it has none."""
+    import os
+    import subprocess
+    import sys
+
+    code = (
+        "import ctypes as C\n"
+        "from hylink_b200._native import lib\n"
+        "lib.hlConfigValue.restype = C.c_longlong\n"
+        "lib.hlConfigValue.argtypes = [C.c_char_p]\n"
+        "print({k: lib.hlConfigValue(k.encode()) for k in ('zero_copy', 'small_msg_timeout_ms', 'ipc_close_on_finalize', 'host_buffer_bytes', 'executor_timeout_ms', 'nope')})\n")
+    env = dict(os.environ, PCCL_DISABLE_DEVICE_IPC="1", PCCL_SMALL_MSG_FASTPATH_TIMEOUT_MS="1234", PCCL_CUDA_IPC_CLOSE_ON_FINALIZE="0",
+               PCCL_HOST_BUFFER_SIZE="64M", PCCL_EXECUTOR_TIMEOUT_MS="5000", PCCL_NCCL_COMPAT_MODE="sp", PCCL_D2D_PUSH="0", HYLINK_LOG_LEVEL="INFO",
+               PYTHONPATH=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = subprocess.run([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert p.returncode == 0, p.stderr[-2000:]
+    got = eval(p.stdout.strip().splitlines()[-1])
+    assert got == {"zero_copy": 0, "small_msg_timeout_ms": 1234, "ipc_close_on_finalize": 0, "host_buffer_bytes": 64 << 20,
+                   "executor_timeout_ms": 5000, "nope": -1}
+    assert "PCCL_NCCL_COMPAT_MODE=sp is accepted and has no effect here" in p.stderr
+    assert "PCCL_D2D_PUSH=0 is accepted and has no effect here" in p.stderr
