@@ -519,6 +519,10 @@ def main() -> int:
                                    "unregistered_busbw_GBs column repeats every cell on ordinary torch tensors (staged kernels)")
                        if registered else "ordinary torch tensors",
                        "busbw": "bytes/time * 2(n-1)/n (all-reduce), * (n-1)/n (reduce-scatter, all-gather); factor 1 with one GPU",
+                       "scaling_note": ("bus bandwidth is the rate every GPU's link sustains, not a sum over GPUs: compare the value at N GPUs "
+                                        "with the link rate (770 GB/s per direction measured for a peer copy) and with NCCL at the same N; "
+                                        "with one GPU nothing crosses a link (the cells are a no-op and two device copies at HBM rate), "
+                                        "so N x the one-GPU value is not a target for N GPUs"),
                        "l2_policy": "two rotating buffer pairs of 1 GiB; a whole pass over the table (> 4 GiB of traffic) lies "
                                     "between two timed calls of a cell, so no cell is served from L2"},
             "clocks": clocks,
