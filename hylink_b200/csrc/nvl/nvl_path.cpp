@@ -636,6 +636,7 @@ hlResult_t NvlPath::launchLowLatency(int kind, const NvlBufs& b, const NvlCall& 
   // one thread per packet it sends to (and receives from) every peer; at most one CTA per SM, so that the CTAs
   // with the same index are resident on every rank at the same time (they wait for one another's packets)
   int cap = c.max_blocks > 0 ? std::min(c.max_blocks, 148) : 148;
+  if (Config::get().nvl_max_blocks > 0) cap = std::min(cap, Config::get().nvl_max_blocks);
   if (emu_) cap = std::min(cap, std::max(1, 148 / nranks_));
   const uint64_t want = std::max<uint64_t>(1, (packets + HL_NVL_THREADS - 1) / HL_NVL_THREADS);
   const int blocks = (int)std::min<uint64_t>(want, (uint64_t)cap);
