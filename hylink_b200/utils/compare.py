@@ -4,6 +4,7 @@
     python -m hylink_b200.utils.compare logs run.log [--csv per_call.csv]
     python -m hylink_b200.utils.compare pipeline --gpus 2,4,8 --out results/ [--bytes-from 1K --bytes-to 1G --factor 4]
     python -m hylink_b200.utils.compare plot nvlink_2gpu.jsonl adaptive_2gpu.jsonl ... --out charts/ [--dtype bf16]
+    python -m hylink_b200.utils.compare interference split_ratio.jsonl static.jsonl --out charts/
 
 * ``sweeps`` merges the JSON lines written by ``hylink_b200.utils.sweep`` (one file per configuration, the file
   name is the label) into one table: a row per (collective, dtype, bytes, ranks), the bus bandwidth of every
@@ -16,6 +17,9 @@
 * ``plot`` draws one chart per collective from sweep files (bus bandwidth against message size, log x axis, one
   line per file plus NCCL's per rank count) as plain SVG, written without any plotting library
   (tests/nccl_test/test_scripts/plot_bw_comparison.py in the reference, which needs matplotlib). ``pipeline`` calls it.
+* ``interference`` draws the two charts of the interference experiment from the files written by
+  ``hylink_b200.utils.interference --out``: bus bandwidth per call and PCIe share per call, one line per controller,
+  the load levels marked.
 * ``pipeline`` runs the sweep for every GPU count in two configurations — NVLink kernels only, and the adaptive
   multipath split — each against NCCL in the same process, and merges the results
   (tests/nccl_test/test_scripts/run_full_pipeline.sh in the reference: baseline vs adaptive x {AG, AR, RS} x
@@ -123,15 +127,18 @@ def _size_label(b: int) -> str:
     return str(b)
 
 
-def svg_chart(title: str, series: dict, path: str, width: int = 860, height: int = 480) -> None:
-    """series: label -> [(bytes, GB/s), ...]. Log2 x axis, linear y axis, dashed lines for labels that start with
-    'NCCL'. Plain SVG text, no dependencies."""
+def svg_chart(title: str, series: dict, path: str, width: int = 860, height: int = 480, logx: bool = True,
+              xlabel: str = "message size (bytes)", ylabel: str = "bus bandwidth (GB/s)", marks=None) -> None:
+    """series: label -> [(x, y), ...]. Log2 (message sizes) or linear x axis, linear y axis, dashed lines for labels
+    that start with 'NCCL'; `marks`: [(x, text), ...] vertical lines with a caption. Plain SVG text, no dependencies."""
     import math
+
+    fx = (lambda v: math.log2(v)) if logx else (lambda v: float(v))
 
     pts = [p for v in series.values() for p in v]
     if not pts:
         return
-    x0, x1 = math.log2(min(p[0] for p in pts)), math.log2(max(p[0] for p in pts))
+    x0, x1 = fx(min(p[0] for p in pts)), fx(max(p[0] for p in pts))
     if x1 == x0:
         x1 = x0 + 1
     ymax = max(p[1] for p in pts) * 1.08 or 1.0
@@ -141,7 +148,7 @@ def svg_chart(title: str, series: dict, path: str, width: int = 860, height: int
     pw, ph = width - ml - mr, height - mt - mb
 
     def sx(b):
-        return ml + (math.log2(b) - x0) / (x1 - x0) * pw
+        return ml + (fx(b) - x0) / (x1 - x0) * pw
 
     def sy(v):
         return mt + ph - v / ymax * ph
@@ -163,16 +170,20 @@ def svg_chart(title: str, series: dict, path: str, width: int = 860, height: int
             continue
         x = sx(b)
         o.append(f'<line x1="{x:.1f}" y1="{mt + ph}" x2="{x:.1f}" y2="{mt + ph + 5}" stroke="#444"/>')
-        o.append(f'<text x="{x:.1f}" y="{mt + ph + 20}" text-anchor="middle">{_size_label(b)}</text>')
-    o.append(f'<text x="{ml + pw / 2}" y="{height - 8}" text-anchor="middle">message size (bytes)</text>')
-    o.append(f'<text x="16" y="{mt + ph / 2}" text-anchor="middle" transform="rotate(-90 16 {mt + ph / 2})">bus bandwidth (GB/s)</text>')
+        o.append(f'<text x="{x:.1f}" y="{mt + ph + 20}" text-anchor="middle">{_size_label(b) if logx else b}</text>')
+    for mx, text in (marks or []):
+        x = sx(mx)
+        o.append(f'<line x1="{x:.1f}" y1="{mt}" x2="{x:.1f}" y2="{mt + ph}" stroke="#999" stroke-dasharray="3 3"/>')
+        o.append(f'<text x="{x + 4:.1f}" y="{mt + 12}" fill="#666">{text}</text>')
+    o.append(f'<text x="{ml + pw / 2}" y="{height - 8}" text-anchor="middle">{xlabel}</text>')
+    o.append(f'<text x="16" y="{mt + ph / 2}" text-anchor="middle" transform="rotate(-90 16 {mt + ph / 2})">{ylabel}</text>')
     for i, (label, data) in enumerate(series.items()):
         col = _COLOURS[i % len(_COLOURS)]
         data = sorted(data)
         dash = ' stroke-dasharray="6 4"' if label.startswith("NCCL") else ""
         o.append(f'<polyline fill="none" stroke="{col}" stroke-width="2"{dash} points="' +
                  " ".join(f"{sx(b):.1f},{sy(v):.1f}" for b, v in data) + '"/>')
-        for b, v in data:
+        for b, v in data if len(data) <= 64 else []:
             o.append(f'<circle cx="{sx(b):.1f}" cy="{sy(v):.1f}" r="3" fill="{col}"/>')
         ly = mt + 14 + 18 * i
         o.append(f'<line x1="{ml + pw + 12}" y1="{ly - 4}" x2="{ml + pw + 36}" y2="{ly - 4}" stroke="{col}" stroke-width="2"{dash}/>')
@@ -203,6 +214,32 @@ def plot_sweeps(files, out_dir: str, dtype: str = "bf16"):
         svg_chart(f"{coll} - bus bandwidth ({dtype})", dict(sorted(series.items())), path)
         written.append(path)
     return written
+
+
+def plot_interference(files, out_dir: str):
+    """Per-call bus bandwidth and PCIe share of interference runs (the JSON lines of ``hylink_b200.utils.interference``,
+    one file per controller), with the load levels marked: the two charts of the reference's experiment
+    (tests/hccl_test/inference_experiment in the reference draws them with matplotlib)."""
+    os.makedirs(out_dir, exist_ok=True)
+    bw, share, marks = {}, {}, []
+    for f in files:
+        label = os.path.splitext(os.path.basename(f))[0]
+        level = None
+        with open(f) as fh:
+            for line in fh:
+                r = json.loads(line)
+                if "iter" not in r:
+                    continue
+                bw.setdefault(label, []).append((r["iter"], r["busbw_GBs"]))
+                share.setdefault(label, []).append((r["iter"], 100.0 * r["alpha"]))
+                if r["interference_pct"] != level and f == files[0]:
+                    level = r["interference_pct"]
+                    marks.append((r["iter"], f"{level} % load"))
+    a, b = os.path.join(out_dir, "interference_busbw_per_call.svg"), os.path.join(out_dir, "interference_pcie_share_per_call.svg")
+    svg_chart("forked all-reduce under PCIe load - bus bandwidth per call", bw, a, logx=False, xlabel="call", marks=marks)
+    svg_chart("forked all-reduce under PCIe load - share of the bytes on PCIe", share, b, logx=False, xlabel="call",
+              ylabel="PCIe share (%)", marks=marks)
+    return [a, b]
 
 
 def run_pipeline(args) -> int:
@@ -256,7 +293,14 @@ def main(argv=None) -> int:
     p.add_argument("files", nargs="+")
     p.add_argument("--out", default=".")
     p.add_argument("--dtype", default="bf16")
+    p = sub.add_parser("interference")
+    p.add_argument("files", nargs="+")
+    p.add_argument("--out", default=".")
     args = ap.parse_args(argv)
+    if args.cmd == "interference":
+        for path in plot_interference(args.files, args.out):
+            print("wrote", path)
+        return 0
     if args.cmd == "plot":
         for path in plot_sweeps(args.files, args.out, args.dtype):
             print("wrote", path)

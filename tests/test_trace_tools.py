@@ -129,6 +129,33 @@ def test_sweep_files_plot_as_svg_without_a_plotting_library(tmp_path):
     assert "nvlink_2gpu" in labels and "NCCL (4 GPUs)" in labels and "1G" in labels
 
 
+def test_interference_runs_plot_as_two_charts(tmp_path):
+    import json
+    import xml.dom.minidom
+
+    from hylink_b200.utils import compare
+
+    def run(alpha):
+        rows = [json.dumps({"event": "nvlink_only", "interference_pct": 0, "ms": 0.5, "busbw_GBs": 600.0})]
+        for i in range(40):
+            lvl = (0, 25, 50, 75)[i // 10]
+            rows.append(json.dumps({"iter": i, "interference_pct": lvl, "ms": 1.0, "busbw_GBs": 400.0 - lvl, "alpha": alpha / (1 + lvl / 25),
+                                    "fast_ms": 0.7, "pcie_ms": 0.9}))
+        return "\n".join(rows) + "\n"
+
+    (tmp_path / "split_ratio.jsonl").write_text(run(0.04))
+    (tmp_path / "static.jsonl").write_text(run(0.05))
+    out = tmp_path / "charts"
+    assert compare.main(["interference", str(tmp_path / "split_ratio.jsonl"), str(tmp_path / "static.jsonl"), "--out", str(out)]) == 0
+    for name in ("interference_busbw_per_call.svg", "interference_pcie_share_per_call.svg"):
+        doc = xml.dom.minidom.parse(str(out / name))
+        lines = doc.getElementsByTagName("polyline")
+        assert len(lines) == 2 and all(len(l.getAttribute("points").split()) == 40 for l in lines)
+        captions = [t.firstChild.data for t in doc.getElementsByTagName("text") if t.firstChild]
+        assert [c for c in captions if c.endswith("% load")] == ["0 % load", "25 % load", "50 % load", "75 % load"]
+        assert "split_ratio" in captions and "static" in captions
+
+
 def test_kernel_timeline_decoder_on_a_synthetic_ring():
     from hylink_b200.utils import kernel_timeline as kt
 
