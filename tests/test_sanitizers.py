@@ -29,3 +29,18 @@ def test_collectives_on_the_host_device_are_clean(kind):
                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300, env=env)
         assert p.returncode == 0 and "Test PASSED." in p.stdout, p.stdout[-3000:]
         assert "WARNING: ThreadSanitizer" not in p.stdout and "ERROR: AddressSanitizer" not in p.stdout, p.stdout[-3000:]
+    # worker-owned host ranges (two NUMA pools, reductions on the CPU) and rounds ordered by chunk guards (pools far
+    # smaller than the message): the two places where threads of several ranks hand data on without the executor
+    scenarios = [
+        (dict(HYLINK_GPU_NUMA_MAP="0011", HYLINK_IR_VARIANT="host_reduce", HYLINK_H2H_WORKERS="2"),
+         ["--coll", "allreduce", "--ranks", "4", "--bytes-from", "4M", "--bytes-to", "4M"]),
+        (dict(HYLINK_GPU_NUMA_MAP="0011", HYLINK_HOST_BUFFER_SIZE="2M", HYLINK_INTERNAL_BUFFER_BYTES="1M"),
+         ["--coll", "allgather", "--ranks", "4", "--bytes-from", "8M", "--bytes-to", "8M"]),
+        (dict(HYLINK_HOST_BUFFER_SIZE="2M", HYLINK_INTERNAL_BUFFER_BYTES="1M"),
+         ["--coll", "allreduce", "--ranks", "2", "--bytes-from", "8M", "--bytes-to", "8M"]),
+    ]
+    for extra, args in scenarios:
+        p = subprocess.run([str(tool)] + args + ["--mode", "threads", "--device", "host", "--iters", "2"],
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=300, env=dict(env, **extra))
+        assert p.returncode == 0 and "Test PASSED." in p.stdout, (extra, p.stdout[-3000:])
+        assert "WARNING: ThreadSanitizer" not in p.stdout and "ERROR: AddressSanitizer" not in p.stdout, (extra, p.stdout[-3000:])
