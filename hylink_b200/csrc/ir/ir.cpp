@@ -358,6 +358,7 @@ hlResult_t generate(const std::string& collective, const std::vector<int>& gpu_n
   g.p.topology = topologyName(gpu_numa);
   const bool single = variant == "single_d2h";
   const bool host_reduce = variant == "host_reduce";
+  const bool ring = variant == "ring";
   const int K = std::max(1, std::min(n - 1, 4));  // landing slots in the internal buffer
   auto numaOf = [&](int r) { return gpu_numa[(size_t)r]; };
 
@@ -400,7 +401,40 @@ hlResult_t generate(const std::string& collective, const std::vector<int>& gpu_n
   } else if (collective == "reducescatter" || collective == "allreduce") {
     const bool ar = collective == "allreduce";
     const int out_chunk_of_owner = 0;
-    if (!host_reduce) {
+    if (ring) {
+      // Segment s travels once around the ring s+1, s+2, ..., s through host memory: the first rank uploads its
+      // contribution, every later rank folds its own contribution into the travelling partial sum on the CPU
+      // (H2HReduce), the owner s folds last and downloads the result. The CPU work of a segment is spread over n - 1
+      // ranks instead of sitting on the owner (the host_reduce variant).
+      g.p.description = "generated: ring through host memory, every rank folds its own contribution into the travelling partial sum on the CPU";
+      auto pos = [&](int s, int r) { const int k = (r - s + n) % n; return k == 0 ? n : k; };   // 1-based place of r in the chain of segment s
+      auto consumer = [&](int s, int r) { return pos(s, r) == 1 ? (r + 1) % n : r; };           // who reads contribution (s, r)
+      auto acc = [&](int s, int k) { return n * n + s * n + k; };                              // partial sum of segment s after k contributions
+      for (int r = 0; r < n; ++r) {
+        const int own_out = ar ? r : out_chunk_of_owner;
+        for (int k = 1; k <= n; ++k) {
+          const int s = (r - k + n) % n;   // the segment in whose chain r has place k
+          g.d2h(r, Buf::Input, s, s * n + r, numaOf(consumer(s, r)));
+        }
+        if (n == 1) {
+          g.h2d(r, r * n + r, numaOf(r), Buf::Output, own_out);
+          continue;
+        }
+        for (int k = 2; k <= n; ++k) {
+          const int s = (r - k + n) % n;
+          const int prev_rank = (r - 1 + n) % n;
+          const int prev = k == 2 ? s * n + prev_rank : acc(s, k - 1);
+          const int dst_numa = k == n ? numaOf(r) : numaOf((r + 1) % n);
+          g.h2hReduce(r, prev, numaOf(r), s * n + r, numaOf(r), acc(s, k), dst_numa);
+        }
+        g.h2d(r, acc(r, n), numaOf(r), Buf::Output, own_out);
+        if (ar)
+          for (int k = 1; k < n; ++k) {
+            const int q = (r + k) % n;
+            g.h2d(r, acc(q, n), numaOf(q), Buf::Output, q);
+          }
+      }
+    } else if (!host_reduce) {
       g.p.description = ar ? "generated: mesh reduce-scatter with device reduce on landing, then all-gather through NUMA-local host chunks"
                            : "generated: one-shot mesh, owner reduces every landed contribution on the device";
       for (int r = 0; r < n; ++r) {

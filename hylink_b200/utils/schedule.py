@@ -123,7 +123,7 @@ def emit_standard_set(directory: str | Path, patterns=STANDARD_PATTERNS) -> list
             if coll in ("allgather", "alltoall") and len(set(pat)) > 1:
                 variants.append("single_d2h")
             if coll in ("allreduce", "reducescatter"):
-                variants.append("host_reduce")
+                variants += ["host_reduce", "ring"]
             for v in variants:
                 p = d / (f"{coll}_{pat}" + (f"_{v}" if v else "") + ".xml")
                 p.write_text(generate(coll, pat, v))

@@ -54,7 +54,7 @@ def test_generator_covers_every_pattern(pattern, coll):
     ss, rs = S.segments(coll, n)
     variants = [""]
     if coll in ("allreduce", "reducescatter"):
-        variants.append("host_reduce")
+        variants += ["host_reduce", "ring"]
     if coll in ("allgather", "alltoall"):
         variants.append("single_d2h")
     for v in variants:
@@ -62,12 +62,12 @@ def test_generator_covers_every_pattern(pattern, coll):
         info = S.inspect(xml, pattern, ss, rs)
         assert info["nranks"] == n
         assert info["numa_nodes"] <= len(set(pattern))
-        assert info["uses_host_reduce"] == (1 if (v == "host_reduce" and n > 1) else 0)
+        assert info["uses_host_reduce"] == (1 if (v in ("host_reduce", "ring") and n > 1) else 0)
         if coll in ("allreduce", "alltoall"):
             S.inspect(xml, pattern, ss, rs, in_place="same")
         if coll == "allgather":
             S.inspect(xml, pattern, ss, rs, in_place="gather_slot")
-        if coll == "reducescatter" and v == "":
+        if coll == "reducescatter" and v in ("", "ring"):
             S.inspect(xml, pattern, ss, rs, in_place="scatter_slot")
 
 

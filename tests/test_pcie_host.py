@@ -416,3 +416,34 @@ def test_allreduce_fp16(n, numa):
     env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP=numa)
     run_ranks(_allreduce_worker, n, 3 << 18, "float16", False, env=env)
     run_ranks(_allreduce_worker, n, 100003, "float16", True, env=dict(env, HYLINK_IR_VARIANT="host_reduce"))
+
+
+def _ring_worker(rank, n, uid):
+    c = _comm(rank, n, uid)
+    count = n * 400003                                   # several slices per chunk, odd segment length
+    x = _data(rank, count, torch.float32, seed=21)
+    out = torch.zeros(count)
+    c.all_reduce(x, out)
+    seg = count // n
+    part = torch.zeros(seg)
+    c.reduce_scatter(x, part)
+    inplace = x.clone()
+    c.all_reduce(inplace, inplace)
+    c.drain()
+    ref = sum(_data(r, count, torch.float32, seed=21).double() for r in range(n))
+    assert torch.allclose(out.double(), ref, atol=1e-5)
+    assert torch.allclose(part.double(), ref[rank * seg:(rank + 1) * seg], atol=1e-5)
+    assert torch.allclose(inplace.double(), ref, atol=1e-5)
+    st = c.stats()
+    c.close()
+    return st["h2h_range_jobs"]
+
+
+@pytest.mark.parametrize("n,numa", [(2, "00"), (3, "001"), (4, "0011"), (8, "00112233")])
+def test_ring_schedules_through_host_memory(n, numa):
+    """The ring variant of the generator: a segment's partial sum travels around the ring through host memory and
+    every rank folds its own contribution on the CPU (the plumbing configuration: fp32 sum, host-memory device)."""
+    env = dict(SMALL_POOLS, HYLINK_GPU_NUMA_MAP=numa, HYLINK_IR_VARIANT="ring", HYLINK_H2H_WORKERS="2")
+    jobs = run_ranks(_ring_worker, n, env=env, timeout=300)
+    if n <= 4:   # with 8 ranks the 64 MiB test pools cut the message into rounds of single-slice chunks
+        assert all(j > 0 for j in (jobs.values() if isinstance(jobs, dict) else jobs))  # the folds ran as worker-owned ranges

@@ -34,6 +34,8 @@ def test_collectives_on_the_host_device_are_clean(kind):
     scenarios = [
         (dict(HYLINK_GPU_NUMA_MAP="0011", HYLINK_IR_VARIANT="host_reduce", HYLINK_H2H_WORKERS="2"),
          ["--coll", "allreduce", "--ranks", "4", "--bytes-from", "4M", "--bytes-to", "4M"]),
+        (dict(HYLINK_GPU_NUMA_MAP="0011", HYLINK_IR_VARIANT="ring", HYLINK_H2H_WORKERS="1"),
+         ["--coll", "allreduce", "--ranks", "4", "--bytes-from", "8M", "--bytes-to", "8M"]),
         (dict(HYLINK_GPU_NUMA_MAP="0011", HYLINK_HOST_BUFFER_SIZE="2M", HYLINK_INTERNAL_BUFFER_BYTES="1M"),
          ["--coll", "allgather", "--ranks", "4", "--bytes-from", "8M", "--bytes-to", "8M"]),
         (dict(HYLINK_HOST_BUFFER_SIZE="2M", HYLINK_INTERNAL_BUFFER_BYTES="1M"),
