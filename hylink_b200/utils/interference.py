@@ -95,6 +95,7 @@ def main(argv=None) -> int:
     ap.add_argument("--static-alpha", type=float, default=0.05)
     ap.add_argument("--coll", default="allreduce", choices=["allreduce", "allgather", "reducescatter"])
     ap.add_argument("--out", default="")
+    ap.add_argument("--charts", default="", metavar="DIR", help="with --out: also draw the per-call bandwidth and PCIe-share charts (SVG) into DIR")
     a = ap.parse_args(argv)
 
     os.environ["HYLINK_ORCH_ENABLE"] = "1"
@@ -194,6 +195,13 @@ def main(argv=None) -> int:
     bg.join(2)
     if rank == 0:
         print(json.dumps({"event": "done", "tuning": json.loads(comm.dump_tuning())}), flush=True)
+        if outf:
+            outf.close()
+            if a.charts:
+                from hylink_b200.utils.compare import plot_interference
+
+                for path in plot_interference([a.out], a.charts):
+                    print(json.dumps({"event": "chart", "file": path}), flush=True)
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
